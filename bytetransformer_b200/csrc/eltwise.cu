@@ -1,0 +1,354 @@
+// HBM-bound row kernels: (add bias + residual +) LayerNorm, the same fused with
+// the packed -> padded scatter, add-bias + GELU, and masked softmax.
+//
+// All of them use 16-byte global accesses and warp-shuffle reductions; one warp
+// owns one row, so no shared memory or block barrier is needed.
+//
+// Reference counterparts (paths relative to the ByteTransformer root):
+//   layernorm_rows_kernel<false>  add_bias_input_layernorm{,_v2}
+//                                 (bytetransformer/include/layernorm.h:273-296, src/layernorm.cu:89-102)
+//   layernorm_rows_kernel<true>   add_bias_input_layernorm_restore_output{,_v2}
+//                                 (layernorm.h:334-373, layernorm.cu:126-148)
+//   add_bias_gelu_kernel          add_bias_gelu (bytetransformer/src/gemm_bias_act.cu:32-47)
+//   masked_softmax_kernel         softmax_kernel_warp_half2* (bytetransformer/include/softmax.h:25-297)
+// Differences kept on purpose: the sums x + bias + residual are formed in fp32
+// (the reference adds in fp16 first, layernorm.h:289-290); statistics are
+// two-pass (mean, then centred variance) in fp32 as in the reference.
+//
+// Algorithmic bytes per row of H halves: LayerNorm reads x (+ residual) and
+// writes out: 6*H bytes with residual, 4*H without; the restore variant writes
+// every padded row (2*H bytes each, zeros for padding).
+#include "common.cuh"
+#include "kernels.h"
+#include "../../include/bt_b200.h"
+
+namespace bt {
+
+namespace {
+
+constexpr int kLnWarps = 4;
+constexpr int kLnMaxVec = 4;  // register-resident rows up to 4*32*8 = 1024 halves
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  q.x = pack_half2(f[0], f[1]);
+  q.y = pack_half2(f[2], f[3]);
+  q.z = pack_half2(f[4], f[5]);
+  q.w = pack_half2(f[6], f[7]);
+  return q;
+}
+
+template <bool GB_FP32>
+__device__ __forceinline__ void load_gb8(const void* p, int vec, float (&f)[8]) {
+  if (GB_FP32) {
+    const float4* fp = reinterpret_cast<const float4*>(p) + 2 * vec;
+    const float4 a = __ldg(fp), b = __ldg(fp + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + vec);
+    unpack8(q, f);
+  }
+}
+
+// RESTORE = false: rows [0, M) of x -> rows [0, M) of out.
+// RESTORE = true : grid covers the B*S padded rows; row (b,i) reads packed row
+//                  batch_idx[b]+i when i < len_b, else writes zeros.
+template <bool RESTORE, bool GB_FP32, int NVEC>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ bias,
+                      const __half* __restrict__ residual, const void* __restrict__ gamma,
+                      const void* __restrict__ beta, __half* __restrict__ out, const int* __restrict__ m_dev,
+                      int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * kLnWarps + warp;
+  const int nvec = hidden / 8;
+  long long src_row = row;
+  if (RESTORE) {
+    if (row >= m_rows) return;  // m_rows = B*S here
+    const int b = static_cast<int>(row / S);
+    const int i = static_cast<int>(row - static_cast<long long>(b) * S);
+    const int off = __ldg(batch_idx + b);
+    const int len = __ldg(batch_idx + b + 1) - off;
+    if (i >= len) {
+      uint4* o4 = reinterpret_cast<uint4*>(out + row * hidden);
+      for (int v = lane; v < nvec; v += 32) o4[v] = make_uint4(0u, 0u, 0u, 0u);
+      return;
+    }
+    src_row = off + i;
+  } else {
+    int M = m_rows;
+    if (m_dev != nullptr) {
+      const int md = __ldg(m_dev);
+      M = md < M ? md : M;
+    }
+    if (row >= M) return;
+  }
+
+  const uint4* x4 = reinterpret_cast<const uint4*>(x + src_row * hidden);
+  const uint4* r4 = residual ? reinterpret_cast<const uint4*>(residual + src_row * hidden) : nullptr;
+  const uint4* b4 = bias ? reinterpret_cast<const uint4*>(bias) : nullptr;
+
+  float val[NVEC][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int it = 0; it < NVEC; ++it) {
+    const int v = it * 32 + lane;
+    if (v < nvec) {
+      unpack8(__ldg(x4 + v), val[it]);
+      if (r4) {
+        float t[8];
+        unpack8(__ldg(r4 + v), t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) val[it][k] += t[k];
+      }
+      if (b4) {
+        float t[8];
+        unpack8(__ldg(b4 + v), t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) val[it][k] += t[k];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sum += val[it][k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) val[it][k] = 0.f;
+    }
+  }
+  const float mean = warp_sum(sum) / static_cast<float>(hidden);
+  float sq = 0.f;
+#pragma unroll
+  for (int it = 0; it < NVEC; ++it) {
+    if (it * 32 + lane < nvec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float d = val[it][k] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(hidden) + eps);
+
+  uint4* o4 = reinterpret_cast<uint4*>(out + row * hidden);
+#pragma unroll
+  for (int it = 0; it < NVEC; ++it) {
+    const int v = it * 32 + lane;
+    if (v < nvec) {
+      float g[8], bt_[8], o[8];
+      load_gb8<GB_FP32>(gamma, v, g);
+      load_gb8<GB_FP32>(beta, v, bt_);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = fmaf((val[it][k] - mean) * rstd, g[k], bt_[k]);
+      o4[v] = pack8(o);
+    }
+  }
+}
+
+template <bool RESTORE, bool GB_FP32>
+cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, const __half* x, const __half* bias,
+                           const __half* residual, const void* gamma, const void* beta, __half* out,
+                           const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps) {
+#define BT_LN_CASE(NV)                                                                                        \
+  case NV:                                                                                                    \
+    layernorm_rows_kernel<RESTORE, GB_FP32, NV><<<grid, kLnWarps * 32, 0, stream>>>(                          \
+        x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps);                       \
+    break;
+  switch (nvec_needed) {
+    BT_LN_CASE(1)
+    BT_LN_CASE(2)
+    BT_LN_CASE(3)
+    BT_LN_CASE(4)
+    default: return cudaErrorInvalidValue;
+  }
+#undef BT_LN_CASE
+  return cudaGetLastError();
+}
+
+__global__ void __launch_bounds__(256)
+add_bias_gelu_kernel(uint4* __restrict__ x, const uint4* __restrict__ bias, const int* __restrict__ m_dev,
+                     int m_rows, int nvec, int gelu_kind) {
+  int M = m_rows;
+  if (m_dev != nullptr) {
+    const int md = __ldg(m_dev);
+    M = md < M ? md : M;
+  }
+  const long long total = static_cast<long long>(M) * nvec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % nvec);
+    float f[8], b[8];
+    unpack8(x[i], f);
+    unpack8(__ldg(bias + v), b);
+    if (gelu_kind == BT_GELU_TANH) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = gelu_tanh(f[k] + b[k]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + b[k]);
+    }
+    x[i] = pack8(f);
+  }
+}
+
+// One warp per logits row; logits are laid out [nh, B, S, S] as in the reference
+// (softmax.h:33: ((head*B + b)*S + i)*S); S <= 1024.  VEC path: S % 8 == 0.
+template <bool VEC>
+__global__ void __launch_bounds__(128)
+masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ mask, int B, int nh, int S,
+                      float scale) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * 4 + warp;
+  const long long rows = static_cast<long long>(B) * nh * S;
+  if (row >= rows) return;
+  const int i = static_cast<int>(row % S);
+  const int b = static_cast<int>((row / S) % B);
+  __half* lp = logits + row * S;
+  const __half* mp = mask + (static_cast<long long>(b) * S + i) * S;
+  if (VEC) {
+    const int nvec = S / 8;
+    float val[4][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int v = it * 32 + lane;
+      if (v < nvec) {
+        float m[8];
+        unpack8(*(reinterpret_cast<const uint4*>(lp) + v), val[it]);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(mp) + v), m);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          val[it][k] = fmaf(val[it][k], scale, (1.0f - m[k]) * -10000.0f);
+          mx = fmaxf(mx, val[it][k]);
+        }
+      }
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      if (it * 32 + lane < nvec) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          val[it][k] = __expf(val[it][k] - mx);
+          sum += val[it][k];
+        }
+      }
+    }
+    const float inv = 1.0f / (warp_sum(sum) + 1e-6f);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int v = it * 32 + lane;
+      if (v < nvec) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) val[it][k] *= inv;
+        *(reinterpret_cast<uint4*>(lp) + v) = pack8(val[it]);
+      }
+    }
+  } else {
+    float val[32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < 32; ++it) {
+      const int j = it * 32 + lane;
+      if (j < S) {
+        val[it] = fmaf(__half2float(lp[j]), scale, (1.0f - __half2float(mp[j])) * -10000.0f);
+        mx = fmaxf(mx, val[it]);
+      }
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < 32; ++it) {
+      if (it * 32 + lane < S) {
+        val[it] = __expf(val[it] - mx);
+        sum += val[it];
+      }
+    }
+    const float inv = 1.0f / (warp_sum(sum) + 1e-6f);
+#pragma unroll
+    for (int it = 0; it < 32; ++it) {
+      const int j = it * 32 + lane;
+      if (j < S) lp[j] = __float2half_rn(val[it] * inv);
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_layernorm(const __half* x, const __half* bias, const __half* residual, const void* gamma,
+                             const void* beta, bool gb_fp32, __half* out, const int* m_dev, int m_rows, int hidden,
+                             float eps, cudaStream_t stream) {
+  if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || m_rows <= 0) return cudaErrorInvalidValue;
+  const int nv = (hidden / 8 + 31) / 32;
+  dim3 grid((m_rows + kLnWarps - 1) / kLnWarps);
+  if (gb_fp32)
+    return launch_ln_nvec<false, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                       nullptr, 0, hidden, eps);
+  return launch_ln_nvec<false, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                      nullptr, 0, hidden, eps);
+}
+
+cudaError_t launch_layernorm_restore(const __half* x, const __half* bias, const __half* residual,
+                                     const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
+                                     const int* batch_idx, int B, int S, int hidden, float eps,
+                                     cudaStream_t stream) {
+  if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || B <= 0 || S <= 0) return cudaErrorInvalidValue;
+  const int nv = (hidden / 8 + 31) / 32;
+  const long long rows = static_cast<long long>(B) * S;
+  dim3 grid(static_cast<unsigned>((rows + kLnWarps - 1) / kLnWarps));
+  if (gb_fp32)
+    return launch_ln_nvec<true, true>(nv, grid, stream, x, bias, residual, gamma, beta, out_padded, nullptr,
+                                      static_cast<int>(rows), batch_idx, S, hidden, eps);
+  return launch_ln_nvec<true, false>(nv, grid, stream, x, bias, residual, gamma, beta, out_padded, nullptr,
+                                     static_cast<int>(rows), batch_idx, S, hidden, eps);
+}
+
+cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev, int m_rows, int n, int gelu_kind,
+                                 cudaStream_t stream) {
+  if (n % 8 != 0 || m_rows <= 0) return cudaErrorInvalidValue;
+  const int nvec = n / 8;
+  long long total = static_cast<long long>(m_rows) * nvec;
+  long long g = (total + 256 * 2 - 1) / (256 * 2);
+  if (g < 1) g = 1;
+  if (g > 148 * 16) g = 148 * 16;
+  add_bias_gelu_kernel<<<static_cast<int>(g), 256, 0, stream>>>(reinterpret_cast<uint4*>(x),
+                                                                reinterpret_cast<const uint4*>(bias), m_dev, m_rows,
+                                                                nvec, gelu_kind);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int nh, int S, float scale,
+                                  cudaStream_t stream) {
+  if (S <= 0 || S > 1024 || B <= 0 || nh <= 0) return cudaErrorInvalidValue;
+  const long long rows = static_cast<long long>(B) * nh * S;
+  dim3 grid(static_cast<unsigned>((rows + 3) / 4));
+  if (S % 8 == 0)
+    masked_softmax_kernel<true><<<grid, 128, 0, stream>>>(logits, mask, B, nh, S, scale);
+  else
+    masked_softmax_kernel<false><<<grid, 128, 0, stream>>>(logits, mask, B, nh, S, scale);
+  return cudaGetLastError();
+}
+
+}  // namespace bt

@@ -1,0 +1,506 @@
+// Host side of the library: the encoder object behind the C ABI, tensor-map
+// management, workspace carving and the per-layer launch sequence.
+//
+// Launch sequence of one layer on a packed batch x[T,H] (compare the reference's
+// nine steps in bytetransformer/src/bert_transformer.cu:62-124):
+//   1. qkv  = x * Wqkv + b_qkv                         GEMM, bias epilogue
+//   2. ctx  = fused MHA(qkv)                           one kernel, any length
+//   3. pre  = ctx * Wo + b_o + x                       GEMM, bias+residual epilogue
+//   4. y    = LN(pre)                                  row kernel
+//   5. mid  = gelu(y * W1 + b_1)                       GEMM, bias+GELU epilogue
+//   6. pre  = mid * W2 + b_2 + y                       GEMM, bias+residual epilogue
+//   7. out  = LN(pre)   (last layer of a padded call: LN + scatter + zero fill)
+// Offsets and pack run once per call, not once per layer, and the token count T
+// never travels to the host: every kernel reads it from batch_idx[B].
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "../../include/bt_b200.h"
+
+namespace bt {
+
+__device__ int g_status_word = 0;
+
+int* device_status_word() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;
+  return p;
+}
+
+// ------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                  uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * 2) % 16 != 0) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// --------------------------------------------------------------------- encoder
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols;
+  uint32_t box_cols, box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows;
+  }
+};
+
+struct LayerState {
+  bt_layer_weights w;
+  bool set = false;
+};
+
+}  // namespace bt
+
+struct bt_encoder_s {
+  bt_config cfg;
+  int hidden = 0;
+  int ffn = 0;
+  int device = 0;
+  int num_sms = 148;
+  int* status = nullptr;
+  std::string err;
+  std::vector<bt::LayerState> layers;
+  // small cache of encoded tensor maps (activations and weights)
+  std::vector<std::pair<bt::TmapKey, CUtensorMap>> tmaps;
+  size_t tmap_next = 0;
+
+  const CUtensorMap* tmap(const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    bt::TmapKey k{base, rows, cols, box_cols, box_rows};
+    for (auto& e : tmaps)
+      if (e.first == k) return &e.second;
+    CUtensorMap m;
+    if (!bt::make_tmap_2d(&m, base, rows, cols, cols, box_cols, box_rows)) return nullptr;
+    const size_t cap = 256;
+    if (tmaps.size() < cap) {
+      tmaps.emplace_back(k, m);
+      return &tmaps.back().second;
+    }
+    tmaps[tmap_next] = std::make_pair(k, m);
+    const CUtensorMap* r = &tmaps[tmap_next].second;
+    tmap_next = (tmap_next + 1) % cap;
+    return r;
+  }
+};
+
+namespace bt {
+
+static int fail(bt_handle h, int code, const char* msg) {
+  if (h) h->err = msg;
+  return code;
+}
+static int fail_cuda(bt_handle h, cudaError_t e, const char* where) {
+  if (h) h->err = std::string(where) + ": " + cudaGetErrorString(e);
+  return BT_ERR_CUDA;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+  int* batch_idx;
+  int* word_idx;
+  __half *xa, *xb, *qkv, *ctx, *pre, *y, *mid;
+  size_t bytes;
+};
+
+// rows = allocated packed rows; n_idx = ints reserved for batch_idx/word_idx (0 for the packed entry)
+static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_batch_idx, size_t n_word_idx) {
+  Workspace w;
+  uint8_t* p = reinterpret_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* r = p ? p + off : nullptr;
+    off += align_up(bytes, 1024);
+    return r;
+  };
+  w.batch_idx = reinterpret_cast<int*>(take(n_batch_idx * 4));
+  w.word_idx = reinterpret_cast<int*>(take(n_word_idx * 4));
+  const size_t rh = rows * static_cast<size_t>(hidden) * 2;
+  w.xa = reinterpret_cast<__half*>(take(rh));
+  w.xb = reinterpret_cast<__half*>(take(rh));
+  w.qkv = reinterpret_cast<__half*>(take(3 * rh));
+  w.ctx = reinterpret_cast<__half*>(take(rh));
+  w.pre = reinterpret_cast<__half*>(take(rh));
+  w.y = reinterpret_cast<__half*>(take(rh));
+  w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
+  w.bytes = off + 1024;  // slack so that an unaligned base can be rounded up
+  return w;
+}
+
+static int run_gemm(bt_handle h, const __half* A, const void* W, __half* out, const void* bias, const __half* residual,
+                    const int* m_dev, int m_rows, int N, int K, int epi, int gelu_kind, cudaStream_t stream) {
+  const CUtensorMap* ta = h->tmap(A, m_rows, K, 64, 128);
+  const CUtensorMap* tb = h->tmap(W, K, N, 64, 64);
+  if (!ta || !tb) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
+  GemmLaunch g;
+  g.tm_a = *ta;
+  g.tm_b = *tb;
+  g.out = out;
+  g.bias = reinterpret_cast<const __half*>(bias);
+  g.residual = residual;
+  g.m_dev = m_dev;
+  g.m_rows = m_rows;
+  g.N = N;
+  g.K = K;
+  g.epilogue = epi;
+  g.gelu_kind = gelu_kind;
+  g.block_n = 0;
+  g.status = h->status;
+  g.num_sms = h->num_sms;
+  cudaError_t e = launch_gemm(g, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "gemm launch");
+  return BT_OK;
+}
+
+static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch_idx, int B, int max_len, int rows,
+                   cudaStream_t stream) {
+  const CUtensorMap* tq = h->tmap(qkv, rows, 3 * static_cast<uint64_t>(h->hidden), 64, 128);
+  if (!tq) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed for qkv");
+  MhaLaunch a;
+  a.tm_qkv = *tq;
+  a.ctx = ctx;
+  a.batch_idx = batch_idx;
+  a.batch = B;
+  a.max_len = max_len;
+  a.head_num = h->cfg.head_num;
+  a.hidden = h->hidden;
+  a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(h->cfg.size_per_head)) / h->cfg.tao;
+  a.status = h->status;
+  cudaError_t e = launch_mha(a, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "attention launch");
+  return BT_OK;
+}
+
+// One layer on packed rows.  `x_in` -> `x_out` (packed) unless restore_to != null,
+// in which case the last LayerNorm scatters into the padded tensor.
+static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, __half* restore_to,
+                     const Workspace& ws, const int* batch_idx, int B, int S_or_maxlen, int rows,
+                     cudaStream_t stream) {
+  if (layer < 0 || layer >= static_cast<int>(h->layers.size()) || !h->layers[layer].set)
+    return fail(h, BT_ERR_INVALID_ARG, "layer weights not set");
+  const bt_layer_weights& w = h->layers[layer].w;
+  const int H = h->hidden, F = h->ffn;
+  const int* m_dev = batch_idx + B;
+  const bool gb32 = h->cfg.gamma_beta_fp32 != 0;
+  int rc;
+  if ((rc = run_gemm(h, x_in, w.qkv_kernel, ws.qkv, w.qkv_bias, nullptr, m_dev, rows, 3 * H, H, BT_EPI_BIAS, 0,
+                     stream)) != BT_OK)
+    return rc;
+  if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream)) != BT_OK) return rc;
+  if ((rc = run_gemm(h, ws.ctx, w.attr_output_kernel, ws.pre, w.attr_output_bias, x_in, m_dev, rows, H, H,
+                     BT_EPI_BIAS_RESIDUAL, 0, stream)) != BT_OK)
+    return rc;
+  cudaError_t e = launch_layernorm(ws.pre, nullptr, nullptr, w.attr_output_layernorm_gamma,
+                                   w.attr_output_layernorm_beta, gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
+  if ((rc = run_gemm(h, ws.y, w.inter_kernel, ws.mid, w.inter_bias, nullptr, m_dev, rows, F, H, BT_EPI_BIAS_GELU,
+                     h->cfg.gelu_kind, stream)) != BT_OK)
+    return rc;
+  if ((rc = run_gemm(h, ws.mid, w.output_kernel, ws.pre, w.output_bias, ws.y, m_dev, rows, H, F,
+                     BT_EPI_BIAS_RESIDUAL, 0, stream)) != BT_OK)
+    return rc;
+  if (restore_to != nullptr)
+    e = launch_layernorm_restore(ws.pre, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32,
+                                 restore_to, batch_idx, B, S_or_maxlen, H, h->cfg.ln_eps, stream);
+  else
+    e = launch_layernorm(ws.pre, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, x_out,
+                         m_dev, rows, H, h->cfg.ln_eps, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
+  return BT_OK;
+}
+
+static int check_shape(bt_handle h, int B, int S) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  if (B <= 0 || S <= 0) return fail(h, BT_ERR_INVALID_ARG, "batch_size and seq_len must be positive");
+  if (S > 1024) return fail(h, BT_ERR_INVALID_ARG, "Input seq_len too long (max 1024)");
+  if (B > 65535) return fail(h, BT_ERR_INVALID_ARG, "batch_size too large (max 65535)");
+  return BT_OK;
+}
+
+static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* input, const void* mask, void* out,
+                        void* workspace, size_t workspace_bytes, int B, int S, void* stream_v) {
+  int rc = check_shape(h, B, S);
+  if (rc != BT_OK) return rc;
+  if (!input || !mask || !out || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
+  if (input == out) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
+  if (n_layers <= 0) return fail(h, BT_ERR_INVALID_ARG, "n_layers must be positive");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  const size_t rows = static_cast<size_t>(B) * S;
+  Workspace need = carve(nullptr, rows, h->hidden, h->ffn, B + 1, rows);
+  if (workspace_bytes < need.bytes) return fail(h, BT_ERR_WORKSPACE, "workspace smaller than bt_workspace_bytes()");
+  void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
+  Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
+
+  cudaError_t e = launch_build_offsets(reinterpret_cast<const __half*>(mask), B, S, ws.batch_idx, ws.word_idx, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "offsets launch");
+  e = launch_pack_rows(reinterpret_cast<const __half*>(input), ws.xa, ws.batch_idx, B, S, h->hidden, stream);
+  if (e != cudaSuccess) return fail_cuda(h, e, "pack launch");
+  __half* cur = ws.xa;
+  __half* nxt = ws.xb;
+  for (int l = 0; l < n_layers; ++l) {
+    const bool last = (l == n_layers - 1);
+    rc = run_layer(h, first_layer + l, cur, nxt, last ? reinterpret_cast<__half*>(out) : nullptr, ws, ws.batch_idx, B,
+                   S, static_cast<int>(rows), stream);
+    if (rc != BT_OK) return rc;
+    __half* t = cur;
+    cur = nxt;
+    nxt = t;
+  }
+  return BT_OK;
+}
+
+}  // namespace bt
+
+using namespace bt;
+
+extern "C" {
+
+const char* bt_version(void) { return "bt_b200 0.1 (sm_100a, tcgen05/TMEM/TMA)"; }
+
+int bt_create(const bt_config* cfg, bt_handle* out) {
+  if (!cfg || !out) return BT_ERR_INVALID_ARG;
+  *out = nullptr;
+  if (cfg->size_per_head != 64 || cfg->head_num <= 0 || cfg->head_num > 64) return BT_ERR_UNSUPPORTED;
+  if (cfg->max_seq_len <= 0 || cfg->max_seq_len > 1024 || cfg->max_batch_size <= 0) return BT_ERR_INVALID_ARG;
+  if (cfg->intermediate_mult <= 0 || !(cfg->tao > 0.f) || !(cfg->ln_eps >= 0.f)) return BT_ERR_INVALID_ARG;
+  if (cfg->gelu_kind != BT_GELU_ERF && cfg->gelu_kind != BT_GELU_TANH) return BT_ERR_INVALID_ARG;
+  int dev = cfg->device;
+  if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) return BT_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return BT_ERR_CUDA;
+  if (prop.major != 10) return BT_ERR_UNSUPPORTED;  // tcgen05 / tensor memory need sm_100
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (cur != dev && cudaSetDevice(dev) != cudaSuccess) return BT_ERR_CUDA;
+  int* status = device_status_word();
+  if (cur != dev) cudaSetDevice(cur);
+  if (status == nullptr) return BT_ERR_CUDA;
+  bt_encoder_s* h = new (std::nothrow) bt_encoder_s();
+  if (!h) return BT_ERR_INVALID_ARG;
+  h->cfg = *cfg;
+  h->hidden = cfg->head_num * cfg->size_per_head;
+  h->ffn = h->hidden * cfg->intermediate_mult;
+  h->device = dev;
+  h->num_sms = prop.multiProcessorCount;
+  h->status = status;
+  h->tmaps.reserve(256);  // pointers into the cache stay valid while it fills
+  *out = h;
+  return BT_OK;
+}
+
+int bt_destroy(bt_handle h) {
+  delete h;
+  return BT_OK;
+}
+
+int bt_set_layer_weights(bt_handle h, int layer, const bt_layer_weights* w) {
+  if (!h || !w) return BT_ERR_INVALID_ARG;
+  if (layer < 0 || layer >= 4096) return fail(h, BT_ERR_INVALID_ARG, "layer index out of range");
+  const void* const* p = reinterpret_cast<const void* const*>(w);
+  for (int i = 0; i < 12; ++i) {
+    if (p[i] == nullptr) return fail(h, BT_ERR_INVALID_ARG, "null weight pointer");
+    if ((reinterpret_cast<uintptr_t>(p[i]) & 15u) != 0) return fail(h, BT_ERR_INVALID_ARG, "weight pointers must be 16-byte aligned");
+  }
+  if (static_cast<int>(h->layers.size()) <= layer) h->layers.resize(layer + 1);
+  h->layers[layer].w = *w;
+  h->layers[layer].set = true;
+  return BT_OK;
+}
+
+int bt_workspace_bytes(bt_handle h, int batch_size, int seq_len, size_t* bytes) {
+  if (!bytes) return BT_ERR_INVALID_ARG;
+  int rc = check_shape(h, batch_size, seq_len);
+  if (rc != BT_OK) return rc;
+  const size_t rows = static_cast<size_t>(batch_size) * seq_len;
+  *bytes = carve(nullptr, rows, h->hidden, h->ffn, batch_size + 1, rows).bytes;
+  return BT_OK;
+}
+
+int bt_workspace_bytes_packed(bt_handle h, int batch_size, int total_tokens, size_t* bytes) {
+  if (!h || !bytes) return BT_ERR_INVALID_ARG;
+  if (batch_size <= 0 || total_tokens <= 0) return fail(h, BT_ERR_INVALID_ARG, "batch_size and total_tokens must be positive");
+  *bytes = carve(nullptr, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0).bytes;
+  return BT_OK;
+}
+
+const char* bt_last_error(bt_handle h) { return h ? h->err.c_str() : "null handle"; }
+
+int bt_device_status(bt_handle h, void* stream, int* status) {
+  if (!h || !status) return BT_ERR_INVALID_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, h->status, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(h, e, "bt_device_status");
+  if (v != 0) {
+    e = cudaMemsetAsync(h->status, 0, sizeof(int), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail_cuda(h, e, "bt_device_status reset");
+  }
+  *status = v;
+  return BT_OK;
+}
+
+int bt_layer_forward_padded(bt_handle h, int layer, const void* input, const void* attr_mask, void* out,
+                            void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  return stack_padded(h, layer, 1, input, attr_mask, out, workspace, workspace_bytes, batch_size, seq_len, stream);
+}
+
+int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const void* attr_mask, void* out,
+                            void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  return stack_padded(h, 0, n_layers, input, attr_mask, out, workspace, workspace_bytes, batch_size, seq_len, stream);
+}
+
+int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, const int* cu_seqlens, int batch_size,
+                            int max_len, int total_tokens, void* out_packed, void* workspace, size_t workspace_bytes,
+                            void* stream_v) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  if (!x_packed || !cu_seqlens || !out_packed || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
+  if (batch_size <= 0 || batch_size > 65535 || total_tokens <= 0 || max_len <= 0 || n_layers <= 0)
+    return fail(h, BT_ERR_INVALID_ARG, "bad batch_size / total_tokens / max_len / n_layers");
+  if (x_packed == out_packed) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  Workspace need = carve(nullptr, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0);
+  if (workspace_bytes < need.bytes) return fail(h, BT_ERR_WORKSPACE, "workspace smaller than bt_workspace_bytes_packed()");
+  void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
+  Workspace ws = carve(base, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0);
+  const __half* cur = reinterpret_cast<const __half*>(x_packed);
+  for (int l = 0; l < n_layers; ++l) {
+    const bool last = (l == n_layers - 1);
+    __half* dst = last ? reinterpret_cast<__half*>(out_packed) : ((l & 1) ? ws.xb : ws.xa);
+    int rc = run_layer(h, l, cur, dst, nullptr, ws, cu_seqlens, batch_size, max_len, total_tokens, stream);
+    if (rc != BT_OK) return rc;
+    cur = dst;
+  }
+  return BT_OK;
+}
+
+int bt_build_offsets(const void* attr_mask, int batch_size, int seq_len, int* batch_idx, int* word_idx, void* stream) {
+  if (!attr_mask || !batch_idx || !word_idx || batch_size <= 0 || seq_len <= 0) return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_build_offsets(reinterpret_cast<const __half*>(attr_mask), batch_size, seq_len, batch_idx,
+                                       word_idx, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_pack_rows(const void* padded, void* packed, const int* batch_idx, const int* word_idx, int batch_size,
+                 int seq_len, int hidden, void* stream) {
+  (void)word_idx;  // right padding makes each sequence one contiguous run; batch_idx is enough
+  if (!padded || !packed || !batch_idx || batch_size <= 0 || batch_size > 65535 || seq_len <= 0 || hidden <= 0 ||
+      hidden % 8 != 0)
+    return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_pack_rows(reinterpret_cast<const __half*>(padded), reinterpret_cast<__half*>(packed),
+                                   batch_idx, batch_size, seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_restore_rows(const void* packed, void* padded, const int* batch_idx, int batch_size, int seq_len, int hidden,
+                    void* stream) {
+  if (!packed || !padded || !batch_idx || batch_size <= 0 || batch_size > 65535 || seq_len <= 0 || hidden <= 0 ||
+      hidden % 8 != 0)
+    return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_restore_rows(reinterpret_cast<const __half*>(packed), reinterpret_cast<__half*>(padded),
+                                      batch_idx, batch_size, seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bias, const void* residual,
+            const int* m_dev, int m_rows, int N, int K, int epilogue, int gelu_kind, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  if (!A || !W || !out) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
+  if (m_rows <= 0 || N <= 0 || K <= 0 || N % 64 != 0 || K % 64 != 0)
+    return fail(h, BT_ERR_INVALID_ARG, "bt_gemm needs m_rows > 0, N % 64 == 0, K % 64 == 0");
+  if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
+  if (epilogue != BT_EPI_NONE && !bias) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs bias");
+  if (epilogue == BT_EPI_BIAS_RESIDUAL && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
+  return run_gemm(h, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
+                  reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, epilogue, gelu_kind,
+                  reinterpret_cast<cudaStream_t>(stream));
+}
+
+int bt_attention(bt_handle h, const void* qkv, void* ctx, const int* batch_idx, int batch_size, int max_len,
+                 int rows_allocated, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  if (!qkv || !ctx || !batch_idx || batch_size <= 0 || batch_size > 65535 || max_len <= 0 || rows_allocated <= 0)
+    return fail(h, BT_ERR_INVALID_ARG, "bad argument to bt_attention");
+  return run_mha(h, reinterpret_cast<const __half*>(qkv), reinterpret_cast<__half*>(ctx), batch_idx, batch_size,
+                 max_len, rows_allocated, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int bt_add_bias_residual_layernorm(const void* x, const void* bias, const void* residual, const void* gamma,
+                                   const void* beta, int gamma_beta_fp32, void* out, const int* m_dev, int m_rows,
+                                   int hidden, float eps, void* stream) {
+  if (!x || !gamma || !beta || !out || m_rows <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 1024)
+    return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_layernorm(reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(bias),
+                                   reinterpret_cast<const __half*>(residual), gamma, beta, gamma_beta_fp32 != 0,
+                                   reinterpret_cast<__half*>(out), m_dev, m_rows, hidden, eps,
+                                   reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_add_bias_residual_layernorm_restore(const void* x, const void* bias, const void* residual, const void* gamma,
+                                           const void* beta, int gamma_beta_fp32, void* out_padded,
+                                           const int* batch_idx, int batch_size, int seq_len, int hidden, float eps,
+                                           void* stream) {
+  if (!x || !gamma || !beta || !out_padded || !batch_idx || batch_size <= 0 || seq_len <= 0 || hidden <= 0 ||
+      hidden % 8 != 0 || hidden > 1024)
+    return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_layernorm_restore(
+      reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(bias),
+      reinterpret_cast<const __half*>(residual), gamma, beta, gamma_beta_fp32 != 0,
+      reinterpret_cast<__half*>(out_padded), batch_idx, batch_size, seq_len, hidden, eps,
+      reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_add_bias_gelu(void* x, const void* bias, const int* m_dev, int m_rows, int n, int gelu_kind, void* stream) {
+  if (!x || !bias || m_rows <= 0 || n <= 0 || n % 8 != 0) return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_add_bias_gelu(reinterpret_cast<__half*>(x), reinterpret_cast<const __half*>(bias), m_dev,
+                                       m_rows, n, gelu_kind, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_masked_softmax(void* logits, const void* attr_mask, int batch_size, int head_num, int seq_len, float scale,
+                      void* stream) {
+  if (!logits || !attr_mask || batch_size <= 0 || head_num <= 0 || seq_len <= 0 || seq_len > 1024)
+    return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_masked_softmax(reinterpret_cast<__half*>(logits), reinterpret_cast<const __half*>(attr_mask),
+                                        batch_size, head_num, seq_len, scale, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Host-side launchers of the sm_100a kernels (internal to the library; the
+// public surface is the C ABI in include/bt_b200.h).  Every launcher enqueues on
+// `stream` and returns the cudaError_t of the launch; none synchronises.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bt {
+
+// ---- tensor maps -----------------------------------------------------------
+// Encodes a 2-D fp16 row-major tensor [rows, cols] (row stride `ld` elements)
+// with a {box_cols, box_rows} box and 128-byte swizzle.  Returns false when the
+// driver entry point is unavailable or the encode fails.
+bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                  uint32_t box_cols, uint32_t box_rows);
+
+// ---- offsets / pack / restore ----------------------------------------------
+cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_idx, int* word_idx,
+                                 cudaStream_t stream);
+cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S,
+                             int hidden, cudaStream_t stream);
+cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int* batch_idx, int B, int S,
+                                int hidden, cudaStream_t stream);
+
+// ---- GEMM ---------------------------------------------------------------------
+struct GemmLaunch {
+  CUtensorMap tm_a;  // A [m_rows, K], box {64, 128}
+  CUtensorMap tm_b;  // W [K, N],     box {64, 64}
+  __half* out;
+  const __half* bias;
+  const __half* residual;
+  const int* m_dev;  // device int with the number of valid rows, or null
+  int m_rows;        // rows allocated in A / out / residual (upper bound of M)
+  int N;
+  int K;
+  int epilogue;      // BT_EPI_*
+  int gelu_kind;     // BT_GELU_*
+  int block_n;       // 64, 128 or 256; 0 = choose from the shape
+  int* status;       // device status word
+  int num_sms;
+};
+int gemm_pick_block_n(int m_rows, int N, int num_sms);
+cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+
+// ---- fused multi-head attention -----------------------------------------------
+struct MhaLaunch {
+  CUtensorMap tm_qkv;  // qkv [rows, 3H], box {64, 128}
+  __half* ctx;         // [rows, H]
+  const int* batch_idx;
+  int batch;
+  int max_len;         // upper bound of every sequence length
+  int head_num;
+  int hidden;          // H = head_num * 64
+  float scale_log2e;   // log2(e) / sqrt(64) / tao
+  int* status;
+};
+cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
+
+// ---- element-wise / normalisation -------------------------------------------
+cudaError_t launch_layernorm(const __half* x, const __half* bias, const __half* residual, const void* gamma,
+                             const void* beta, bool gb_fp32, __half* out, const int* m_dev, int m_rows,
+                             int hidden, float eps, cudaStream_t stream);
+cudaError_t launch_layernorm_restore(const __half* x, const __half* bias, const __half* residual,
+                                     const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
+                                     const int* batch_idx, int B, int S, int hidden, float eps,
+                                     cudaStream_t stream);
+cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev, int m_rows, int n,
+                                 int gelu_kind, cudaStream_t stream);
+cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int nh, int S, float scale,
+                                  cudaStream_t stream);
+
+// Address of the per-device status word (a __device__ variable of the library).
+int* device_status_word();
+
+}  // namespace bt

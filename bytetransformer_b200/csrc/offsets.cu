@@ -1,0 +1,165 @@
+// Padding removal bookkeeping: mask -> lengths -> prefix-sum offsets, and the
+// pack (padded -> packed) / restore (packed -> padded, zero fill) row copies.
+//
+// Integer results are bit-exact with the reference's
+// `parallel_prefix` (bytetransformer/include/remove_padding.h:36-86):
+//   len_b        = #{ j : mask[b,0,j] >= 0.5 }          (only mask row 0 is read)
+//   batch_idx[0] = 0, batch_idx[b+1] = batch_idx[b] + len_b   (batch_idx[B] = T)
+//   word_idx[batch_idx[b] + i] = b*S + i  for i < len_b
+// Unlike the reference there is no device-to-host copy of T: the consumers read
+// batch_idx[B] on the device.
+//
+// Both are HBM-bound.  Algorithmic bytes: offsets 2*B*S (mask row 0) + 4*(B+1) +
+// 4*T; pack 4*T*H (read + write fp16); restore 2*T*H + 2*B*S*H.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bt {
+
+namespace {
+
+constexpr int kOffThreads = 1024;
+
+__global__ void __launch_bounds__(kOffThreads, 1)
+build_offsets_kernel(const __half* __restrict__ mask, int B, int S, int* __restrict__ batch_idx,
+                     int* __restrict__ word_idx) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n_warps = kOffThreads / 32;
+  const __half half_thr = __float2half(0.5f);
+
+  // 1. lengths: one warp per sequence; len goes to batch_idx[b+1] for now
+  const bool vec_ok = (S % 8) == 0;
+  for (int b = warp; b < B; b += n_warps) {
+    const __half* row = mask + static_cast<size_t>(b) * S * S;
+    int cnt = 0;
+    if (vec_ok) {
+      const uint4* row4 = reinterpret_cast<const uint4*>(row);
+      for (int v = lane; v < S / 8; v += 32) {
+        const uint4 q = __ldg(row4 + v);
+        const __half* hp = reinterpret_cast<const __half*>(&q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cnt += __hge(hp[i], half_thr) ? 1 : 0;
+      }
+    } else {
+      for (int j = lane; j < S; j += 32) cnt += __hge(row[j], half_thr) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if (lane == 0) batch_idx[b + 1] = cnt;
+  }
+  if (tid == 0) {
+    batch_idx[0] = 0;
+    carry_s = 0;
+  }
+  __syncthreads();
+
+  // 2. inclusive scan of batch_idx[1..B] in chunks of 1024 (any B)
+  for (int base = 0; base < B; base += kOffThreads) {
+    const int i = base + tid;
+    const int len = i < B ? batch_idx[i + 1] : 0;
+    int x = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    const int incl = x + (warp > 0 ? warp_sums[warp - 1] : 0) + carry;
+    if (i < B) batch_idx[i + 1] = incl;
+    __syncthreads();
+    if (tid == kOffThreads - 1) carry_s = incl;
+    __syncthreads();
+  }
+
+  // 3. packed row -> padded row map
+  for (int b = warp; b < B; b += n_warps) {
+    const int off = batch_idx[b];
+    const int len = batch_idx[b + 1] - off;
+    for (int i = lane; i < len; i += 32) word_idx[off + i] = b * S + i;
+  }
+}
+
+// With right padding the valid rows of sequence b are one contiguous run of
+// len_b*H halves in both layouts, so pack / restore are B segment copies done
+// with 16-byte accesses (the reference gathers row by row through word_idx,
+// remove_padding.h:104-121).
+__global__ void __launch_bounds__(256)
+pack_rows_kernel(const uint4* __restrict__ padded, uint4* __restrict__ packed, const int* __restrict__ batch_idx,
+                 int S, int vec_per_row) {
+  const int b = blockIdx.y;
+  const int off = __ldg(batch_idx + b);
+  const int len = __ldg(batch_idx + b + 1) - off;
+  const long long n = static_cast<long long>(len) * vec_per_row;
+  const uint4* src = padded + static_cast<size_t>(b) * S * vec_per_row;
+  uint4* dst = packed + static_cast<size_t>(off) * vec_per_row;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < n;
+       v += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[v] = __ldg(src + v);
+}
+
+__global__ void __launch_bounds__(256)
+restore_rows_kernel(const uint4* __restrict__ packed, uint4* __restrict__ padded, const int* __restrict__ batch_idx,
+                    int S, int vec_per_row) {
+  const int b = blockIdx.y;
+  const int off = __ldg(batch_idx + b);
+  const int len = __ldg(batch_idx + b + 1) - off;
+  const long long n = static_cast<long long>(len) * vec_per_row;
+  const long long total = static_cast<long long>(S) * vec_per_row;
+  const uint4* src = packed + static_cast<size_t>(off) * vec_per_row;
+  uint4* dst = padded + static_cast<size_t>(b) * S * vec_per_row;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
+       v += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[v] = v < n ? __ldg(src + v) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+inline int copy_grid_x(int S, int vec_per_row) {
+  const long long total = static_cast<long long>(S) * vec_per_row;
+  long long g = (total + 256 * 4 - 1) / (256 * 4);  // ~4 vectors (64 B) per thread
+  if (g < 1) g = 1;
+  if (g > 1024) g = 1024;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_idx, int* word_idx,
+                                 cudaStream_t stream) {
+  build_offsets_kernel<<<1, kOffThreads, 0, stream>>>(mask, B, S, batch_idx, word_idx);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S, int hidden,
+                             cudaStream_t stream) {
+  const int vec = hidden / 8;
+  dim3 grid(copy_grid_x(S, vec), B);
+  pack_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(padded),
+                                             reinterpret_cast<uint4*>(packed), batch_idx, S, vec);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int* batch_idx, int B, int S,
+                                int hidden, cudaStream_t stream) {
+  const int vec = hidden / 8;
+  dim3 grid(copy_grid_x(S, vec), B);
+  restore_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(packed),
+                                                reinterpret_cast<uint4*>(padded), batch_idx, S, vec);
+  return cudaGetLastError();
+}
+
+}  // namespace bt

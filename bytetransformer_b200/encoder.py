@@ -1,0 +1,313 @@
+"""Python host side over the C ABI: torch tensors supply device memory and
+streams, every computation goes through libbt_b200.so.
+
+`bert_transformer(...)` mirrors the reference's functional operator
+`torch.ops.ByteTransformer.BertTransformer` (bytetransformer/th_op/ths_op_f.cc:28-95):
+same argument order, names, defaults and error behaviour (RuntimeError on bad
+input).  `Encoder` is the reusable object form (the reference's C++
+`BertTransformer<HALF>` used through bytetransformer/th_op/bert_transformer_ext.h:40-118)
+extended to a stack of layers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _abi
+
+WEIGHT_NAMES = (
+    "qkv_kernel", "qkv_bias", "attr_output_kernel", "attr_output_bias",
+    "attr_output_layernorm_gamma", "attr_output_layernorm_beta", "inter_kernel", "inter_bias",
+    "output_kernel", "output_bias", "output_layernorm_gamma", "output_layernorm_beta")
+_LOOSE = {4, 5, 10, 11}  # LayerNorm gamma/beta: dtype not checked by the reference (CHECK_INPUT_LOOSE)
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check(t: torch.Tensor, name: str, dtype=None):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"Inconsistency of Tensor type: {name}")
+
+
+class Encoder:
+    """A stack of BERT encoder layers bound to one CUDA device."""
+
+    def __init__(self, head_num: int, head_size: int, layers: Sequence[Sequence[torch.Tensor]], *,
+                 max_batch_size: int = 65535, max_seq_len: int = 1024, ln_eps: float = 1e-6,
+                 gelu: str = "erf", tao: float = 1.0):
+        if not layers:
+            raise RuntimeError("at least one layer of weights is required")
+        self._lib = _abi.load()
+        self.head_num, self.head_size = int(head_num), int(head_size)
+        self.hidden = self.head_num * self.head_size
+        first = layers[0]
+        if len(first) != 12:
+            raise RuntimeError("each layer needs 12 weight tensors")
+        self.device = first[0].device
+        if first[0].dtype != torch.float16:
+            raise RuntimeError("only fp16 weights are supported (the fp32 template of the reference "
+                               "is not built for sm_100a)")
+        gb_fp32 = first[10].dtype == torch.float32  # bert_transformer_ext.h:60-63
+        self._layers = []  # keeps the tensors alive: the library stores raw pointers only
+        cfg = _abi.bt_config(self.head_num, self.head_size, int(max_batch_size), int(max_seq_len), 4,
+                             float(ln_eps), _abi.BT_GELU_ERF if gelu == "erf" else _abi.BT_GELU_TANH,
+                             float(tao), int(gb_fp32), self.device.index if self.device.index is not None else -1)
+        if gelu not in ("erf", "tanh"):
+            raise RuntimeError("gelu must be 'erf' or 'tanh'")
+        h = C.c_void_p()
+        rc = self._lib.bt_create(C.byref(cfg), C.byref(h))
+        if rc != _abi.BT_OK:
+            raise _abi.BtError(rc, "bt_create",
+                               "head_size must be 64 and the device must be compute capability 10.x")
+        self._h = h
+        H = self.hidden
+        shapes = [(H, 3 * H), (3 * H,), (H, H), (H,), (H,), (H,), (H, 4 * H), (4 * H,), (4 * H, H), (H,), (H,), (H,)]
+        for li, w in enumerate(layers):
+            if len(w) != 12:
+                raise RuntimeError("each layer needs 12 weight tensors")
+            for i, t in enumerate(w):
+                _check(t, WEIGHT_NAMES[i], None if i in _LOOSE else torch.float16)
+                if tuple(t.shape) != shapes[i]:
+                    raise RuntimeError(f"{WEIGHT_NAMES[i]} has shape {tuple(t.shape)}, expected {shapes[i]}")
+                if i in _LOOSE and t.dtype != (torch.float32 if gb_fp32 else torch.float16):
+                    raise RuntimeError("LayerNorm gamma/beta must all be fp16 or all be fp32")
+            lw = _abi.bt_layer_weights(*[t.data_ptr() for t in w])
+            self._call("bt_set_layer_weights", self._h, li, C.byref(lw))
+            self._layers.append(list(w))
+        self.n_layers = len(self._layers)
+        self._ws: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ helpers
+    def _call(self, name, *args):
+        rc = getattr(self._lib, name)(*args)
+        if rc != _abi.BT_OK:
+            raise _abi.BtError(rc, name, self._lib.bt_last_error(self._h).decode())
+        return rc
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.bt_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _workspace(self, nbytes: int) -> torch.Tensor:
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = torch.empty(nbytes, dtype=torch.int8, device=self.device)
+        return self._ws
+
+    def device_status(self) -> int:
+        st = C.c_int(0)
+        self._call("bt_device_status", self._h, _stream_ptr(self.device), C.byref(st))
+        return st.value
+
+    # ----------------------------------------------------------------- forwards
+    def _check_io(self, x, attr_mask):
+        _check(x, "input", torch.float16)
+        _check(attr_mask, "attr_mask", torch.float16)
+        if x.dim() != 3 or x.shape[2] != self.hidden:
+            raise RuntimeError("input must be [batch, seq_len, head_num*head_size]")
+        B, S = int(x.shape[0]), int(x.shape[1])
+        if S > 1024:
+            raise RuntimeError("Input seq_len too long")  # th_op/util.h:40
+        if tuple(attr_mask.shape) != (B, S, S):
+            raise RuntimeError("attr_mask must be [batch, seq_len, seq_len]")
+        return B, S
+
+    def forward_layer(self, layer: int, x: torch.Tensor, attr_mask: torch.Tensor) -> torch.Tensor:
+        """One layer, padded in / padded out, padding rows zero (the reference op)."""
+        B, S = self._check_io(x, attr_mask)
+        with torch.cuda.device(self.device):
+            out = torch.empty_like(x)
+            n = C.c_size_t()
+            self._call("bt_workspace_bytes", self._h, B, S, C.byref(n))
+            ws = self._workspace(n.value)
+            self._call("bt_layer_forward_padded", self._h, int(layer), x.data_ptr(), attr_mask.data_ptr(),
+                       out.data_ptr(), ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
+        return out
+
+    def forward(self, x: torch.Tensor, attr_mask: torch.Tensor, n_layers: Optional[int] = None) -> torch.Tensor:
+        """All layers in one call: pack once, run the stack packed, scatter once."""
+        B, S = self._check_io(x, attr_mask)
+        nl = self.n_layers if n_layers is None else int(n_layers)
+        with torch.cuda.device(self.device):
+            out = torch.empty_like(x)
+            n = C.c_size_t()
+            self._call("bt_workspace_bytes", self._h, B, S, C.byref(n))
+            ws = self._workspace(n.value)
+            self._call("bt_stack_forward_padded", self._h, nl, x.data_ptr(), attr_mask.data_ptr(), out.data_ptr(),
+                       ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
+        return out
+
+    def packed_workspace_bytes(self, batch: int, total_tokens: int) -> int:
+        n = C.c_size_t()
+        self._call("bt_workspace_bytes_packed", self._h, int(batch), int(total_tokens), C.byref(n))
+        return n.value
+
+    def forward_packed(self, x_packed: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int,
+                       out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                       n_layers: Optional[int] = None) -> torch.Tensor:
+        """Packed in / packed out: x_packed [T,H] fp16, cu_seqlens int32 [B+1] on the device."""
+        _check(x_packed, "x_packed", torch.float16)
+        _check(cu_seqlens, "cu_seqlens", torch.int32)
+        if x_packed.dim() != 2 or x_packed.shape[1] != self.hidden:
+            raise RuntimeError("x_packed must be [total_tokens, head_num*head_size]")
+        T = int(x_packed.shape[0])
+        B = int(cu_seqlens.numel()) - 1
+        nl = self.n_layers if n_layers is None else int(n_layers)
+        with torch.cuda.device(self.device):
+            if out is None:
+                out = torch.empty_like(x_packed)
+            ws = workspace if workspace is not None else self._workspace(self.packed_workspace_bytes(B, T))
+            self._call("bt_stack_forward_packed", self._h, nl, x_packed.data_ptr(), cu_seqlens.data_ptr(), B,
+                       int(max_len), T, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream_ptr(self.device))
+        return out
+
+    # -------------------------------------------------------- single steps (tests, tools)
+    def gemm(self, a: torch.Tensor, w: torch.Tensor, bias=None, residual=None, *, epilogue=_abi.BT_EPI_NONE,
+             gelu=_abi.BT_GELU_ERF, m_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _check(a, "a", torch.float16)
+        _check(w, "w", torch.float16)
+        M, K = a.shape
+        N = w.shape[1]
+        out = torch.zeros(M, N, dtype=torch.float16, device=a.device)
+        self._call("bt_gemm", self._h, a.data_ptr(), w.data_ptr(), out.data_ptr(),
+                   bias.data_ptr() if bias is not None else None,
+                   residual.data_ptr() if residual is not None else None,
+                   m_dev.data_ptr() if m_dev is not None else None, int(M), int(N), int(K), int(epilogue), int(gelu),
+                   _stream_ptr(a.device))
+        return out
+
+    def attention(self, qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int) -> torch.Tensor:
+        _check(qkv, "qkv", torch.float16)
+        _check(cu_seqlens, "cu_seqlens", torch.int32)
+        rows = int(qkv.shape[0])
+        ctx = torch.zeros(rows, self.hidden, dtype=torch.float16, device=qkv.device)
+        self._call("bt_attention", self._h, qkv.data_ptr(), ctx.data_ptr(), cu_seqlens.data_ptr(),
+                   int(cu_seqlens.numel()) - 1, int(max_len), rows, _stream_ptr(qkv.device))
+        return ctx
+
+
+# ---------------------------------------------------------------------------------------------
+# free functions over the stateless entry points
+def build_offsets(attr_mask: torch.Tensor):
+    """(batch_idx int32[B+1], word_idx int32[B*S]) on the device; only the first
+    batch_idx[B] entries of word_idx are defined."""
+    lib = _abi.load()
+    _check(attr_mask, "attr_mask", torch.float16)
+    B, S = int(attr_mask.shape[0]), int(attr_mask.shape[1])
+    batch_idx = torch.empty(B + 1, dtype=torch.int32, device=attr_mask.device)
+    word_idx = torch.full((B * S,), -1, dtype=torch.int32, device=attr_mask.device)
+    rc = lib.bt_build_offsets(attr_mask.data_ptr(), B, S, batch_idx.data_ptr(), word_idx.data_ptr(),
+                              _stream_ptr(attr_mask.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_build_offsets")
+    return batch_idx, word_idx
+
+
+def pack_rows(x_padded: torch.Tensor, batch_idx: torch.Tensor, out: Optional[torch.Tensor] = None):
+    lib = _abi.load()
+    B, S, H = x_padded.shape
+    if out is None:
+        out = torch.zeros(B * S, H, dtype=torch.float16, device=x_padded.device)
+    rc = lib.bt_pack_rows(x_padded.data_ptr(), out.data_ptr(), batch_idx.data_ptr(), None, B, S, H,
+                          _stream_ptr(x_padded.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_pack_rows")
+    return out
+
+
+def restore_rows(x_packed: torch.Tensor, batch_idx: torch.Tensor, B: int, S: int):
+    lib = _abi.load()
+    H = x_packed.shape[1]
+    out = torch.full((B, S, H), float("nan"), dtype=torch.float16, device=x_packed.device)
+    rc = lib.bt_restore_rows(x_packed.data_ptr(), out.data_ptr(), batch_idx.data_ptr(), B, S, H,
+                             _stream_ptr(x_packed.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_restore_rows")
+    return out
+
+
+def add_bias_residual_layernorm(x, bias, residual, gamma, beta, eps=1e-6, m_dev=None):
+    lib = _abi.load()
+    M, H = x.shape
+    out = torch.zeros_like(x)
+    rc = lib.bt_add_bias_residual_layernorm(
+        x.data_ptr(), bias.data_ptr() if bias is not None else None,
+        residual.data_ptr() if residual is not None else None, gamma.data_ptr(), beta.data_ptr(),
+        int(gamma.dtype == torch.float32), out.data_ptr(), m_dev.data_ptr() if m_dev is not None else None,
+        M, H, float(eps), _stream_ptr(x.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_add_bias_residual_layernorm")
+    return out
+
+
+def add_bias_residual_layernorm_restore(x, bias, residual, gamma, beta, batch_idx, B, S, eps=1e-6):
+    lib = _abi.load()
+    H = x.shape[1]
+    out = torch.full((B, S, H), float("nan"), dtype=torch.float16, device=x.device)
+    rc = lib.bt_add_bias_residual_layernorm_restore(
+        x.data_ptr(), bias.data_ptr() if bias is not None else None,
+        residual.data_ptr() if residual is not None else None, gamma.data_ptr(), beta.data_ptr(),
+        int(gamma.dtype == torch.float32), out.data_ptr(), batch_idx.data_ptr(), B, S, H, float(eps),
+        _stream_ptr(x.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_add_bias_residual_layernorm_restore")
+    return out
+
+
+def add_bias_gelu_(x, bias, gelu="erf"):
+    lib = _abi.load()
+    M, N = x.shape
+    rc = lib.bt_add_bias_gelu(x.data_ptr(), bias.data_ptr(), None, M, N,
+                              _abi.BT_GELU_ERF if gelu == "erf" else _abi.BT_GELU_TANH, _stream_ptr(x.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_add_bias_gelu")
+    return x
+
+
+def masked_softmax_(logits, attr_mask, scale=1.0):
+    """logits [nh,B,S,S] (the reference's layout), in place."""
+    lib = _abi.load()
+    nh, B, S, _ = logits.shape
+    rc = lib.bt_masked_softmax(logits.data_ptr(), attr_mask.data_ptr(), B, nh, S, float(scale),
+                               _stream_ptr(logits.device))
+    if rc != _abi.BT_OK:
+        raise _abi.BtError(rc, "bt_masked_softmax")
+    return logits
+
+
+def bert_transformer(head_num: int, head_size: int,
+                     qkv_kernel, qkv_bias, attr_output_kernel, attr_output_bias,
+                     attr_output_layernorm_gamma, attr_output_layernorm_beta,
+                     inter_kernel, inter_bias, output_kernel, output_bias,
+                     output_layernorm_gamma, output_layernorm_beta,
+                     input, attr_mask, is_remove_padding: bool = True,
+                     use_fused_attention: bool = True, *, ln_eps: float = 1e-6, gelu: str = "erf"):
+    """Drop-in for `torch.ops.ByteTransformer.BertTransformer` (ths_op_f.cc:85-95).
+
+    `is_remove_padding` and `use_fused_attention` are accepted for signature
+    compatibility; this library always runs padding-free with fused attention
+    (both settings give the same result on valid rows, padding rows are zero).
+    The encoder object is built per call, as the reference does
+    (bert_transformer_ext.h:86-110)."""
+    w = [qkv_kernel, qkv_bias, attr_output_kernel, attr_output_bias, attr_output_layernorm_gamma,
+         attr_output_layernorm_beta, inter_kernel, inter_bias, output_kernel, output_bias,
+         output_layernorm_gamma, output_layernorm_beta]
+    enc = Encoder(head_num, head_size, [w], ln_eps=ln_eps, gelu=gelu)
+    try:
+        return enc.forward_layer(0, input, attr_mask)
+    finally:
+        enc.close()

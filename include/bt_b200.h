@@ -1,0 +1,205 @@
+/*
+ * bt_b200 — C ABI of the B200 (sm_100a) padding-free BERT encoder library.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * int status (0 = BT_OK) and never throws, exits or synchronises the host.  All
+ * data pointers are DEVICE pointers owned by the caller; `stream` is a
+ * `cudaStream_t` passed as `void*`.  The library allocates no device memory:
+ * scratch is the caller's `workspace` (size from bt_workspace_bytes()).
+ *
+ * Each declaration names the reference interface it stands in for
+ * (paths relative to the ByteTransformer project root).
+ *
+ * Data layout conventions (identical to the reference):
+ *   - fp16 everywhere (`__half`), GEMM weights row-major [in_features, out_features]
+ *   - qkv_kernel [H,3H] with column thirds Q|K|V, head h = columns h*64..h*64+63 of a third
+ *   - padded activations [B,S,H]; packed activations [T,H], T = number of valid tokens
+ *   - attention mask [B,S,S] fp16, 1 = attend, 0 = masked, right padded
+ *   - batch_idx int32[B+1] (exclusive prefix sum of lengths, batch_idx[B] = T),
+ *     word_idx int32[T] (packed row -> padded row b*S+i)
+ */
+#ifndef BT_B200_H_
+#define BT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define BT_OK 0
+#define BT_ERR_INVALID_ARG 1   /* null pointer, bad shape, unsupported size       */
+#define BT_ERR_WORKSPACE 2     /* workspace too small                             */
+#define BT_ERR_CUDA 3          /* a CUDA runtime / driver call failed             */
+#define BT_ERR_UNSUPPORTED 4   /* e.g. head size != 64, device is not sm_100      */
+#define BT_ERR_DEVICE_STATUS 5 /* a kernel reported a bounded-wait / bounds error */
+
+#define BT_GELU_ERF 0  /* exact GELU: what the reference's PyTorch encoder computes */
+#define BT_GELU_TANH 1 /* tanh approximation: what the reference's CUDA kernels compute */
+
+/* epilogue selector of bt_gemm() */
+#define BT_EPI_NONE 0          /* out = A*W                         */
+#define BT_EPI_BIAS 1          /* out = A*W + bias                  */
+#define BT_EPI_BIAS_GELU 2     /* out = gelu(A*W + bias)            */
+#define BT_EPI_BIAS_RESIDUAL 3 /* out = A*W + bias + residual       */
+
+typedef struct bt_encoder_s* bt_handle;
+
+/* Replaces the constructor arguments of `BertTransformer<OpType>`
+ * (bytetransformer/include/bert_transformer.h:120-131) and the numeric
+ * constants the reference hard-codes in its kernels. */
+typedef struct {
+  int head_num;
+  int size_per_head;   /* must be 64 (as for every fused path of the reference) */
+  int max_batch_size;
+  int max_seq_len;     /* <= 1024, as th_op/util.h:40 */
+  int intermediate_mult; /* FFN width = mult * hidden; the reference fixes 4 (bert_transformer.h:74) */
+  float ln_eps;        /* reference kernels: 1e-6 (layernorm.h:133) */
+  int gelu_kind;       /* BT_GELU_ERF or BT_GELU_TANH */
+  float tao;           /* softmax temperature (attention.h:33-39); 1.0 = standard */
+  int gamma_beta_fp32; /* LayerNorm gamma/beta are float (1) or half (0): `use_fp32` of the reference */
+  int device;          /* CUDA device ordinal; -1 = current device */
+} bt_config;
+
+/* Replaces `BertTransformerParam<OpType>` + `AttentionParam::attr_bias_QKV`
+ * (bert_transformer.h:31-82, attention.h:25-39): the 12 weight tensors of one layer. */
+typedef struct {
+  const void* qkv_kernel;                  /* [H,3H] half */
+  const void* qkv_bias;                    /* [3H]   half */
+  const void* attr_output_kernel;          /* [H,H]  half */
+  const void* attr_output_bias;            /* [H]    half */
+  const void* attr_output_layernorm_gamma; /* [H] half or float */
+  const void* attr_output_layernorm_beta;  /* [H] half or float */
+  const void* inter_kernel;                /* [H,4H] half */
+  const void* inter_bias;                  /* [4H]   half */
+  const void* output_kernel;               /* [4H,H] half */
+  const void* output_bias;                 /* [H]    half */
+  const void* output_layernorm_gamma;      /* [H] half or float */
+  const void* output_layernorm_beta;       /* [H] half or float */
+} bt_layer_weights;
+
+/* ---- object life cycle -------------------------------------------------- */
+
+/* `new BertTransformer<HALF>(max_batch, heads, 64, max_seq, ...)`
+ * (bert_transformer.h:120-185).  Host-only; fails with BT_ERR_UNSUPPORTED on a
+ * device that is not compute capability 10.x. */
+int bt_create(const bt_config* cfg, bt_handle* out);
+int bt_destroy(bt_handle h);
+
+/* `BertTransformer::initialize(param)` (bert_transformer.h:187-191), for layer
+ * `layer` of a stack (the reference object holds one layer).  Stores raw
+ * pointers only. */
+int bt_set_layer_weights(bt_handle h, int layer, const bt_layer_weights* w);
+
+/* `BertTransformer::cal_bufsize()` (bert_transformer.h:193-213). */
+int bt_workspace_bytes(bt_handle h, int batch_size, int seq_len, size_t* bytes);
+
+/* Human-readable text of the last host-side error of this handle. */
+const char* bt_last_error(bt_handle h);
+/* Reads (and clears) the device status word that kernels write when a bounded
+ * wait ran out.  Synchronises `stream`.  0 = no device-side error. */
+int bt_device_status(bt_handle h, void* stream, int* status);
+
+/* ---- forward passes ----------------------------------------------------- */
+
+/* `BertTransformer::infer(param)` (bert_transformer.h:215-222 ->
+ * src/bert_transformer.cu:28-130): one encoder layer on a padded batch;
+ * padding rows of `out` are written as zeros.  `input` and `out` must not alias. */
+int bt_layer_forward_padded(bt_handle h, int layer, const void* input /*[B,S,H]*/,
+                            const void* attr_mask /*[B,S,S]*/, void* out /*[B,S,H]*/,
+                            void* workspace, size_t workspace_bytes, int batch_size, int seq_len,
+                            void* stream);
+
+/* The reference's `for layer in range(n_layers)` loop
+ * (unit_test/python_scripts/bert_transformer_test.py:191-200) as ONE call:
+ * offsets + pack once, `n_layers` layers on the packed batch, one scatter. */
+int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const void* attr_mask,
+                            void* out, void* workspace, size_t workspace_bytes, int batch_size,
+                            int seq_len, void* stream);
+
+/* Same stack on an already packed batch: x_packed [T,H], cu_seqlens int32[B+1]
+ * on the DEVICE (same meaning as batch_idx), `total_tokens` = T known to the
+ * host (rows allocated in x_packed / out_packed), `max_len` >= every length.
+ * The reference has no packed entry; its packed state lives between
+ * src/bert_transformer.cu:68 and :124. */
+int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, const int* cu_seqlens,
+                            int batch_size, int max_len, int total_tokens, void* out_packed,
+                            void* workspace, size_t workspace_bytes, void* stream);
+/* Workspace for bt_stack_forward_packed(). */
+int bt_workspace_bytes_packed(bt_handle h, int batch_size, int total_tokens, size_t* bytes);
+
+/* ---- the individual steps of the path (each usable on its own) ---------- */
+
+/* `build_sequence_length_padding_offset_kernelLauncher`
+ * (bytetransformer/include/remove_padding.h:88-101) without its blocking D2H
+ * copy: T stays on the device in batch_idx[B]. */
+int bt_build_offsets(const void* attr_mask /*[B,S,S] half*/, int batch_size, int seq_len,
+                     int* batch_idx /*[B+1]*/, int* word_idx /*[B*S], first T used*/, void* stream);
+
+/* `compressBertInput_kernelLauncher` (remove_padding.h:104-121): packed[t,:] =
+ * padded[word_idx[t],:].  Rows are `hidden` halves, hidden % 8 == 0. */
+int bt_pack_rows(const void* padded /*[B*S,hidden]*/, void* packed /*[T,hidden]*/,
+                 const int* batch_idx, const int* word_idx, int batch_size, int seq_len, int hidden,
+                 void* stream);
+
+/* Inverse of bt_pack_rows with zero fill of padding rows (the scatter half of
+ * `add_bias_input_layernorm_restore_output_kernel_launcher`, layernorm.h:430-446). */
+int bt_restore_rows(const void* packed, void* padded, const int* batch_idx, int batch_size,
+                    int seq_len, int hidden, void* stream);
+
+/* `dense_layer_kernel_launcher` (bytetransformer/src/gemm.cu:32-39) and
+ * `gemm_bias_gelu` (src/gemm_bias_act.cu:76-148): out[M,N] = epi(A[M,K] * W[K,N]).
+ * A row-major with row stride K, W row-major [K,N], out/residual row stride N.
+ * The number of valid rows is min(*m_dev, m_rows) when m_dev != NULL (device
+ * int, e.g. batch_idx + B), else m_rows; A/out/residual must have m_rows rows
+ * allocated.  K % 64 == 0 and N % 64 == 0.  fp32 accumulation in tensor memory. */
+int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bias,
+            const void* residual, const int* m_dev, int m_rows, int N, int K, int epilogue,
+            int gelu_kind, void* stream);
+
+/* `Attention<HALF>::infer` (bytetransformer/include/attention.h:124-139; packed
+ * kernels src/attention_fused.cu:295-414, src/attention_fused_long.cu:171-312):
+ * ctx[T,H] = per sequence, per head softmax(Q K^T / sqrt(64) / tao) V over the
+ * sequence's own valid tokens.  qkv [rows,3H] already holds Q|K|V + bias. */
+int bt_attention(bt_handle h, const void* qkv, void* ctx, const int* batch_idx, int batch_size,
+                 int max_len, int rows_allocated, void* stream);
+
+/* `add_bias_input_layernorm_kernel_launcher` (layernorm.h:410-428):
+ * out = LN(x + bias + residual) * gamma + beta over rows [0, min(*m_dev, m_rows)).
+ * bias and residual may be NULL (treated as zero).  hidden % 8 == 0, <= 8192. */
+int bt_add_bias_residual_layernorm(const void* x, const void* bias, const void* residual,
+                                   const void* gamma, const void* beta, int gamma_beta_fp32,
+                                   void* out, const int* m_dev, int m_rows, int hidden, float eps,
+                                   void* stream);
+
+/* `add_bias_input_layernorm_restore_output_kernel_launcher` (layernorm.h:430-446):
+ * same LayerNorm, but row (b,i) of the padded output takes packed row
+ * batch_idx[b]+i, and rows i >= len_b are written as zeros. */
+int bt_add_bias_residual_layernorm_restore(const void* x, const void* bias, const void* residual,
+                                           const void* gamma, const void* beta,
+                                           int gamma_beta_fp32, void* out_padded,
+                                           const int* batch_idx, int batch_size, int seq_len,
+                                           int hidden, float eps, void* stream);
+
+/* `add_bias_gelu` (bytetransformer/src/gemm_bias_act.cu:32-66): x = gelu(x + bias) in place
+ * over [rows, n]. */
+int bt_add_bias_gelu(void* x, const void* bias, const int* m_dev, int m_rows, int n, int gelu_kind,
+                     void* stream);
+
+/* `softmax_kernelLauncher` (bytetransformer/include/softmax.h:318-475): in-place
+ * masked softmax over logits laid out [nh,B,S,S] (softmax.h:33):
+ * p = softmax(scale*x + (1-mask)*-10000) with 1/(sum+1e-6) normalisation;
+ * mask [B,S,S].  The reference applies the scale in the preceding GEMM; pass 1.0
+ * for identical behaviour. */
+int bt_masked_softmax(void* logits, const void* attr_mask, int batch_size, int head_num, int seq_len,
+                      float scale, void* stream);
+
+/* Library build information, e.g. "bt_b200 sm_100a". */
+const char* bt_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BT_B200_H_ */

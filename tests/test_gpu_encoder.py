@@ -1,0 +1,190 @@
+"""GPU parity of the encoder layer / stack through the C ABI against the oracle
+(the reference's own fp32 PyTorch encoder, oracle/bert_oracle.py), on the
+committed golden vectors and on seeded inputs with the benchmark shapes.
+
+Tolerance (fp16 path vs fp32 oracle): max-abs <= 2e-2, mean-abs <= 1e-3."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (MAX_ABS_TOL, MEAN_ABS_TOL, assert_close_fp16, fp16_round, make_layer_weights,
+                     to_device_weights)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _oracle(x, mask, layers, nh, hs, **kw):
+    from oracle.bert_oracle import encoder_stack
+    return encoder_stack(x, mask, layers, nh, hs, **kw)
+
+
+def _valid(lens, S):
+    return torch.arange(S)[None, :] < torch.as_tensor(lens)[:, None]
+
+
+def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf", eps=1e-6, per_layer_op=False):
+    from bytetransformer_b200.encoder import Encoder, bert_transformer
+    from oracle.bert_oracle import build_attr_mask
+    H = nh * 64
+    g = torch.Generator().manual_seed(seed)
+    layers = [make_layer_weights(H, g, recipe=recipe) for _ in range(n_layers)]
+    x = torch.randn(B, S, H, generator=g) if recipe == "normal" else torch.empty(B, S, H).uniform_(-0.4, 0.4, generator=g)
+    lens_t = torch.as_tensor(lens)
+    mask = build_attr_mask(lens_t, S)
+    want = _oracle(x.half().float(), mask, [fp16_round(w) for w in layers], nh, 64, ln_eps=eps, gelu_kind=gelu)[-1]
+    dl = [to_device_weights(w, dev, gb32) for w in layers]
+    xd, md = x.half().to(dev), mask.half().to(dev)
+    if per_layer_op:
+        h = xd
+        for w in dl:
+            h = bert_transformer(nh, 64, *w, h, md, True, True, ln_eps=eps, gelu=gelu)
+        got = h
+    else:
+        enc = Encoder(nh, 64, dl, ln_eps=eps, gelu=gelu)
+        got = enc.forward(xd, md)
+        assert enc.device_status() == 0
+        enc.close()
+    v = _valid(lens, S)
+    mx, mn = assert_close_fp16(got.cpu()[v], want[v], f"encoder B{B} S{S} L{n_layers} {recipe}")
+    assert (got.cpu()[~v] == 0).all(), "padding rows must be exact zeros"
+    return mx, mn
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "*.npz"))), ids=os.path.basename)
+def test_golden_vectors_from_reference_script(cuda_device, path):
+    """Inputs, weights and outputs produced by the reference's own test script
+    (tests/golden/make_golden.py); its PyTorch encoder uses exact GELU and the
+    LayerNorm default eps 1e-5, so the library is configured the same way."""
+    from bytetransformer_b200.encoder import Encoder
+    from oracle.bert_oracle import WEIGHT_NAMES
+    d = np.load(path)
+    B, S, nh, hs, nl, _ = d["meta"].tolist()
+    layers = [[torch.from_numpy(d[f"l{l}_{n}"]) for n in WEIGHT_NAMES] for l in range(nl)]
+    x = torch.from_numpy(d["from_tensor"])
+    mask = torch.from_numpy(d["attr_mask"])
+    lens = d["input_lens"].tolist()
+    dl = [to_device_weights(w, cuda_device) for w in layers]
+    enc = Encoder(nh, hs, dl, ln_eps=1e-5, gelu="erf")
+    h = x.half().to(cuda_device)
+    md = mask.half().to(cuda_device)
+    v = _valid(lens, S)
+    # the reference's weights are U(-0.4,0.4): activations are O(10), so the bound scales with them
+    for l in range(nl):
+        h = enc.forward_layer(l, h, md)
+        want = torch.from_numpy(d[f"l{l}_out"])
+        # golden weights/inputs are fp32; the GPU sees them rounded to fp16 -> looser bound than the oracle test
+        assert_close_fp16(h.cpu()[v], want[v], f"golden layer {l}", max_abs=6e-2, mean_abs=6e-3)
+        assert (h.cpu()[~v] == 0).all()
+    assert enc.device_status() == 0
+    enc.close()
+
+
+def test_config1_single_layer_b16_s64(cuda_device):
+    """BERT-base layer, batch 16, max_seq 64, lengths uniform in [1,64] (seeded)."""
+    g = torch.Generator().manual_seed(101)
+    lens = torch.randint(1, 65, (16,), generator=g).tolist()
+    _run_case(cuda_device, 16, 64, 12, 1, lens, "normal", seed=1)
+
+
+def test_config1_reference_recipe_uniform_weights(cuda_device):
+    """Same shape with the reference's own recipe (everything U(-0.4,0.4), lengths U[13,64]):
+    exercises bias / gamma / beta.  Activations reach O(10), hence a scaled bound."""
+    from bytetransformer_b200.encoder import Encoder
+    from oracle.bert_oracle import build_attr_mask, encoder_stack
+    g = torch.Generator().manual_seed(202)
+    B, S, nh, H = 16, 64, 12, 768
+    lens = torch.randint(13, 65, (B,), generator=g).tolist()
+    layers = [make_layer_weights(H, g, recipe="uniform")]
+    x = torch.empty(B, S, H).uniform_(-0.4, 0.4, generator=g)
+    mask = build_attr_mask(torch.as_tensor(lens), S)
+    want = encoder_stack(x.half().float(), mask, [fp16_round(w) for w in layers], nh, 64, ln_eps=1e-6)[-1]
+    enc = Encoder(nh, 64, [to_device_weights(w, cuda_device) for w in layers])
+    got = enc.forward(x.half().to(cuda_device), mask.half().to(cuda_device))
+    v = _valid(lens, S)
+    assert_close_fp16(got.cpu()[v], want[v], "uniform recipe")
+    assert (got.cpu()[~v] == 0).all()
+    enc.close()
+
+
+def test_fp32_gamma_beta_and_tanh_gelu(cuda_device):
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(0, 49, (6,), generator=g).tolist()
+    _run_case(cuda_device, 6, 48, 2, 2, lens, "uniform", seed=3, gb32=True, gelu="tanh", eps=1e-5)
+
+
+def test_per_layer_op_equals_stack(cuda_device):
+    """Calling the one-layer operator N times (the reference's loop) and the one-call
+    stack give the same result within tolerance (re-packing between layers is exact)."""
+    g = torch.Generator().manual_seed(6)
+    lens = torch.randint(1, 97, (4,), generator=g).tolist()
+    _run_case(cuda_device, 4, 96, 12, 3, lens, "normal", seed=8, per_layer_op=True)
+    _run_case(cuda_device, 4, 96, 12, 3, lens, "normal", seed=8, per_layer_op=False)
+
+
+def test_config3_b16_s512_12_layers(cuda_device):
+    """BERT-base 12 layers, batch 16, max_seq 512, lengths uniform in [1,512] (seeded)."""
+    g = torch.Generator().manual_seed(303)
+    lens = torch.randint(1, 513, (16,), generator=g).tolist()
+    _run_case(cuda_device, 16, 512, 12, 12, lens, "normal", seed=4)
+
+
+@pytest.mark.parametrize("S", [64, 320, 1024])
+def test_config2_batch1(cuda_device, S):
+    """Batch 1, valid length round(0.6*S), 12 layers."""
+    _run_case(cuda_device, 1, S, 12, 12, [round(0.6 * S)], "normal", seed=S)
+
+
+def test_config4_bert_large_shapes_sampled(cuda_device):
+    """BERT-large (hidden 1024, 16 heads), max_seq 384, truncated-normal lengths; 8 of the 64
+    sequences and 3 of the 24 layers so that the CPU oracle finishes in seconds."""
+    g = torch.Generator().manual_seed(404)
+    lens = torch.clamp(torch.round(torch.randn(8, generator=g) * 80 + 230), 8, 384).long().tolist()
+    _run_case(cuda_device, 8, 384, 16, 3, lens, "normal", seed=9)
+
+
+def test_packed_entry_matches_padded(cuda_device):
+    """bt_stack_forward_packed on x[T,H] + cu_seqlens gives the rows of the padded call."""
+    from bytetransformer_b200.encoder import Encoder, build_offsets, pack_rows
+    from oracle.bert_oracle import build_attr_mask
+    g = torch.Generator().manual_seed(12)
+    B, S, nh, H, nl = 7, 200, 12, 768, 2
+    lens = torch.randint(0, S + 1, (B,), generator=g).tolist()
+    layers = [to_device_weights(make_layer_weights(H, g), cuda_device) for _ in range(nl)]
+    x = torch.randn(B, S, H, generator=g).half().to(cuda_device)
+    mask = build_attr_mask(torch.as_tensor(lens), S, torch.float16).to(cuda_device)
+    enc = Encoder(nh, 64, layers)
+    padded = enc.forward(x, mask)
+    bi, _ = build_offsets(mask)
+    T = int(bi[-1].item())
+    xp = pack_rows(x, bi)[:T].contiguous()
+    outp = enc.forward_packed(xp, bi, max(lens))
+    v = _valid(lens, S)
+    assert torch.equal(outp.cpu(), padded.cpu()[v])
+    assert enc.device_status() == 0
+    enc.close()
+
+
+def test_error_behaviour(cuda_device):
+    """Bad input raises RuntimeError, as TORCH_CHECK does in the reference's plugin."""
+    from bytetransformer_b200.encoder import Encoder
+    g = torch.Generator().manual_seed(1)
+    w = to_device_weights(make_layer_weights(128, g), cuda_device)
+    enc = Encoder(2, 64, [w])
+    x = torch.zeros(2, 8, 128, dtype=torch.float16, device=cuda_device)
+    m = torch.ones(2, 8, 8, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        enc.forward(x.float(), m)                       # wrong dtype
+    with pytest.raises(RuntimeError):
+        enc.forward(x.cpu(), m)                         # not CUDA
+    with pytest.raises(RuntimeError):
+        enc.forward(x.transpose(0, 1), m)               # not contiguous
+    with pytest.raises(RuntimeError):
+        enc.forward(torch.zeros(1, 1025, 128, dtype=torch.float16, device=cuda_device),
+                    torch.ones(1, 1, 1, dtype=torch.float16, device=cuda_device))   # seq_len too long
+    with pytest.raises(RuntimeError):
+        Encoder(2, 32, [w])                             # head size must be 64
+    enc.close()

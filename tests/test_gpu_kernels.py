@@ -1,0 +1,267 @@
+"""GPU parity tests of the individual steps of the path, through the C ABI,
+against the CPU oracle (oracle/bert_oracle.py)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close_fp16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def enc(cuda_device):
+    from bytetransformer_b200.encoder import Encoder
+    from helpers import make_layer_weights, to_device_weights
+    g = torch.Generator().manual_seed(0)
+    w = to_device_weights(make_layer_weights(768, g), cuda_device)
+    e = Encoder(12, 64, [w])
+    yield e
+    assert e.device_status() == 0
+    e.close()
+
+
+def _mask_from_lens(lens, S):
+    from oracle.bert_oracle import build_attr_mask
+    return build_attr_mask(torch.tensor(lens), S, torch.float16)
+
+
+# ---------------------------------------------------------------- offsets / pack / restore
+@pytest.mark.parametrize("B,S,lens", [
+    (1, 8, [5]),
+    (4, 24, [13, 7, 15, 13]),
+    (5, 16, [3, 8, 5, 10, 0]),            # zero-length sequence
+    (3, 13, [13, 0, 1]),                   # S not a multiple of 8, full + empty
+    (40, 64, None),                        # more than 32 sequences: crosses the warp-scan boundary
+    (1500, 32, None),                      # more than 1024 sequences: crosses the block-scan chunk
+    (16, 512, None),
+])
+def test_offsets_bit_exact(cuda_device, B, S, lens):
+    from bytetransformer_b200.encoder import build_offsets
+    from oracle.bert_oracle import build_offsets as ref_offsets
+    if lens is None:
+        g = torch.Generator().manual_seed(B * 1000 + S)
+        lens = torch.randint(0, S + 1, (B,), generator=g).tolist()
+    mask = _mask_from_lens(lens, S)
+    bi, wi = build_offsets(mask.to(cuda_device))
+    rbi, rwi = ref_offsets(mask.numpy())
+    assert np.array_equal(bi.cpu().numpy(), rbi)
+    T = int(rbi[-1])
+    assert np.array_equal(wi.cpu().numpy()[:T], rwi)
+
+
+def test_offsets_counts_mask_values_ge_half(cuda_device):
+    """Length is the COUNT of entries >= 0.5 in mask row 0 (remove_padding.h:51-54),
+    whatever the other rows hold."""
+    from bytetransformer_b200.encoder import build_offsets
+    from oracle.bert_oracle import build_offsets as ref_offsets
+    B, S = 3, 16
+    m = torch.zeros(B, S, S, dtype=torch.float16)
+    m[0, 0, :5] = 1.0
+    m[1, 0, :7] = 0.5
+    m[1, 0, 7:9] = 0.49
+    m[2, 0, :3] = 2.0
+    m[:, 1:, :] = 1.0  # other rows must not matter
+    bi, wi = build_offsets(m.to(cuda_device))
+    rbi, rwi = ref_offsets(m.numpy())
+    assert rbi.tolist() == [0, 5, 12, 15]
+    assert np.array_equal(bi.cpu().numpy(), rbi)
+    assert np.array_equal(wi.cpu().numpy()[:15], rwi)
+
+
+@pytest.mark.parametrize("B,S,H", [(5, 16, 64), (16, 64, 768), (3, 13, 128)])
+def test_pack_restore_round_trip(cuda_device, B, S, H):
+    from bytetransformer_b200.encoder import build_offsets, pack_rows, restore_rows
+    from oracle.bert_oracle import build_offsets as ref_offsets, pack_rows as ref_pack, restore_rows as ref_restore
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(0, S + 1, (B,), generator=g).tolist()
+    mask = _mask_from_lens(lens, S)
+    x = torch.randn(B, S, H, generator=g).half()
+    bi, _ = build_offsets(mask.to(cuda_device))
+    packed = pack_rows(x.to(cuda_device), bi)
+    rbi, rwi = ref_offsets(mask.numpy())
+    T = int(rbi[-1])
+    want = ref_pack(x.numpy(), rwi)
+    assert np.array_equal(packed.cpu().numpy()[:T], want)          # bit-exact copy
+    back = restore_rows(packed, bi, B, S)
+    assert np.array_equal(back.cpu().numpy(), ref_restore(want, rbi, B, S))  # zeros in padding rows
+
+
+# ---------------------------------------------------------------- row kernels
+@pytest.mark.parametrize("M,H,gb32", [(7, 64, False), (129, 768, False), (300, 1024, True), (33, 128, True)])
+def test_add_bias_residual_layernorm(cuda_device, M, H, gb32):
+    from bytetransformer_b200.encoder import add_bias_residual_layernorm
+    from oracle.bert_oracle import add_bias_residual_layernorm as ref
+    g = torch.Generator().manual_seed(M + H)
+    x = torch.randn(M, H, generator=g).half()
+    r = torch.randn(M, H, generator=g).half()
+    b = torch.empty(H).uniform_(-0.4, 0.4, generator=g).half()
+    gamma = torch.empty(H).uniform_(-0.4, 0.4, generator=g)
+    beta = torch.empty(H).uniform_(-0.4, 0.4, generator=g)
+    gd = gamma if gb32 else gamma.half()
+    bd = beta if gb32 else beta.half()
+    got = add_bias_residual_layernorm(x.to(cuda_device), b.to(cuda_device), r.to(cuda_device),
+                                      gd.to(cuda_device), bd.to(cuda_device), eps=1e-6)
+    want = ref(x.float(), b.float(), r.float(), gd.float(), bd.float(), eps=1e-6)
+    assert_close_fp16(got, want, "layernorm", max_abs=4e-3, mean_abs=5e-4)
+
+
+def test_layernorm_row_count_from_device(cuda_device):
+    from bytetransformer_b200.encoder import add_bias_residual_layernorm
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 256, generator=g).half().to(cuda_device)
+    gamma = torch.ones(256).half().to(cuda_device)
+    beta = torch.zeros(256).half().to(cuda_device)
+    m_dev = torch.tensor([10], dtype=torch.int32, device=cuda_device)
+    out = add_bias_residual_layernorm(x, None, None, gamma, beta, m_dev=m_dev)
+    assert out[10:].abs().max().item() == 0.0      # rows beyond the device-side count untouched
+    assert out[:10].abs().max().item() > 0.1
+
+
+def test_layernorm_restore(cuda_device):
+    from bytetransformer_b200.encoder import add_bias_residual_layernorm_restore, build_offsets
+    from oracle.bert_oracle import add_bias_residual_layernorm as ref, build_offsets as ref_offsets, restore_rows
+    B, S, H = 5, 16, 768
+    lens = [3, 16, 0, 10, 1]
+    mask = _mask_from_lens(lens, S)
+    rbi, _ = ref_offsets(mask.numpy())
+    T = int(rbi[-1])
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, H, generator=g).half()
+    r = torch.randn(T, H, generator=g).half()
+    b = torch.empty(H).uniform_(-0.4, 0.4, generator=g).half()
+    gamma = torch.empty(H).uniform_(-0.4, 0.4, generator=g).half()
+    beta = torch.empty(H).uniform_(-0.4, 0.4, generator=g).half()
+    bi, _ = build_offsets(mask.to(cuda_device))
+    got = add_bias_residual_layernorm_restore(x.to(cuda_device), b.to(cuda_device), r.to(cuda_device),
+                                              gamma.to(cuda_device), beta.to(cuda_device), bi, B, S)
+    want_packed = ref(x.float(), b.float(), r.float(), gamma.float(), beta.float(), eps=1e-6)
+    want = torch.from_numpy(restore_rows(want_packed.numpy(), rbi, B, S))
+    assert_close_fp16(got, want, "layernorm_restore", max_abs=4e-3, mean_abs=5e-4)
+    pad = ~(torch.arange(S)[None, :] < torch.tensor(lens)[:, None])
+    assert (got.cpu()[pad] == 0).all()            # exact zeros in padding rows
+
+
+@pytest.mark.parametrize("kind", ["erf", "tanh"])
+def test_add_bias_gelu(cuda_device, kind):
+    from bytetransformer_b200.encoder import add_bias_gelu_
+    from oracle.bert_oracle import add_bias_gelu as ref
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(37, 3072, generator=g) * 2).half()
+    b = torch.empty(3072).uniform_(-0.4, 0.4, generator=g).half()
+    got = add_bias_gelu_(x.clone().to(cuda_device), b.to(cuda_device), kind)
+    want = ref(x.float(), b.float(), kind)
+    assert_close_fp16(got, want, "add_bias_gelu", max_abs=4e-3, mean_abs=3e-4)
+
+
+@pytest.mark.parametrize("B,nh,S", [(2, 3, 64), (2, 2, 13), (1, 2, 512)])
+def test_masked_softmax(cuda_device, B, nh, S):
+    from bytetransformer_b200.encoder import masked_softmax_
+    from oracle.bert_oracle import masked_softmax as ref
+    g = torch.Generator().manual_seed(S)
+    lens = torch.randint(1, S + 1, (B,), generator=g).tolist()
+    mask = _mask_from_lens(lens, S)
+    x = (torch.randn(nh, B, S, S, generator=g) * 3).half()
+    got = masked_softmax_(x.clone().to(cuda_device), mask.to(cuda_device), 0.125)
+    want = ref(x.float(), mask.float(), 0.125)
+    assert_close_fp16(got, want, "masked_softmax", max_abs=2e-3, mean_abs=1e-4)
+
+
+# ---------------------------------------------------------------- GEMM
+def _gemm_case(enc, dev, M, N, K, epi, gelu="erf", m_valid=None, seed=0):
+    from bytetransformer_b200 import _abi
+    g = torch.Generator().manual_seed(seed + M + N + K)
+    a = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(K, N, generator=g) * 0.05).half()
+    bias = torch.empty(N).uniform_(-0.4, 0.4, generator=g).half()
+    res = torch.randn(M, N, generator=g).half()
+    m_dev = None if m_valid is None else torch.tensor([m_valid], dtype=torch.int32, device=dev)
+    got = enc.gemm(a.to(dev), w.to(dev), bias.to(dev), res.to(dev), epilogue=epi,
+                   gelu=_abi.BT_GELU_ERF if gelu == "erf" else _abi.BT_GELU_TANH, m_dev=m_dev)
+    want = a.float() @ w.float()
+    if epi != _abi.BT_EPI_NONE:
+        want = want + bias.float()
+    if epi == _abi.BT_EPI_BIAS_GELU:
+        want = torch.nn.functional.gelu(want, approximate="none" if gelu == "erf" else "tanh")
+    if epi == _abi.BT_EPI_BIAS_RESIDUAL:
+        want = want + res.float()
+    mv = M if m_valid is None else m_valid
+    scale = max(1.0, want.abs().max().item())
+    assert_close_fp16(got[:mv], want[:mv], f"gemm {M}x{N}x{K} epi{epi}", max_abs=4e-3 * scale, mean_abs=4e-4 * scale)
+    if mv < M:
+        assert got[mv:].abs().max().item() == 0.0, "rows beyond the device-side row count were written"
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (1, 64, 64), (7, 128, 64), (128, 256, 128), (129, 192, 192), (300, 768, 768),
+    (640, 2304, 768), (1000, 768, 3072), (4500, 3072, 768), (257, 1024, 1024),
+])
+def test_gemm_plain(enc, cuda_device, M, N, K):
+    from bytetransformer_b200 import _abi
+    _gemm_case(enc, cuda_device, M, N, K, _abi.BT_EPI_NONE)
+
+
+@pytest.mark.parametrize("epi,gelu", [(1, "erf"), (2, "erf"), (2, "tanh"), (3, "erf")])
+@pytest.mark.parametrize("M,N,K", [(200, 768, 768), (515, 3072, 768)])
+def test_gemm_epilogues(enc, cuda_device, M, N, K, epi, gelu):
+    _gemm_case(enc, cuda_device, M, N, K, epi, gelu)
+
+
+def test_gemm_row_count_from_device(enc, cuda_device):
+    from bytetransformer_b200 import _abi
+    _gemm_case(enc, cuda_device, 700, 768, 768, _abi.BT_EPI_BIAS, m_valid=333)
+    _gemm_case(enc, cuda_device, 256, 256, 64, _abi.BT_EPI_NONE, m_valid=0)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_every_tile_width(enc, cuda_device, bn):
+    from bytetransformer_b200 import _abi
+    lib = _abi.load()
+    lib.bt_debug_set(4, bn)
+    try:
+        _gemm_case(enc, cuda_device, 390, 768, 768, _abi.BT_EPI_BIAS_RESIDUAL)
+        _gemm_case(enc, cuda_device, 4000, 768, 3072, _abi.BT_EPI_BIAS)
+    finally:
+        lib.bt_debug_set(4, 0)
+
+
+def test_gemm_twice_bit_identical(enc, cuda_device):
+    """Same launch twice must give bit-identical output (catches smem / TMEM races)."""
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(2000, 768, generator=g).half().to(cuda_device)
+    w = (torch.randn(768, 2304, generator=g) * 0.05).half().to(cuda_device)
+    o1 = enc.gemm(a, w)
+    o2 = enc.gemm(a, w)
+    assert torch.equal(o1, o2)
+
+
+# ---------------------------------------------------------------- attention
+@pytest.mark.parametrize("lens", [
+    [1], [15], [16], [17], [64], [127], [128], [129], [255, 3], [300, 1, 128, 77],
+    [512, 17, 0, 200], [1024], [5, 0, 0, 9],
+])
+def test_attention(enc, cuda_device, lens):
+    from oracle.bert_oracle import attention_packed
+    H = enc.hidden
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T = int(cu[-1])
+    g = torch.Generator().manual_seed(sum(lens))
+    rows = T + 5                                   # a few allocated rows beyond T, filled with NaN
+    qkv = torch.randn(rows, 3 * H, generator=g).half()
+    qkv[T:] = float("nan")
+    got = enc.attention(qkv.to(cuda_device), torch.from_numpy(cu).to(cuda_device), max(lens))
+    want = attention_packed(qkv[:T].float(), cu.tolist(), enc.head_num, enc.head_size)
+    assert_close_fp16(got[:T], want, f"attention {lens}", max_abs=5e-3, mean_abs=3e-4)
+    assert got[T:].abs().max().item() == 0.0 if rows > T else True
+
+
+def test_attention_twice_bit_identical(enc, cuda_device):
+    lens = [300, 77, 129]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32), device=cuda_device)
+    g = torch.Generator().manual_seed(1)
+    qkv = torch.randn(sum(lens), 3 * enc.hidden, generator=g).half().to(cuda_device)
+    a = enc.attention(qkv, cu, 300)
+    b = enc.attention(qkv, cu, 300)
+    assert torch.equal(a, b)
