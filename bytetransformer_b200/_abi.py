@@ -24,6 +24,7 @@ BT_EPI_NONE = 0
 BT_EPI_BIAS = 1
 BT_EPI_BIAS_GELU = 2
 BT_EPI_BIAS_RESIDUAL = 3
+BT_EPI_BIAS_RESIDUAL_F32OUT = 4
 
 ERROR_NAMES = {0: "BT_OK", 1: "BT_ERR_INVALID_ARG", 2: "BT_ERR_WORKSPACE", 3: "BT_ERR_CUDA",
                4: "BT_ERR_UNSUPPORTED", 5: "BT_ERR_DEVICE_STATUS"}
@@ -63,8 +64,8 @@ SIGNATURES = {
     "bt_restore_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "bt_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
-    "bt_add_bias_residual_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp]),
-    "bt_add_bias_residual_layernorm_restore": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "bt_add_bias_residual_layernorm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp]),
+    "bt_add_bias_residual_layernorm_restore": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp]),
     "bt_add_bias_gelu": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_masked_softmax": (_i, [_vp, _vp, _i, _i, _i, _f, _vp]),
 }

@@ -74,9 +74,9 @@ __device__ __forceinline__ void load_gb8(const void* p, int vec, float (&f)[8]) 
 // RESTORE = false: rows [0, M) of x -> rows [0, M) of out.
 // RESTORE = true : grid covers the B*S padded rows; row (b,i) reads packed row
 //                  batch_idx[b]+i when i < len_b, else writes zeros.
-template <bool RESTORE, bool GB_FP32, int NVEC>
+template <bool RESTORE, bool GB_FP32, bool X_FP32, int NVEC>
 __global__ void __launch_bounds__(kLnWarps * 32)
-layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ bias,
+layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ bias,
                       const __half* __restrict__ residual, const void* __restrict__ gamma,
                       const void* __restrict__ beta, __half* __restrict__ out, const int* __restrict__ m_dev,
                       int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps) {
@@ -106,7 +106,8 @@ layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ b
     if (row >= M) return;
   }
 
-  const uint4* x4 = reinterpret_cast<const uint4*>(x + src_row * hidden);
+  const uint4* x4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(x_v) + src_row * hidden);
+  const float4* xf = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x_v) + src_row * hidden);
   const uint4* r4 = residual ? reinterpret_cast<const uint4*>(residual + src_row * hidden) : nullptr;
   const uint4* b4 = bias ? reinterpret_cast<const uint4*>(bias) : nullptr;
 
@@ -116,7 +117,13 @@ layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ b
   for (int it = 0; it < NVEC; ++it) {
     const int v = it * 32 + lane;
     if (v < nvec) {
-      unpack8(__ldg(x4 + v), val[it]);
+      if (X_FP32) {
+        const float4 a = __ldg(xf + 2 * v), b = __ldg(xf + 2 * v + 1);
+        val[it][0] = a.x; val[it][1] = a.y; val[it][2] = a.z; val[it][3] = a.w;
+        val[it][4] = b.x; val[it][5] = b.y; val[it][6] = b.z; val[it][7] = b.w;
+      } else {
+        unpack8(__ldg(x4 + v), val[it]);
+      }
       if (r4) {
         float t[8];
         unpack8(__ldg(r4 + v), t);
@@ -165,13 +172,13 @@ layernorm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ b
   }
 }
 
-template <bool RESTORE, bool GB_FP32>
-cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, const __half* x, const __half* bias,
+template <bool RESTORE, bool GB_FP32, bool X_FP32>
+cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, const void* x, const __half* bias,
                            const __half* residual, const void* gamma, const void* beta, __half* out,
                            const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps) {
 #define BT_LN_CASE(NV)                                                                                        \
   case NV:                                                                                                    \
-    layernorm_rows_kernel<RESTORE, GB_FP32, NV><<<grid, kLnWarps * 32, 0, stream>>>(                          \
+    layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV><<<grid, kLnWarps * 32, 0, stream>>>(                          \
         x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps);                       \
     break;
   switch (nvec_needed) {
@@ -297,20 +304,36 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
 
 }  // namespace
 
-cudaError_t launch_layernorm(const __half* x, const __half* bias, const __half* residual, const void* gamma,
-                             const void* beta, bool gb_fp32, __half* out, const int* m_dev, int m_rows, int hidden,
-                             float eps, cudaStream_t stream) {
+template <bool RESTORE>
+static cudaError_t launch_ln_dispatch(bool gb_fp32, bool x_fp32, int nv, dim3 grid, cudaStream_t stream, const void* x,
+                                      const __half* bias, const __half* residual, const void* gamma, const void* beta,
+                                      __half* out, const int* m_dev, int m_rows, const int* batch_idx, int S,
+                                      int hidden, float eps) {
+  if (gb_fp32) {
+    if (x_fp32)
+      return launch_ln_nvec<RESTORE, true, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                                 batch_idx, S, hidden, eps);
+    return launch_ln_nvec<RESTORE, true, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                                batch_idx, S, hidden, eps);
+  }
+  if (x_fp32)
+    return launch_ln_nvec<RESTORE, false, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                                batch_idx, S, hidden, eps);
+  return launch_ln_nvec<RESTORE, false, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
+                                               batch_idx, S, hidden, eps);
+}
+
+cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, const __half* residual,
+                             const void* gamma, const void* beta, bool gb_fp32, __half* out, const int* m_dev,
+                             int m_rows, int hidden, float eps, cudaStream_t stream) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || m_rows <= 0) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   dim3 grid((m_rows + kLnWarps - 1) / kLnWarps);
-  if (gb_fp32)
-    return launch_ln_nvec<false, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                       nullptr, 0, hidden, eps);
-  return launch_ln_nvec<false, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                      nullptr, 0, hidden, eps);
+  return launch_ln_dispatch<false>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev,
+                                   m_rows, nullptr, 0, hidden, eps);
 }
 
-cudaError_t launch_layernorm_restore(const __half* x, const __half* bias, const __half* residual,
+cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                                      const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
                                      const int* batch_idx, int B, int S, int hidden, float eps,
                                      cudaStream_t stream) {
@@ -318,11 +341,8 @@ cudaError_t launch_layernorm_restore(const __half* x, const __half* bias, const 
   const int nv = (hidden / 8 + 31) / 32;
   const long long rows = static_cast<long long>(B) * S;
   dim3 grid(static_cast<unsigned>((rows + kLnWarps - 1) / kLnWarps));
-  if (gb_fp32)
-    return launch_ln_nvec<true, true>(nv, grid, stream, x, bias, residual, gamma, beta, out_padded, nullptr,
-                                      static_cast<int>(rows), batch_idx, S, hidden, eps);
-  return launch_ln_nvec<true, false>(nv, grid, stream, x, bias, residual, gamma, beta, out_padded, nullptr,
-                                     static_cast<int>(rows), batch_idx, S, hidden, eps);
+  return launch_ln_dispatch<true>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out_padded,
+                                  nullptr, static_cast<int>(rows), batch_idx, S, hidden, eps);
 }
 
 cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev, int m_rows, int n, int gelu_kind,

@@ -5,10 +5,10 @@
 // nine steps in bytetransformer/src/bert_transformer.cu:62-124):
 //   1. qkv  = x * Wqkv + b_qkv                         GEMM, bias epilogue
 //   2. ctx  = fused MHA(qkv)                           one kernel, any length
-//   3. pre  = ctx * Wo + b_o + x                       GEMM, bias+residual epilogue
+//   3. pre  = ctx * Wo + b_o + x   (fp32)              GEMM, bias+residual epilogue
 //   4. y    = LN(pre)                                  row kernel
 //   5. mid  = gelu(y * W1 + b_1)                       GEMM, bias+GELU epilogue
-//   6. pre  = mid * W2 + b_2 + y                       GEMM, bias+residual epilogue
+//   6. pre  = mid * W2 + b_2 + y   (fp32)              GEMM, bias+residual epilogue
 //   7. out  = LN(pre)   (last layer of a padded call: LN + scatter + zero fill)
 // Offsets and pack run once per call, not once per layer, and the token count T
 // never travels to the host: every kernel reads it from batch_idx[B].
@@ -131,7 +131,8 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 struct Workspace {
   int* batch_idx;
   int* word_idx;
-  __half *xa, *xb, *qkv, *ctx, *pre, *y, *mid;
+  __half *xa, *xb, *qkv, *ctx, *y, *mid;
+  float* pre;  // pre-LayerNorm sum, kept in fp32
   size_t bytes;
 };
 
@@ -152,7 +153,7 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   w.xb = reinterpret_cast<__half*>(take(rh));
   w.qkv = reinterpret_cast<__half*>(take(3 * rh));
   w.ctx = reinterpret_cast<__half*>(take(rh));
-  w.pre = reinterpret_cast<__half*>(take(rh));
+  w.pre = reinterpret_cast<float*>(take(2 * rh));
   w.y = reinterpret_cast<__half*>(take(rh));
   w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
   w.bytes = off + 1024;  // slack so that an unaligned base can be rounded up
@@ -219,23 +220,23 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
                      stream)) != BT_OK)
     return rc;
   if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream)) != BT_OK) return rc;
-  if ((rc = run_gemm(h, ws.ctx, w.attr_output_kernel, ws.pre, w.attr_output_bias, x_in, m_dev, rows, H, H,
-                     BT_EPI_BIAS_RESIDUAL, 0, stream)) != BT_OK)
+  if ((rc = run_gemm(h, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre), w.attr_output_bias, x_in, m_dev, rows, H,
+                     H, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
     return rc;
-  cudaError_t e = launch_layernorm(ws.pre, nullptr, nullptr, w.attr_output_layernorm_gamma,
+  cudaError_t e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.attr_output_layernorm_gamma,
                                    w.attr_output_layernorm_beta, gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream);
   if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
   if ((rc = run_gemm(h, ws.y, w.inter_kernel, ws.mid, w.inter_bias, nullptr, m_dev, rows, F, H, BT_EPI_BIAS_GELU,
                      h->cfg.gelu_kind, stream)) != BT_OK)
     return rc;
-  if ((rc = run_gemm(h, ws.mid, w.output_kernel, ws.pre, w.output_bias, ws.y, m_dev, rows, H, F,
-                     BT_EPI_BIAS_RESIDUAL, 0, stream)) != BT_OK)
+  if ((rc = run_gemm(h, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias, ws.y, m_dev, rows, H, F,
+                     BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
     return rc;
   if (restore_to != nullptr)
-    e = launch_layernorm_restore(ws.pre, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32,
+    e = launch_layernorm_restore(ws.pre, true, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32,
                                  restore_to, batch_idx, B, S_or_maxlen, H, h->cfg.ln_eps, stream);
   else
-    e = launch_layernorm(ws.pre, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, x_out,
+    e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, x_out,
                          m_dev, rows, H, h->cfg.ln_eps, stream);
   if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
   return BT_OK;
@@ -443,9 +444,9 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
   if (!A || !W || !out) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (m_rows <= 0 || N <= 0 || K <= 0 || N % 64 != 0 || K % 64 != 0)
     return fail(h, BT_ERR_INVALID_ARG, "bt_gemm needs m_rows > 0, N % 64 == 0, K % 64 == 0");
-  if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
+  if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL_F32OUT) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
   if (epilogue != BT_EPI_NONE && !bias) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs bias");
-  if (epilogue == BT_EPI_BIAS_RESIDUAL && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
+  if ((epilogue == BT_EPI_BIAS_RESIDUAL || epilogue == BT_EPI_BIAS_RESIDUAL_F32OUT) && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
   return run_gemm(h, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
                   reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, epilogue, gelu_kind,
                   reinterpret_cast<cudaStream_t>(stream));
@@ -460,19 +461,19 @@ int bt_attention(bt_handle h, const void* qkv, void* ctx, const int* batch_idx, 
                  max_len, rows_allocated, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int bt_add_bias_residual_layernorm(const void* x, const void* bias, const void* residual, const void* gamma,
+int bt_add_bias_residual_layernorm(const void* x, int x_fp32, const void* bias, const void* residual, const void* gamma,
                                    const void* beta, int gamma_beta_fp32, void* out, const int* m_dev, int m_rows,
                                    int hidden, float eps, void* stream) {
   if (!x || !gamma || !beta || !out || m_rows <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 1024)
     return BT_ERR_INVALID_ARG;
-  cudaError_t e = launch_layernorm(reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(bias),
+  cudaError_t e = launch_layernorm(x, x_fp32 != 0, reinterpret_cast<const __half*>(bias),
                                    reinterpret_cast<const __half*>(residual), gamma, beta, gamma_beta_fp32 != 0,
                                    reinterpret_cast<__half*>(out), m_dev, m_rows, hidden, eps,
                                    reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
 }
 
-int bt_add_bias_residual_layernorm_restore(const void* x, const void* bias, const void* residual, const void* gamma,
+int bt_add_bias_residual_layernorm_restore(const void* x, int x_fp32, const void* bias, const void* residual, const void* gamma,
                                            const void* beta, int gamma_beta_fp32, void* out_padded,
                                            const int* batch_idx, int batch_size, int seq_len, int hidden, float eps,
                                            void* stream) {
@@ -480,7 +481,7 @@ int bt_add_bias_residual_layernorm_restore(const void* x, const void* bias, cons
       hidden % 8 != 0 || hidden > 1024)
     return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_layernorm_restore(
-      reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(bias),
+      x, x_fp32 != 0, reinterpret_cast<const __half*>(bias),
       reinterpret_cast<const __half*>(residual), gamma, beta, gamma_beta_fp32 != 0,
       reinterpret_cast<__half*>(out_padded), batch_idx, batch_size, seq_len, hidden, eps,
       reinterpret_cast<cudaStream_t>(stream));

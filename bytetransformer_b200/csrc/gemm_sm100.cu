@@ -238,7 +238,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
         if (row_ok) {
           const size_t off = static_cast<size_t>(row) * args.N + gcol;
-          if (EPI == BT_EPI_BIAS_RESIDUAL) {
+          if (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) {
             const uint4* rp = reinterpret_cast<const uint4*>(args.residual + off);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -252,15 +252,21 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
               }
             }
           }
-          uint4* op = reinterpret_cast<uint4*>(args.out + off);
+          if (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) {
+            float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + off);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
-            o.y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
-            o.z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
-            o.w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
-            op[q] = o;
+            for (int q = 0; q < 8; ++q) op[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+            uint4* op = reinterpret_cast<uint4*>(args.out + off);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
+              op[q] = o;
+            }
           }
         }
       }
@@ -311,6 +317,7 @@ cudaError_t launch_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
     case BT_EPI_BIAS: return launch_one<BLOCK_N, BT_EPI_BIAS>(g, a, stream);
     case BT_EPI_BIAS_GELU: return launch_one<BLOCK_N, BT_EPI_BIAS_GELU>(g, a, stream);
     case BT_EPI_BIAS_RESIDUAL: return launch_one<BLOCK_N, BT_EPI_BIAS_RESIDUAL>(g, a, stream);
+    case BT_EPI_BIAS_RESIDUAL_F32OUT: return launch_one<BLOCK_N, BT_EPI_BIAS_RESIDUAL_F32OUT>(g, a, stream);
     default: return cudaErrorInvalidValue;
   }
 }

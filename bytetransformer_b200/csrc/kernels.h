@@ -60,10 +60,10 @@ struct MhaLaunch {
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
 
 // ---- element-wise / normalisation -------------------------------------------
-cudaError_t launch_layernorm(const __half* x, const __half* bias, const __half* residual, const void* gamma,
+cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, const __half* residual, const void* gamma,
                              const void* beta, bool gb_fp32, __half* out, const int* m_dev, int m_rows,
                              int hidden, float eps, cudaStream_t stream);
-cudaError_t launch_layernorm_restore(const __half* x, const __half* bias, const __half* residual,
+cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                                      const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
                                      const int* batch_idx, int B, int S, int hidden, float eps,
                                      cudaStream_t stream);

@@ -182,7 +182,8 @@ class Encoder:
         _check(w, "w", torch.float16)
         M, K = a.shape
         N = w.shape[1]
-        out = torch.zeros(M, N, dtype=torch.float16, device=a.device)
+        odt = torch.float32 if epilogue == _abi.BT_EPI_BIAS_RESIDUAL_F32OUT else torch.float16
+        out = torch.zeros(M, N, dtype=odt, device=a.device)
         self._call("bt_gemm", self._h, a.data_ptr(), w.data_ptr(), out.data_ptr(),
                    bias.data_ptr() if bias is not None else None,
                    residual.data_ptr() if residual is not None else None,
@@ -243,9 +244,9 @@ def restore_rows(x_packed: torch.Tensor, batch_idx: torch.Tensor, B: int, S: int
 def add_bias_residual_layernorm(x, bias, residual, gamma, beta, eps=1e-6, m_dev=None):
     lib = _abi.load()
     M, H = x.shape
-    out = torch.zeros_like(x)
+    out = torch.zeros(M, H, dtype=torch.float16, device=x.device)
     rc = lib.bt_add_bias_residual_layernorm(
-        x.data_ptr(), bias.data_ptr() if bias is not None else None,
+        x.data_ptr(), int(x.dtype == torch.float32), bias.data_ptr() if bias is not None else None,
         residual.data_ptr() if residual is not None else None, gamma.data_ptr(), beta.data_ptr(),
         int(gamma.dtype == torch.float32), out.data_ptr(), m_dev.data_ptr() if m_dev is not None else None,
         M, H, float(eps), _stream_ptr(x.device))
@@ -259,7 +260,7 @@ def add_bias_residual_layernorm_restore(x, bias, residual, gamma, beta, batch_id
     H = x.shape[1]
     out = torch.full((B, S, H), float("nan"), dtype=torch.float16, device=x.device)
     rc = lib.bt_add_bias_residual_layernorm_restore(
-        x.data_ptr(), bias.data_ptr() if bias is not None else None,
+        x.data_ptr(), int(x.dtype == torch.float32), bias.data_ptr() if bias is not None else None,
         residual.data_ptr() if residual is not None else None, gamma.data_ptr(), beta.data_ptr(),
         int(gamma.dtype == torch.float32), out.data_ptr(), batch_idx.data_ptr(), B, S, H, float(eps),
         _stream_ptr(x.device))

@@ -44,6 +44,7 @@ extern "C" {
 #define BT_EPI_BIAS 1          /* out = A*W + bias                  */
 #define BT_EPI_BIAS_GELU 2     /* out = gelu(A*W + bias)            */
 #define BT_EPI_BIAS_RESIDUAL 3 /* out = A*W + bias + residual       */
+#define BT_EPI_BIAS_RESIDUAL_F32OUT 4 /* same, but `out` is float[M,N]: the pre-LayerNorm sum keeps fp32 */
 
 typedef struct bt_encoder_s* bt_handle;
 
@@ -168,8 +169,10 @@ int bt_attention(bt_handle h, const void* qkv, void* ctx, const int* batch_idx, 
 
 /* `add_bias_input_layernorm_kernel_launcher` (layernorm.h:410-428):
  * out = LN(x + bias + residual) * gamma + beta over rows [0, min(*m_dev, m_rows)).
- * bias and residual may be NULL (treated as zero).  hidden % 8 == 0, <= 8192. */
-int bt_add_bias_residual_layernorm(const void* x, const void* bias, const void* residual,
+ * bias and residual may be NULL (treated as zero).  x is half[rows,hidden], or
+ * float[rows,hidden] when x_fp32 != 0 (the output of a BT_EPI_BIAS_RESIDUAL_F32OUT
+ * GEMM).  hidden % 8 == 0, <= 1024. */
+int bt_add_bias_residual_layernorm(const void* x, int x_fp32, const void* bias, const void* residual,
                                    const void* gamma, const void* beta, int gamma_beta_fp32,
                                    void* out, const int* m_dev, int m_rows, int hidden, float eps,
                                    void* stream);
@@ -177,7 +180,7 @@ int bt_add_bias_residual_layernorm(const void* x, const void* bias, const void* 
 /* `add_bias_input_layernorm_restore_output_kernel_launcher` (layernorm.h:430-446):
  * same LayerNorm, but row (b,i) of the padded output takes packed row
  * batch_idx[b]+i, and rows i >= len_b are written as zeros. */
-int bt_add_bias_residual_layernorm_restore(const void* x, const void* bias, const void* residual,
+int bt_add_bias_residual_layernorm_restore(const void* x, int x_fp32, const void* bias, const void* residual,
                                            const void* gamma, const void* beta,
                                            int gamma_beta_fp32, void* out_padded,
                                            const int* batch_idx, int batch_size, int seq_len,

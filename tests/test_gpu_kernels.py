@@ -265,3 +265,26 @@ def test_attention_twice_bit_identical(enc, cuda_device):
     a = enc.attention(qkv, cu, 300)
     b = enc.attention(qkv, cu, 300)
     assert torch.equal(a, b)
+
+
+def test_gemm_fp32_out_feeds_layernorm(enc, cuda_device):
+    """The attention-output / FFN2 GEMMs keep the pre-LayerNorm sum in fp32
+    (BT_EPI_BIAS_RESIDUAL_F32OUT) and the LayerNorm kernel reads it as float."""
+    from bytetransformer_b200 import _abi
+    from bytetransformer_b200.encoder import add_bias_residual_layernorm
+    g = torch.Generator().manual_seed(21)
+    M, N, K = 333, 768, 768
+    a = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(K, N, generator=g) * 0.05).half()
+    bias = torch.empty(N).uniform_(-0.4, 0.4, generator=g).half()
+    res = torch.randn(M, N, generator=g).half()
+    gamma = torch.empty(N).uniform_(0.5, 1.5, generator=g).half()
+    beta = torch.empty(N).uniform_(-0.4, 0.4, generator=g).half()
+    pre = enc.gemm(a.to(cuda_device), w.to(cuda_device), bias.to(cuda_device), res.to(cuda_device),
+                   epilogue=_abi.BT_EPI_BIAS_RESIDUAL_F32OUT)
+    assert pre.dtype == torch.float32
+    want_pre = a.float() @ w.float() + bias.float() + res.float()
+    assert (pre.cpu() - want_pre).abs().max().item() < 2e-4
+    out = add_bias_residual_layernorm(pre, None, None, gamma.to(cuda_device), beta.to(cuda_device), eps=1e-6)
+    want = torch.nn.functional.layer_norm(want_pre, (N,), gamma.float(), beta.float(), eps=1e-6)
+    assert_close_fp16(out, want, "gemm->ln", max_abs=3e-3, mean_abs=3e-4)
