@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the padding-free BERT encoder path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1..8): the whole-box configuration — BERT-base, 12 layers, 1024
+sequences of max_seq 1024 with seeded lengths uniform in [16,1024] (about 556k
+valid tokens), split over the N GPUs by packed-token cost (LPT), every GPU
+holding a full weight replica; no collective on the data path.  One "step" is
+one pass over all 1024 sequences.  Total work is fixed as N grows ("strong").
+
+Printed JSON line (rank 0): `value` = valid tokens/s with inputs resident in
+HBM; `e2e` = the same through the public packed-forward call with pinned HOST
+buffers (H2D + compute + D2H inside the timed region); `roofline` = the GEMM
+kernel's achieved algorithmic TFLOP/s from CUDA events around every GEMM launch
+of the timed region against the measured dense bf16/fp16 peak; `cpu_baseline`
+= the CPU oracle (the reference's fp32 PyTorch encoder restated) on a bounded
+sample.  `--impl reference` times that CPU encoder alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bert_base_12L_packed_tokens_per_sec"
+UNIT = "tokens/s"
+WORKLOAD = "whole_box_1024x1024"
+WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
+
+
+# ----------------------------------------------------------------------------- peaks
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"tflops": float(d.get("bf16_tflops_sustained", d.get("bf16_tflops"))),
+                "tflops_burst": float(d.get("bf16_tflops")), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            sel = str(device_index)
+        self.cmd = ["nvidia-smi", "-i", sel, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"]
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU oracle timing
+def cpu_oracle_tokens_per_sec(lengths, target_seconds=12.0, reps=1):
+    """Times the CPU oracle (fp32 PyTorch encoder, 12 layers) on the first sequences of
+    the workload until about `target_seconds` of work; returns (tokens/s, sample text, cores)."""
+    from oracle.bert_oracle import encoder_stack_packed
+    from bytetransformer_b200.workloads import BERT_BASE, make_weights
+    layers = [[t.float() for t in w] for w in make_weights(BERT_BASE, seed=7)]
+    cores = torch.get_num_threads()
+    g = torch.Generator().manual_seed(3)
+    # probe: one sequence
+    order = list(range(len(lengths)))
+    probe_len = int(lengths[order[0]])
+    x = torch.randn(probe_len, BERT_BASE.hidden, generator=g)
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        encoder_stack_packed(x, [0, probe_len], layers, BERT_BASE.head_num, 64, ln_eps=1e-6)
+        dt = time.perf_counter() - t0
+    rate = probe_len / dt
+    n_tok_target = max(probe_len, int(rate * target_seconds))
+    ids, tok = [], 0
+    for i in order:
+        if tok + int(lengths[i]) > n_tok_target and ids:
+            break
+        ids.append(i)
+        tok += int(lengths[i])
+    cu = np.concatenate([[0], np.cumsum([int(lengths[i]) for i in ids])]).tolist()
+    x = torch.randn(tok, BERT_BASE.hidden, generator=g)
+    best = None
+    with torch.no_grad():
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            encoder_stack_packed(x, cu, layers, BERT_BASE.head_num, 64, ln_eps=1e-6)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+    sample = f"first {len(ids)} sequences ({tok} tokens) of the workload, 12 layers, fp32, {best:.2f} s"
+    return tok / best, sample, cores, tok, best
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from bytetransformer_b200.workloads import lengths_for
+    lengths = lengths_for(WORKLOAD)
+    cores = torch.get_num_threads()
+    # every step is a bounded sample (about 6 s of CPU work)
+    per_step = []
+    sample = ""
+    tok = 0
+    for i in range(args.warmup + args.steps):
+        tps, sample, cores, tok, dt = cpu_oracle_tokens_per_sec(lengths, target_seconds=6.0)
+        if i >= args.warmup:
+            per_step.append((tok, dt))
+    tot_tok = sum(t for t, _ in per_step)
+    tot_dt = sum(d for _, d in per_step)
+    value = tot_tok / tot_dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * tot_dt / max(1, len(per_step)),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "desc": WORKLOAD_DESC, "sample_per_step": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------- our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-kernel-events", action="store_true", help="do not bracket kernels with events in the timed region")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--token-budget", type=int, default=0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the encoder path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        dist = dist_mod
+    n_gpus = world
+
+    from bytetransformer_b200.encoder import Encoder
+    from bytetransformer_b200.runner import DEFAULT_TOKEN_BUDGET, PackedRunner
+    from bytetransformer_b200.sharding import lpt_shards
+    from bytetransformer_b200.workloads import (BERT_BASE, attention_flops_per_layer, gemm_flops_per_layer,
+                                                lengths_for, make_weights)
+
+    lengths = lengths_for(WORKLOAD)
+    total_tokens = int(lengths.sum())
+    shards = lpt_shards(lengths, n_gpus, BERT_BASE.hidden)
+    mine = shards[rank]
+    enc = Encoder(BERT_BASE.head_num, 64, make_weights(BERT_BASE, seed=7, device=dev), ln_eps=1e-6, gelu="erf")
+    budget = args.token_budget or DEFAULT_TOKEN_BUDGET
+    runner = PackedRunner(enc, lengths, mine, token_budget=budget)
+    xs, outs = runner.make_device_inputs(seed=rank)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        runner.run_device(xs, outs)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    enc.profile_enable(True)
+    if args.no_kernel_events:
+        enc.profile_enable(False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        runner.run_device(xs, outs)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    prof = enc.profile_read()
+    enc.profile_enable(False)
+    if enc.device_status() != 0:
+        raise SystemExit("a kernel reported a device-side error status")
+    ms_per_step = ms_total / args.steps
+    value = total_tokens / (ms_per_step / 1000.0)
+
+    # ---- end to end from pinned host memory ------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        xh, oh = runner.make_host_inputs(seed=100 + rank)
+        h2d = d2h = 0
+        for _ in range(max(args.warmup, 3)):
+            h2d, d2h = runner.run_host(xh, oh)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            h2d, d2h = runner.run_host(xh, oh)
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+        if dist is not None:
+            t = torch.tensor([h2d, d2h], dtype=torch.float64, device=dev)
+            dist.all_reduce(t)
+            h2d, d2h = int(t[0].item()), int(t[1].item())
+        e2e = {"value": total_tokens / (ms_e2e / 1000.0), "unit": UNIT, "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+
+    # ---- roofline of the dominant kernel (the GEMM), rank 0's launches -----------------
+    peaks = measured_peaks()
+    my_lengths = lengths[mine]
+    my_tokens = int(my_lengths.sum())
+    gemm_kinds = ("gemm_qkv", "gemm_attn_out", "gemm_ffn1", "gemm_ffn2")
+    gemm_ms = sum(prof[k][0] for k in gemm_kinds)
+    gemm_launches = sum(prof[k][1] for k in gemm_kinds)
+    gemm_flops = args.steps * BERT_BASE.layers * gemm_flops_per_layer(my_tokens, BERT_BASE.hidden)
+    roofline = None
+    kernels = {}
+    if not args.no_kernel_events and gemm_ms > 0:
+        achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "gemm_dram_traffic.json")
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+        roofline = {"bound": "tensor", "kernel": "gemm_f16_kernel (4 shapes per layer)", "achieved": achieved,
+                    "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                    "peak_source": peaks["source"] + " sustained bf16 dense", "traffic": traffic,
+                    "launches": int(gemm_launches), "avg_launch_ms": gemm_ms / max(1, gemm_launches)}
+        shape_flops = {"gemm_qkv": 6.0, "gemm_attn_out": 2.0, "gemm_ffn1": 8.0, "gemm_ffn2": 8.0}
+        for k in gemm_kinds:
+            fl = args.steps * BERT_BASE.layers * shape_flops[k] * my_tokens * BERT_BASE.hidden ** 2
+            kernels[k] = {"ms": prof[k][0], "launches": int(prof[k][1]),
+                          "tflops": fl / (prof[k][0] / 1000.0) / 1e12 if prof[k][0] > 0 else None}
+        afl = args.steps * BERT_BASE.layers * attention_flops_per_layer(my_lengths, BERT_BASE.hidden)
+        kernels["mha"] = {"ms": prof["mha"][0], "launches": int(prof["mha"][1]),
+                          "tflops": afl / (prof["mha"][0] / 1000.0) / 1e12 if prof["mha"][0] > 0 else None}
+        ln_bytes = args.steps * BERT_BASE.layers * 2 * my_tokens * BERT_BASE.hidden * 6.0  # fp32 in, fp16 out
+        kernels["layernorm"] = {"ms": prof["layernorm"][0], "launches": int(prof["layernorm"][1]),
+                                "gbs": ln_bytes / (prof["layernorm"][0] / 1000.0) / 1e9 if prof["layernorm"][0] > 0 else None,
+                                "hbm_peak_gbs": peaks["hbm_gbs"]}
+    launches = int(sum(v[1] for v in prof.values()))
+    if dist is not None:
+        t = torch.tensor([launches], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        launches = int(t.item())
+
+    # ---- CPU baseline (rank 0, N = 1 only) ---------------------------------------------
+    cpu = None
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        tps, sample, cores, _, _ = cpu_oracle_tokens_per_sec(lengths, target_seconds=12.0)
+        cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "desc": WORKLOAD_DESC, "total_tokens": total_tokens,
+                       "micro_batch_token_budget": budget, "micro_batches_rank0": len(runner.batches),
+                       "l2": "inputs larger than L2 (>= 100 MB of activations per GPU per step)",
+                       "kernel_events_in_timed_region": not args.no_kernel_events},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
+            "kernels": kernels,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

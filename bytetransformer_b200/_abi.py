@@ -68,7 +68,11 @@ SIGNATURES = {
     "bt_add_bias_residual_layernorm_restore": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp]),
     "bt_add_bias_gelu": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_masked_softmax": (_i, [_vp, _vp, _i, _i, _i, _f, _vp]),
+    "bt_profile_enable": (_i, [_vp, _i]),
+    "bt_profile_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_longlong)]),
 }
+PROF_KINDS = ("offsets", "pack", "gemm_qkv", "mha", "gemm_attn_out", "layernorm", "gemm_ffn1", "gemm_ffn2",
+              "gemm_other")
 
 _lib = None
 

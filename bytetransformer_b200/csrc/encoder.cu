@@ -97,6 +97,23 @@ struct bt_encoder_s {
   std::vector<std::pair<bt::TmapKey, CUtensorMap>> tmaps;
   size_t tmap_next = 0;
 
+  // launch accounting / optional per-kernel event timing (bt_profile_*)
+  long long launches[BT_PROF_KINDS] = {};
+  bool prof_on = false;
+  std::vector<cudaEvent_t> ev_pool;
+  size_t ev_used = 0;
+  struct Span { int kind; cudaEvent_t beg, end; };
+  std::vector<Span> spans;
+
+  cudaEvent_t take_event() {
+    if (ev_used == ev_pool.size()) {
+      cudaEvent_t e = nullptr;
+      if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+      ev_pool.push_back(e);
+    }
+    return ev_pool[ev_used++];
+  }
+
   const CUtensorMap* tmap(const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
     bt::TmapKey k{base, rows, cols, box_cols, box_rows};
     for (auto& e : tmaps)
@@ -116,6 +133,32 @@ struct bt_encoder_s {
 };
 
 namespace bt {
+
+// Counts one launch of `kind`; with profiling on, brackets it with two events on
+// the launching stream.
+struct LaunchScope {
+  bt_handle h;
+  cudaStream_t stream;
+  cudaEvent_t end = nullptr;
+  int kind;
+  LaunchScope(bt_handle h_, int kind_, cudaStream_t s) : h(h_), stream(s), kind(kind_) {
+    if (!h) return;
+    h->launches[kind]++;
+    if (h->prof_on) {
+      cudaEvent_t beg = h->take_event();
+      end = h->take_event();
+      if (beg && end) {
+        cudaEventRecord(beg, stream);
+        h->spans.push_back({kind, beg, end});
+      } else {
+        end = nullptr;
+      }
+    }
+  }
+  ~LaunchScope() {
+    if (end) cudaEventRecord(end, stream);
+  }
+};
 
 static int fail(bt_handle h, int code, const char* msg) {
   if (h) h->err = msg;
@@ -160,8 +203,9 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   return w;
 }
 
-static int run_gemm(bt_handle h, const __half* A, const void* W, __half* out, const void* bias, const __half* residual,
-                    const int* m_dev, int m_rows, int N, int K, int epi, int gelu_kind, cudaStream_t stream) {
+static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __half* out, const void* bias,
+                    const __half* residual, const int* m_dev, int m_rows, int N, int K, int epi, int gelu_kind,
+                    cudaStream_t stream) {
   const CUtensorMap* ta = h->tmap(A, m_rows, K, 64, 128);
   const CUtensorMap* tb = h->tmap(W, K, N, 64, 64);
   if (!ta || !tb) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
@@ -180,7 +224,11 @@ static int run_gemm(bt_handle h, const __half* A, const void* W, __half* out, co
   g.block_n = 0;
   g.status = h->status;
   g.num_sms = h->num_sms;
-  cudaError_t e = launch_gemm(g, stream);
+  cudaError_t e;
+  {
+    LaunchScope scope(h, kind, stream);
+    e = launch_gemm(g, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(h, e, "gemm launch");
   return BT_OK;
 }
@@ -199,7 +247,11 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   a.hidden = h->hidden;
   a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(h->cfg.size_per_head)) / h->cfg.tao;
   a.status = h->status;
-  cudaError_t e = launch_mha(a, stream);
+  cudaError_t e;
+  {
+    LaunchScope scope(h, BT_PROF_MHA, stream);
+    e = launch_mha(a, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(h, e, "attention launch");
   return BT_OK;
 }
@@ -216,22 +268,27 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
   const int* m_dev = batch_idx + B;
   const bool gb32 = h->cfg.gamma_beta_fp32 != 0;
   int rc;
-  if ((rc = run_gemm(h, x_in, w.qkv_kernel, ws.qkv, w.qkv_bias, nullptr, m_dev, rows, 3 * H, H, BT_EPI_BIAS, 0,
+  if ((rc = run_gemm(h, BT_PROF_GEMM_QKV, x_in, w.qkv_kernel, ws.qkv, w.qkv_bias, nullptr, m_dev, rows, 3 * H, H, BT_EPI_BIAS, 0,
                      stream)) != BT_OK)
     return rc;
   if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream)) != BT_OK) return rc;
-  if ((rc = run_gemm(h, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre), w.attr_output_bias, x_in, m_dev, rows, H,
+  if ((rc = run_gemm(h, BT_PROF_GEMM_ATTN_OUT, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre), w.attr_output_bias, x_in, m_dev, rows, H,
                      H, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
     return rc;
-  cudaError_t e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.attr_output_layernorm_gamma,
-                                   w.attr_output_layernorm_beta, gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream);
+  cudaError_t e;
+  {
+    LaunchScope scope(h, BT_PROF_LAYERNORM, stream);
+    e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta,
+                         gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
-  if ((rc = run_gemm(h, ws.y, w.inter_kernel, ws.mid, w.inter_bias, nullptr, m_dev, rows, F, H, BT_EPI_BIAS_GELU,
+  if ((rc = run_gemm(h, BT_PROF_GEMM_FFN1, ws.y, w.inter_kernel, ws.mid, w.inter_bias, nullptr, m_dev, rows, F, H, BT_EPI_BIAS_GELU,
                      h->cfg.gelu_kind, stream)) != BT_OK)
     return rc;
-  if ((rc = run_gemm(h, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias, ws.y, m_dev, rows, H, F,
+  if ((rc = run_gemm(h, BT_PROF_GEMM_FFN2, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias, ws.y, m_dev, rows, H, F,
                      BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
     return rc;
+  LaunchScope scope(h, BT_PROF_LAYERNORM, stream);
   if (restore_to != nullptr)
     e = launch_layernorm_restore(ws.pre, true, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32,
                                  restore_to, batch_idx, B, S_or_maxlen, H, h->cfg.ln_eps, stream);
@@ -264,9 +321,16 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
   void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
   Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
 
-  cudaError_t e = launch_build_offsets(reinterpret_cast<const __half*>(mask), B, S, ws.batch_idx, ws.word_idx, stream);
+  cudaError_t e;
+  {
+    LaunchScope scope(h, BT_PROF_OFFSETS, stream);
+    e = launch_build_offsets(reinterpret_cast<const __half*>(mask), B, S, ws.batch_idx, ws.word_idx, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(h, e, "offsets launch");
-  e = launch_pack_rows(reinterpret_cast<const __half*>(input), ws.xa, ws.batch_idx, B, S, h->hidden, stream);
+  {
+    LaunchScope scope(h, BT_PROF_PACK, stream);
+    e = launch_pack_rows(reinterpret_cast<const __half*>(input), ws.xa, ws.batch_idx, B, S, h->hidden, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(h, e, "pack launch");
   __half* cur = ws.xa;
   __half* nxt = ws.xb;
@@ -322,6 +386,8 @@ int bt_create(const bt_config* cfg, bt_handle* out) {
 }
 
 int bt_destroy(bt_handle h) {
+  if (h)
+    for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
   delete h;
   return BT_OK;
 }
@@ -353,6 +419,33 @@ int bt_workspace_bytes_packed(bt_handle h, int batch_size, int total_tokens, siz
   if (!h || !bytes) return BT_ERR_INVALID_ARG;
   if (batch_size <= 0 || total_tokens <= 0) return fail(h, BT_ERR_INVALID_ARG, "batch_size and total_tokens must be positive");
   *bytes = carve(nullptr, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0).bytes;
+  return BT_OK;
+}
+
+int bt_profile_enable(bt_handle h, int on) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  h->prof_on = on != 0;
+  if (on) {
+    h->spans.clear();
+    h->ev_used = 0;
+    for (int i = 0; i < BT_PROF_KINDS; ++i) h->launches[i] = 0;
+  }
+  return BT_OK;
+}
+
+int bt_profile_read(bt_handle h, double* ms_by_kind, long long* launches_by_kind) {
+  if (!h || !ms_by_kind || !launches_by_kind) return BT_ERR_INVALID_ARG;
+  for (int i = 0; i < BT_PROF_KINDS; ++i) {
+    ms_by_kind[i] = 0.0;
+    launches_by_kind[i] = h->launches[i];
+  }
+  for (const auto& sp : h->spans) {
+    cudaError_t e = cudaEventSynchronize(sp.end);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, sp.beg, sp.end);
+    if (e != cudaSuccess) return fail_cuda(h, e, "bt_profile_read");
+    ms_by_kind[sp.kind] += ms;
+  }
   return BT_OK;
 }
 
@@ -447,7 +540,7 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
   if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL_F32OUT) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
   if (epilogue != BT_EPI_NONE && !bias) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs bias");
   if ((epilogue == BT_EPI_BIAS_RESIDUAL || epilogue == BT_EPI_BIAS_RESIDUAL_F32OUT) && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
-  return run_gemm(h, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
+  return run_gemm(h, BT_PROF_GEMM_OTHER, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
                   reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, epilogue, gelu_kind,
                   reinterpret_cast<cudaStream_t>(stream));
 }

@@ -113,6 +113,17 @@ class Encoder:
         self._call("bt_device_status", self._h, _stream_ptr(self.device), C.byref(st))
         return st.value
 
+    def profile_enable(self, on: bool = True):
+        self._call("bt_profile_enable", self._h, int(bool(on)))
+
+    def profile_read(self):
+        """{kind: (milliseconds, launches)} since the last profile_enable(True)."""
+        n = len(_abi.PROF_KINDS)
+        ms = (C.c_double * n)()
+        cnt = (C.c_longlong * n)()
+        self._call("bt_profile_read", self._h, ms, cnt)
+        return {k: (ms[i], cnt[i]) for i, k in enumerate(_abi.PROF_KINDS)}
+
     # ----------------------------------------------------------------- forwards
     def _check_io(self, x, attr_mask):
         _check(x, "input", torch.float16)

@@ -199,6 +199,27 @@ int bt_add_bias_gelu(void* x, const void* bias, const int* m_dev, int m_rows, in
 int bt_masked_softmax(void* logits, const void* attr_mask, int batch_size, int head_num, int seq_len,
                       float scale, void* stream);
 
+/* ---- launch accounting and per-kernel timing ------------------------------ */
+/* Kernel kinds of the arrays below (one slot per kind, BT_PROF_KINDS slots). */
+#define BT_PROF_OFFSETS 0
+#define BT_PROF_PACK 1
+#define BT_PROF_GEMM_QKV 2
+#define BT_PROF_MHA 3
+#define BT_PROF_GEMM_ATTN_OUT 4
+#define BT_PROF_LAYERNORM 5
+#define BT_PROF_GEMM_FFN1 6
+#define BT_PROF_GEMM_FFN2 7
+#define BT_PROF_GEMM_OTHER 8
+#define BT_PROF_KINDS 9
+/* on != 0: reset the counters and bracket every kernel the handle launches with
+ * CUDA events on the launching stream; on == 0: stop timing (counting goes on).
+ * Replaces the reference's unused timing events (src/bert_transformer.cu:89-93). */
+int bt_profile_enable(bt_handle h, int on);
+/* Waits for the recorded events and returns, per kind, the summed kernel time in
+ * milliseconds and the number of launches since the last bt_profile_enable(h, 1)
+ * (or since bt_create).  Both arrays have BT_PROF_KINDS entries. */
+int bt_profile_read(bt_handle h, double* ms_by_kind, long long* launches_by_kind);
+
 /* Library build information, e.g. "bt_b200 sm_100a". */
 const char* bt_version(void);
 

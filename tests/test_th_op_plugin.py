@@ -1,0 +1,99 @@
+"""The PyTorch plugin (libths_bytetransformer.so): schema on CPU, behaviour on GPU."""
+import io
+import os
+
+import pytest
+import torch
+
+from helpers import assert_close_fp16, fp16_round, make_layer_weights, to_device_weights
+
+EXPECTED_SCHEMA = (
+    "ByteTransformer::BertTransformer(int head_num, int head_size, Tensor qkv_kernel, Tensor qkv_bias, "
+    "Tensor attr_output_kernel, Tensor attr_output_bias, Tensor attr_output_layernorm_gamma, "
+    "Tensor attr_output_layernorm_beta, Tensor inter_kernel, Tensor inter_bias, Tensor output_kernel, "
+    "Tensor output_bias, Tensor output_layernorm_gamma, Tensor output_layernorm_beta, Tensor input, "
+    "Tensor attr_mask, bool is_remove_padding=True, bool use_fused_attention=True) -> Tensor")
+
+
+@pytest.fixture(scope="module")
+def plugin():
+    from bytetransformer_b200 import build
+    path = build.build_th_op()
+    torch.ops.load_library(path)
+    return path
+
+
+def test_operator_schema_matches_reference(plugin):
+    """Same schema string as the reference registers (th_op/ths_op_f.cc:85-95)."""
+    schemas = torch._C._jit_get_schemas_for_operator("ByteTransformer::BertTransformer")
+    assert len(schemas) == 1 and str(schemas[0]) == EXPECTED_SCHEMA
+
+
+def test_custom_class_registered(plugin):
+    cls = torch.classes.ByteTransformer.BertTransformer
+    assert cls is not None
+
+
+def test_cpu_tensors_are_rejected(plugin):
+    g = torch.Generator().manual_seed(0)
+    w = [t.half() for t in make_layer_weights(64, g)]
+    x = torch.zeros(1, 4, 64, dtype=torch.float16)
+    m = torch.ones(1, 4, 4, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        torch.ops.ByteTransformer.BertTransformer(1, 64, *w, x, m, True, True)
+
+
+@pytest.mark.gpu
+def test_functional_op_and_class_on_gpu(plugin, cuda_device):
+    from oracle.bert_oracle import build_attr_mask, encoder_layer
+    g = torch.Generator().manual_seed(31)
+    nh, H, B, S = 12, 768, 5, 80
+    w = make_layer_weights(H, g, recipe="normal")
+    lens = torch.tensor([80, 3, 0, 64, 17])
+    x = torch.randn(B, S, H, generator=g).half()
+    mask = build_attr_mask(lens, S, torch.float16)
+    want = encoder_layer(x.float(), mask.float(), fp16_round(w), nh, 64, ln_eps=1e-6, gelu_kind="erf")
+    wd = to_device_weights(w, cuda_device)
+    got = torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd, x.to(cuda_device), mask.to(cuda_device), True, True)
+    valid = torch.arange(S)[None, :] < lens[:, None]
+    assert_close_fp16(got.cpu()[valid], want[valid], "th_op functional")
+    assert (got.cpu()[~valid] == 0).all()
+
+    obj = torch.classes.ByteTransformer.BertTransformer(nh, 64, *wd)
+    got2 = obj.forward(x.to(cuda_device), mask.to(cuda_device))
+    assert torch.equal(got2, got)
+    got3 = obj.forwardv2(x.to(cuda_device), mask.to(cuda_device), False, False)
+    assert torch.equal(got3, got)
+
+    # fp32 LayerNorm gamma/beta (use_fp32 of the reference) are accepted
+    wd32 = to_device_weights(w, cuda_device, gb_fp32=True)
+    got4 = torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd32, x.to(cuda_device), mask.to(cuda_device), True, True)
+    assert_close_fp16(got4.cpu()[valid], want[valid], "th_op fp32 gamma/beta")
+
+    with pytest.raises(RuntimeError):
+        torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd, x.float().to(cuda_device), mask.to(cuda_device), True, True)
+
+
+@pytest.mark.gpu
+def test_torchscript_pickle_round_trip(plugin, cuda_device):
+    """Scripted module holding the custom class saves and loads (12 tensors + head info)."""
+    g = torch.Generator().manual_seed(32)
+    nh, H = 2, 128
+    wd = to_device_weights(make_layer_weights(H, g), cuda_device)
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.enc = torch.classes.ByteTransformer.BertTransformer(nh, 64, *wd)
+
+        def forward(self, x, m):
+            return self.enc.forward(x, m)
+
+    sm = torch.jit.script(M())
+    buf = io.BytesIO()
+    torch.jit.save(sm, buf)
+    buf.seek(0)
+    sm2 = torch.jit.load(buf)
+    x = torch.randn(2, 16, H, generator=g).half().to(cuda_device)
+    m = torch.ones(2, 16, 16, dtype=torch.float16, device=cuda_device)
+    assert torch.equal(sm(x, m), sm2(x, m))
