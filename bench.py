@@ -186,6 +186,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--token-budget", type=int, default=0)
+    ap.add_argument("--max-seqs", type=int, default=0,
+                    help="profiling aid: keep only the first N sequences of the workload (small ncu captures)")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only the first L layers")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -212,6 +215,10 @@ def main():
                                                 lengths_for, make_weights)
 
     lengths = lengths_for(WORKLOAD)
+    if args.max_seqs > 0:
+        lengths = lengths[:args.max_seqs]
+    if args.layers > 0:
+        BERT_BASE.layers = args.layers
     total_tokens = int(lengths.sum())
     shards = lpt_shards(lengths, n_gpus, BERT_BASE.hidden)
     mine = shards[rank]
@@ -240,9 +247,8 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    enc.profile_enable(True)
-    if args.no_kernel_events:
-        enc.profile_enable(False)
+    enc.profile_enable(True)     # resets the launch counters ...
+    enc.profile_enable(False)    # ... without bracketing kernels: the headline region runs undisturbed
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -251,9 +257,24 @@ def main():
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launch_counts = enc.profile_read()
+    # The same K steps once more with CUDA events around every kernel launch (on the
+    # launching stream): per-kernel durations for the roofline.  The brackets cost a
+    # few percent of step time, which is why the headline value is not taken here.
+    ms_events_region = None
+    prof = launch_counts
+    if not args.no_kernel_events:
+        enc.profile_enable(True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            runner.run_device(xs, outs)
+        e1.record()
+        barrier()
+        ms_events_region = e0.elapsed_time(e1) / args.steps
+        prof = enc.profile_read()
+        enc.profile_enable(False)
     clocks = sampler.stop() if sampler else None
-    prof = enc.profile_read()
-    enc.profile_enable(False)
     if enc.device_status() != 0:
         raise SystemExit("a kernel reported a device-side error status")
     ms_per_step = ms_total / args.steps
@@ -312,7 +333,7 @@ def main():
         kernels["layernorm"] = {"ms": prof["layernorm"][0], "launches": int(prof["layernorm"][1]),
                                 "gbs": ln_bytes / (prof["layernorm"][0] / 1000.0) / 1e9 if prof["layernorm"][0] > 0 else None,
                                 "hbm_peak_gbs": peaks["hbm_gbs"]}
-    launches = int(sum(v[1] for v in prof.values()))
+    launches = int(sum(v[1] for v in launch_counts.values()))
     if dist is not None:
         t = torch.tensor([launches], dtype=torch.float64, device=dev)
         dist.all_reduce(t)
@@ -329,10 +350,14 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "desc": WORKLOAD_DESC, "total_tokens": total_tokens,
+            "config": {"workload": WORKLOAD if not (args.max_seqs or args.layers) else
+                       f"{WORKLOAD} reduced: max_seqs={args.max_seqs} layers={args.layers} (profiling aid, not a bench line)",
+                       "desc": WORKLOAD_DESC, "total_tokens": total_tokens,
                        "micro_batch_token_budget": budget, "micro_batches_rank0": len(runner.batches),
                        "l2": "inputs larger than L2 (>= 100 MB of activations per GPU per step)",
-                       "kernel_events_in_timed_region": not args.no_kernel_events},
+                       "roofline_measurement": "the K timed steps repeated right after, with CUDA events around every "
+                                               "kernel launch on the launching stream",
+                       "ms_per_step_with_kernel_events": ms_events_region},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
             "kernels": kernels,
         }

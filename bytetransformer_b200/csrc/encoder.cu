@@ -53,15 +53,15 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
-                  uint32_t box_rows) {
+                  uint32_t box_rows, int elem_bytes) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * 2) % 16 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * elem_bytes) % 16 != 0) return false;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -72,8 +72,10 @@ struct TmapKey {
   const void* base;
   uint64_t rows, cols;
   uint32_t box_cols, box_rows;
+  int elem_bytes;
   bool operator==(const TmapKey& o) const {
-    return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows;
+    return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows &&
+           elem_bytes == o.elem_bytes;
   }
 };
 
@@ -114,12 +116,13 @@ struct bt_encoder_s {
     return ev_pool[ev_used++];
   }
 
-  const CUtensorMap* tmap(const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
-    bt::TmapKey k{base, rows, cols, box_cols, box_rows};
+  const CUtensorMap* tmap(const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows,
+                          int elem_bytes = 2) {
+    bt::TmapKey k{base, rows, cols, box_cols, box_rows, elem_bytes};
     for (auto& e : tmaps)
       if (e.first == k) return &e.second;
     CUtensorMap m;
-    if (!bt::make_tmap_2d(&m, base, rows, cols, cols, box_cols, box_rows)) return nullptr;
+    if (!bt::make_tmap_2d(&m, base, rows, cols, cols, box_cols, box_rows, elem_bytes)) return nullptr;
     const size_t cap = 256;
     if (tmaps.size() < cap) {
       tmaps.emplace_back(k, m);
@@ -208,10 +211,14 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
                     cudaStream_t stream) {
   const CUtensorMap* ta = h->tmap(A, m_rows, K, 64, 128);
   const CUtensorMap* tb = h->tmap(W, K, N, 64, 64);
-  if (!ta || !tb) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
+  const bool f32out = epi == BT_EPI_BIAS_RESIDUAL_F32OUT;
+  const CUtensorMap* to = f32out ? h->tmap(out, m_rows, N, 32, 32, 4) : h->tmap(out, m_rows, N, 64, 32, 2);
+  if (!ta || !tb || !to)
+    return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
   GemmLaunch g;
   g.tm_a = *ta;
   g.tm_b = *tb;
+  g.tm_out = *to;
   g.out = out;
   g.bias = reinterpret_cast<const __half*>(bias);
   g.residual = residual;

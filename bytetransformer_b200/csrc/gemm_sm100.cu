@@ -12,8 +12,10 @@
 //               kind::f16) from one elected lane; accumulators are double buffered
 //               in tensor memory (2 x BLOCK_N columns) so the epilogue of tile i
 //               overlaps the main loop of tile i+1.
-//   warps 2..9  epilogue: tcgen05.ld 32-column chunks -> +bias -> GELU / +residual
-//               -> fp16 -> 16-byte global stores, rows predicated on M.
+//   warps 2..9  epilogue: tcgen05.ld -> +bias -> GELU / +residual -> fp16 (or fp32)
+//               -> 128B-swizzled staging rows in shared memory -> TMA bulk store
+//               (full 128-byte lines); a 32-row slab that crosses M falls back to
+//               row-predicated 16-byte stores, so rows >= M are never written.
 // M is read from device memory (the packed token count is only known on the
 // device), so the host never blocks; the grid is sized from the allocated rows.
 // Every mbarrier wait is bounded: on expiry the CTA records a code in the status
@@ -31,6 +33,7 @@ constexpr int kBlockK = 64;
 constexpr int kGemmThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KiB
+constexpr int kStagingBytesPerWarp = 32 * 128;  // 32 rows x 128 B
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -38,7 +41,11 @@ struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * BLOCK_N;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  // Output leaves through per-warp staging rows + TMA bulk stores when a warp's
+  // column share is at least 128 bytes wide (BLOCK_N >= 128).
+  static constexpr bool kTmaStore = BLOCK_N >= 128;
+  static constexpr int kStagingBytes = kEpiWarps * kStagingBytesPerWarp;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 struct GemmArgs {
@@ -64,13 +71,13 @@ long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block
 template <int BLOCK_N, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                const GemmArgs args) {
+                const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
   uint64_t* full_bar = bars;                    // [kStages]
   uint64_t* empty_bar = bars + kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;      // [2]
@@ -188,6 +195,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
     const int col_half = e >> 2;             // which half of the tile's columns
     constexpr int kColsPerWarp = BLOCK_N / 2;
+    constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+    constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+    // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
+    constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
+    constexpr bool kTmaStore = Cfg::kTmaStore;
+    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;  // 32 rows x 128 B, swizzled
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
@@ -195,28 +208,47 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       const int n0 = (tile % n_tiles) * BLOCK_N;
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
+      const int row0 = m0 + quarter * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < M;
+      // The residual slice of this thread's row is fetched before waiting for the
+      // accumulator, so its latency hides behind the main loop of the tile.
+      uint4 resv[kHasResidual ? kColsPerWarp / 8 : 1];
+      if (kHasResidual) {
+        const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + n0 +
+                                                         col_half * kColsPerWarp);
+#pragma unroll
+        for (int q = 0; q < kColsPerWarp / 8; ++q) resv[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
+      }
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      const bool row_ok = row < M;
+      const bool slab_full = kTmaStore && (row0 + 32 <= M);  // all 32 rows valid: bulk store, else predicated stores
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BLOCK_N;
-#pragma unroll 1
-      for (int c = 0; c < kColsPerWarp; c += 32) {
-        const int col = col_half * kColsPerWarp + c;  // column inside the tile
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + col, r);
-        tmem_ld_wait();
-        const int gcol = n0 + col;
-        float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      for (int c = 0; c < kColsPerWarp; c += kChunk) {
+        const int col = col_half * kColsPerWarp + c;  // column inside the tile
+        const int gcol = n0 + col;
+        float v[kChunk];
+        {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + col, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (kChunk == 64) {
+            tmem_ld_32x32(t_row + col + 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[(kChunk == 64 ? 32 : 0) + i] = __uint_as_float(r[i]);
+          }
+        }
         if (EPI != BT_EPI_NONE) {
           const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < kChunk / 8; ++q) {
             const uint4 b4 = __ldg(bp + q);
             const __half2* bh = reinterpret_cast<const __half2*>(&b4);
 #pragma unroll
@@ -230,50 +262,68 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (EPI == BT_EPI_BIAS_GELU) {
           if (args.gelu_kind == BT_GELU_TANH) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+            for (int i = 0; i < kChunk; ++i) v[i] = gelu_tanh(v[i]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+            for (int i = 0; i < kChunk; ++i) v[i] = gelu_erf_fast(v[i]);
           }
         }
-        if (row_ok) {
-          const size_t off = static_cast<size_t>(row) * args.N + gcol;
-          if (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) {
-            const uint4* rp = reinterpret_cast<const uint4*>(args.residual + off);
+        const size_t off = static_cast<size_t>(row) * args.N + gcol;
+        if (kHasResidual) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 r4 = __ldg(rp + q);
-              const __half2* rh = reinterpret_cast<const __half2*>(&r4);
+          for (int q = 0; q < kChunk / 8; ++q) {
+            const uint4 r4 = resv[c / 8 + q];
+            const __half2* rh = reinterpret_cast<const __half2*>(&r4);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(rh[j]);
-                v[q * 8 + 2 * j] += f.x;
-                v[q * 8 + 2 * j + 1] += f.y;
-              }
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(rh[j]);
+              v[q * 8 + 2 * j] += f.x;
+              v[q * 8 + 2 * j + 1] += f.y;
             }
           }
-          if (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) {
-            float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + off);
+        }
+        // 8 units of 16 bytes per row
+        uint4 units[8];
+        if (kF32Out) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) op[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-          } else {
-            uint4* op = reinterpret_cast<uint4*>(args.out + off);
+          for (int q = 0; q < 8; ++q)
+            units[q] = make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
+                                  __float_as_uint(v[q * 4 + 3]));
+        } else {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
-              op[q] = o;
-            }
+          for (int q = 0; q < kChunk / 8; ++q) {
+            units[q].x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
+            units[q].y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
+            units[q].z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
+            units[q].w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
           }
+        }
+        constexpr int kUnits = kF32Out ? 8 : kChunk / 8;
+        if (slab_full) {
+          // the previous bulk store of this warp must have finished reading the staging rows
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          uint8_t* srow = stg + lane * 128;
+#pragma unroll
+          for (int q = 0; q < kUnits; ++q) *reinterpret_cast<uint4*>(srow + ((q ^ (lane & 7)) << 4)) = units[q];
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tm_out, stg, gcol, row0);
+            tma_store_commit();
+          }
+        } else if (row_ok) {
+          uint4* op = kF32Out ? reinterpret_cast<uint4*>(reinterpret_cast<float*>(args.out) + off)
+                              : reinterpret_cast<uint4*>(args.out + off);
+#pragma unroll
+          for (int q = 0; q < kUnits; ++q) op[q] = units[q];
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
     }
+    if (kTmaStore && lane == 0) tma_store_wait_all();  // staging rows must outlive the last bulk store
   }
 
   // ------------------------------------------------------------------ teardown
@@ -306,7 +356,7 @@ cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   long long tiles = static_cast<long long>(n_tiles) * m_tiles;
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(g.tm_a, g.tm_b, a);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(g.tm_a, g.tm_b, g.tm_out, a);
   return cudaGetLastError();
 }
 

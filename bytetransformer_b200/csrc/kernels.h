@@ -11,11 +11,11 @@
 namespace bt {
 
 // ---- tensor maps -----------------------------------------------------------
-// Encodes a 2-D fp16 row-major tensor [rows, cols] (row stride `ld` elements)
+// Encodes a 2-D fp16 (elem_bytes 2) or fp32 (elem_bytes 4) row-major tensor [rows, cols] (row stride `ld` elements)
 // with a {box_cols, box_rows} box and 128-byte swizzle.  Returns false when the
 // driver entry point is unavailable or the encode fails.
 bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                  uint32_t box_cols, uint32_t box_rows);
+                  uint32_t box_cols, uint32_t box_rows, int elem_bytes = 2);
 
 // ---- offsets / pack / restore ----------------------------------------------
 cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_idx, int* word_idx,
@@ -29,6 +29,7 @@ cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int*
 struct GemmLaunch {
   CUtensorMap tm_a;  // A [m_rows, K], box {64, 128}
   CUtensorMap tm_b;  // W [K, N],     box {64, 64}
+  CUtensorMap tm_out;  // out [m_rows, N]: fp16 box {64, 32} or fp32 box {32, 32} (128-byte rows)
   __half* out;
   const __half* bias;
   const __half* residual;

@@ -3,9 +3,15 @@
 // Stands in for the reference's packed attention kernels
 // (bytetransformer/src/attention_fused.cu:295-414 for short sequences,
 // bytetransformer/src/attention_fused_long.cu:171-312 and the grouped-GEMM path
-// of bytetransformer/src/cutlass_attention.cu:150-210 for long ones) with ONE
-// kernel: 128 query rows per CTA, online softmax over 128-key tiles, so no
-// S x S logits ever reach HBM and any length up to the tensor map's extent works.
+// of bytetransformer/src/cutlass_attention.cu:150-210 for long ones).  One
+// templated kernel, two instantiations:
+//   TILES = 1  short sequences (max length <= 128): 128 query rows per CTA,
+//              192 threads, two CTAs per SM overlap each other's phases;
+//   TILES = 2  long sequences: 256 query rows per CTA as two 128-row tiles that
+//              ping-pong on the tensor core (while one tile's softmax runs, the
+//              other tile's QK^T / PV MMAs execute), 320 threads, one CTA per SM.
+// Both run an online softmax over 128-key tiles, so no S x S logits ever reach
+// HBM and any length works.
 //
 // Input is the packed QKV activation [rows, 3H] with bias already added by the
 // QKV GEMM epilogue; head h of Q/K/V is the 64-column slice at h*64 / H+h*64 /
@@ -14,13 +20,16 @@
 // no counterpart here).  Only `batch_idx` tells where sequences start and end;
 // as in the reference's packed kernels the mask tensor is not consulted again.
 //
-// CTA = 192 threads: warp 0 TMA loads, warp 1 tcgen05.mma issue (+ tensor-memory
-// allocation), warps 2-5 softmax (one query row per thread).
-//   S = Q K^T      128x128x64  -> tensor memory columns [0,128)
-//   P = exp2(...)  written as fp16 into 128B-swizzled shared memory (A operand)
-//   O_j = P V      128x64x128  -> tensor memory columns [128,192), V consumed
-//                  MN-major exactly as it lies in the QKV buffer
-//   O += alpha * ... accumulated in registers with the running max / sum.
+// Roles: warp 0 TMA loads, warp 1 tcgen05.mma issue (+ tensor-memory allocation),
+// then one warpgroup of 4 softmax warps per query tile (one query row per thread).
+//   S = Q K^T      128x128x64  -> tensor memory, 128 columns per tile
+//   P = 2^(c*S-m)  fp16, written into 128B-swizzled shared memory (A operand)
+//   O += P V       128x64x128  -> tensor memory, 64 columns per tile; V is
+//                  consumed MN-major exactly as it lies in the QKV buffer
+// O stays in tensor memory across key tiles.  The exponent reference m only
+// moves when the running maximum grows by more than 2^8 (then the O row is
+// rescaled in tensor memory); otherwise P simply grows up to 2^8, which fp16
+// holds, and the final division by the row sum makes the result exact.
 // Keys beyond the sequence end are masked by selection (never by arithmetic on
 // the fetched values) and their V rows are zeroed in shared memory, so rows of
 // neighbouring sequences or never-written workspace cannot leak in.
@@ -34,19 +43,24 @@ namespace {
 constexpr int kQRows = 128;
 constexpr int kKvRows = 128;
 constexpr int kHeadDim = 64;
-constexpr int kMhaThreads = 192;
 constexpr int kTileBytes = 128 * kHeadDim * 2;  // 16 KiB: Q, K or V tile
 constexpr int kPBytes = kQRows * kKvRows * 2;   // 32 KiB
-constexpr int kKvStages = 2;
-constexpr int kSmemQ = 0;
-constexpr int kSmemK = kSmemQ + kTileBytes;
-constexpr int kSmemV = kSmemK + kKvStages * kTileBytes;
-constexpr int kSmemP = kSmemV + kKvStages * kTileBytes;
-constexpr int kSmemBar = kSmemP + kPBytes;
-constexpr int kMhaSmemBytes = kSmemBar + 128;
-constexpr int kMhaTmemCols = 256;
-constexpr uint32_t kTmemS = 0;
-constexpr uint32_t kTmemO = 128;
+constexpr float kRescaleThreshold = 8.0f;       // log2 units
+
+template <int TILES>
+struct MhaCfg {
+  static constexpr int kStages = TILES == 2 ? 3 : 2;
+  static constexpr int kThreads = 64 + 128 * TILES;
+  static constexpr int kSmemQ = 0;
+  static constexpr int kSmemK = kSmemQ + TILES * kTileBytes;
+  static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
+  static constexpr int kSmemP = kSmemV + kStages * kTileBytes;
+  static constexpr int kSmemBar = kSmemP + TILES * kPBytes;
+  static constexpr int kSmemBytes = kSmemBar + 256;
+  static constexpr int kTmemCols = TILES == 2 ? 512 : 256;
+  static constexpr uint32_t kTmemO = TILES * 128;  // S tiles first, then O tiles
+  static constexpr int kMinBlocks = TILES == 2 ? 1 : 2;
+};
 
 struct MhaArgs {
   __half* ctx;
@@ -56,30 +70,53 @@ struct MhaArgs {
   int* status;
 };
 
-__global__ void __launch_bounds__(kMhaThreads, 2)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int TILES>
+__global__ void __launch_bounds__(MhaCfg<TILES>::kThreads, MhaCfg<TILES>::kMinBlocks)
 mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
+  using Cfg = MhaCfg<TILES>;
+  constexpr int kStages = Cfg::kStages;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   const int b = blockIdx.z;
   const int head = blockIdx.y;
   const int seq_start = __ldg(args.batch_idx + b);
   const int L = __ldg(args.batch_idx + b + 1) - seq_start;
-  const int q0 = blockIdx.x * kQRows;
+  const int q0 = blockIdx.x * (kQRows * TILES);
   if (q0 >= L) return;  // whole CTA leaves before any barrier / allocation exists
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0 && args.status != nullptr) atomicCAS(args.status, 0, kStatusMhaLoadTimeout + 0x10);
     return;
   }
+  const int n_tiles = (TILES == 2 && q0 + kQRows < L) ? 2 : 1;  // query tiles with at least one valid row
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
-  uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* v_full = bars + 3;    // [2]
-  uint64_t* kv_empty = bars + 5;  // [2]
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 8;
-  uint64_t* o_full = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kSmemBar);
+  uint64_t* q_full = bars;                       // [TILES]
+  uint64_t* k_full = bars + 2;                   // [kStages]
+  uint64_t* v_full = bars + 2 + kStages;         // [kStages]
+  uint64_t* kv_empty = bars + 2 + 2 * kStages;   // [kStages]
+  uint64_t* s_full = bars + 2 + 3 * kStages;     // [TILES]
+  uint64_t* p_full = bars + 4 + 3 * kStages;     // [TILES]
+  uint64_t* o_done = bars + 6 + 3 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 3 * kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -87,20 +124,22 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   const int n_kv = (L + kKvRows - 1) / kKvRows;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < kKvStages; ++s) {
+    for (int t = 0; t < TILES; ++t) {
+      mbar_init(&q_full[t], 1);
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+    }
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kMhaTmemCols);
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -116,18 +155,20 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
     // ------------------------------------------------------------------ loads
     if (lane == 0) {
       tma_prefetch_desc(&tm_qkv);
-      mbar_arrive_expect_tx(q_full, kTileBytes);
-      tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, col_q, seq_start + q0);
+      for (int t = 0; t < n_tiles; ++t) {
+        mbar_arrive_expect_tx(&q_full[t], kTileBytes);
+        tma_load_2d(smem + Cfg::kSmemQ + t * kTileBytes, &tm_qkv, &q_full[t], col_q, seq_start + q0 + t * kQRows);
+      }
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < n_kv; ++j) {
         if (!mbar_wait_bounded(&kv_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) break;
         const int row = seq_start + j * kKvRows;
         mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
-        tma_load_2d(smem + kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], col_k, row);
+        tma_load_2d(smem + Cfg::kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], col_k, row);
         mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
-        tma_load_2d(smem + kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], col_v, row);
-        if (++stage == kKvStages) {
+        tma_load_2d(smem + Cfg::kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], col_v, row);
+        if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
@@ -142,154 +183,233 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
       constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
       constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
       constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
-      const uint32_t sq = smem_u32(smem + kSmemQ);
-      const uint32_t sp = smem_u32(smem + kSmemP);
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, args.status, kStatusMhaMmaTimeout);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const uint32_t jpar = j & 1;
-        if (!mbar_wait_bounded(&k_full[stage], phase, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + kSmemK + stage * kTileBytes);
+      const uint32_t s_q = smem_u32(smem + Cfg::kSmemQ);
+      const uint32_t s_k = smem_u32(smem + Cfg::kSmemK);
+      const uint32_t s_v = smem_u32(smem + Cfg::kSmemV);
+      const uint32_t s_p = smem_u32(smem + Cfg::kSmemP);
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t sq = s_q + t * kTileBytes;
+        const uint32_t sk = s_k + stage * kTileBytes;
 #pragma unroll
         for (int k = 0; k < kHeadDim / 16; ++k)
-          umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, sq + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
+          umma_f16_ss(tmem_base + t * 128, smem_desc(kDescK, sq + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
                       k != 0 ? 1u : 0u);
-        umma_commit(s_full);
-
-        if (!mbar_wait_bounded(p_full, jpar, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        tc_fence_after();
-        const uint32_t sv = smem_u32(smem + kSmemV + stage * kTileBytes);
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t sp = s_p + t * kPBytes;
+        const uint32_t sv = s_v + stage * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < kKvRows / 16; ++kk) {
           const uint32_t pa = sp + (kk >> 2) * (kQRows * 128) + (kk & 3) * 32;
-          umma_f16_ss(tmem_base + kTmemO, smem_desc(kDescK, pa), smem_desc(kDescV, sv + kk * 2048), kIdescO,
-                      kk != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + Cfg::kTmemO + t * 64, smem_desc(kDescK, pa), smem_desc(kDescV, sv + kk * 2048),
+                      kIdescO, (accumulate || kk != 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[stage]);
-        umma_commit(o_full);
-        if (++stage == kKvStages) {
+      };
+      bool ok = true;
+      for (int t = 0; t < n_tiles && ok; ++t)
+        ok = mbar_wait_bounded(&q_full[t], 0, abort_flag, args.status, kStatusMhaMmaTimeout);
+      if (ok) ok = mbar_wait_bounded(&k_full[0], 0, abort_flag, args.status, kStatusMhaMmaTimeout);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < n_tiles; ++t) issue_s(t, 0);
+      }
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t jpar = j & 1;
+        const int st_n = (st + 1 == kStages) ? 0 : st + 1;
+        const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
+        const bool more = j + 1 < n_kv;
+        // ---- tile 0: O0 += P0 V(j), then S0(j+1)
+        if (!mbar_wait_bounded(&p_full[0], jpar, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+        if (!mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+        tc_fence_after();
+        issue_pv(0, st, j > 0);
+        if (more) {
+          if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+          tc_fence_after();
+          issue_s(0, st_n);
+        }
+        // ---- tile 1
+        if (n_tiles == 2) {
+          if (!mbar_wait_bounded(&p_full[1], jpar, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+          tc_fence_after();
+          issue_pv(1, st, j > 0);
+        }
+        umma_commit(&kv_empty[st]);  // every MMA that reads K/V stage `st` has been issued
+        if (n_tiles == 2 && more) issue_s(1, st_n);
+        st = st_n;
+        ph = ph_n;
+      }
+      umma_commit(o_done);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax
+    const int t = (warp - 2) >> 2;  // query tile of this warpgroup
+    if (t < n_tiles) {
+      const int quarter = warp & 3;
+      const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t t_s = t_lane + t * 128;
+      const uint32_t t_o = t_lane + Cfg::kTmemO + t * 64;
+      const float c = args.scale_log2e;
+      float m_ref = -INFINITY;  // exponent reference, in log2 units
+      float l_run = 0.f;
+      uint8_t* p_row = smem + Cfg::kSmemP + t * kPBytes + r * 128;
+      const int sw = r & 7;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
+        const uint32_t jpar = j & 1;
+        const int kv_valid = min(kKvRows, L - j * kKvRows);
+        const bool full_tile = kv_valid == kKvRows;
+        if (!mbar_wait_bounded(&s_full[t], jpar, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // pass 1: row maximum over the valid keys (two loads in flight, four
+        // independent running maxima so that no long dependent chain forms)
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
+        for (int cb = 0; cb < kKvRows; cb += 64) {
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32(t_s + cb, va);
+          tmem_ld_32x32(t_s + cb + 32, vb);
+          tmem_ld_wait();
+          if (full_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              mx0 = fmaxf(mx0, fmaxf(__uint_as_float(va[i]), __uint_as_float(vb[i])));
+              mx1 = fmaxf(mx1, fmaxf(__uint_as_float(va[i + 1]), __uint_as_float(vb[i + 1])));
+              mx2 = fmaxf(mx2, fmaxf(__uint_as_float(va[i + 2]), __uint_as_float(vb[i + 2])));
+              mx3 = fmaxf(mx3, fmaxf(__uint_as_float(va[i + 3]), __uint_as_float(vb[i + 3])));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              mx0 = fmaxf(mx0, (cb + i < kv_valid) ? __uint_as_float(va[i]) : -INFINITY);
+              mx1 = fmaxf(mx1, (cb + 32 + i < kv_valid) ? __uint_as_float(vb[i]) : -INFINITY);
+            }
+          }
+        }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        mx *= c;
+        if (j == 0) {
+          m_ref = mx;
+        } else {
+          const float m_new = fmaxf(m_ref, mx);
+          const bool need = (m_new - m_ref) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            // the PV of the previous key tile has retired (S of this tile was issued after it)
+            const float f = ex2_approx(m_ref - m_new);
+#pragma unroll
+            for (int cb = 0; cb < kHeadDim; cb += 32) {
+              uint32_t v[32];
+              tmem_ld_32x32(t_o + cb, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+              tmem_st_32x32(t_o + cb, v);
+            }
+            tmem_st_wait();
+            l_run *= f;
+            m_ref = m_new;
+          }
+        }
+        // pass 2: probabilities -> fp16 -> swizzled shared memory, row sum
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll 1
+        for (int cb = 0; cb < kKvRows; cb += 64) {
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32(t_s + cb, va);
+          tmem_ld_32x32(t_s + cb + 32, vb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            uint32_t(&v)[32] = hb == 0 ? va : vb;
+            const int cbase = cb + hb * 32;
+            float p[32];
+            if (full_tile) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(v[i]), c, -m_ref));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float e = ex2_approx(fmaf(__uint_as_float(v[i]), c, -m_ref));
+                p[i] = (cbase + i < kv_valid) ? e : 0.f;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              l0 += p[i];
+              l1 += p[i + 1];
+              l2 += p[i + 2];
+              l3 += p[i + 3];
+            }
+#pragma unroll
+            for (int u4 = 0; u4 < 4; ++u4) {
+              const int u = (cbase >> 3) + u4;  // 16-byte unit index along the 128 keys
+              uint4 w;
+              w.x = pack_half2(p[u4 * 8 + 0], p[u4 * 8 + 1]);
+              w.y = pack_half2(p[u4 * 8 + 2], p[u4 * 8 + 3]);
+              w.z = pack_half2(p[u4 * 8 + 4], p[u4 * 8 + 5]);
+              w.w = pack_half2(p[u4 * 8 + 6], p[u4 * 8 + 7]);
+              *reinterpret_cast<uint4*>(p_row + (u >> 3) * (kQRows * 128) + (((u & 7) ^ sw) << 4)) = w;
+            }
+          }
+        }
+        const float l_tile = (l0 + l1) + (l2 + l3);
+        l_run += l_tile;
+        if (!full_tile && t == 0) {
+          // tail tile: blank the V rows of keys that do not belong to this sequence
+          // (tile 0's PV is issued before tile 1's, so tile 0's warpgroup does it for both)
+          if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+            ok = false;
+            break;
+          }
+          if (r >= kv_valid) {
+            uint4* vr = reinterpret_cast<uint4*>(smem + Cfg::kSmemV + stage * kTileBytes + r * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&p_full[t]);
+        if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
-    }
-  } else {
-    // ---------------------------------------------------------------- softmax
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const float c = args.scale_log2e;
-    float o_acc[kHeadDim];
-#pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY;
-    float l_run = 0.f;
-    uint8_t* p_row = smem + kSmemP + r * 128;
-    const int sw = r & 7;
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const uint32_t jpar = j & 1;
-      const int kv_valid = min(kKvRows, L - j * kKvRows);
-      if (!mbar_wait_bounded(s_full, jpar, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-        ok = false;
-        break;
-      }
+      if (ok) ok = mbar_wait_bounded(o_done, 0, abort_flag, args.status, kStatusMhaSoftmaxTimeout);
       tc_fence_after();
-      // pass 1: row maximum over the valid keys
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int cb = 0; cb < kKvRows; cb += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + kTmemS + cb, v);
-        tmem_ld_wait();
+      if (ok) {
+        const int q_row = q0 + t * kQRows + r;
+        const float inv = 1.0f / l_run;
+        uint4* dst = reinterpret_cast<uint4*>(args.ctx + static_cast<size_t>(seq_start + q_row) * args.hidden +
+                                              head * kHeadDim);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = (cb + i < kv_valid) ? __uint_as_float(v[i]) : -INFINITY;
-          m_tile = fmaxf(m_tile, s);
+        for (int cb = 0; cb < kHeadDim; cb += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + cb, v);
+          tmem_ld_wait();
+          if (q_row < L) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_half2(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+              w.y = pack_half2(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+              w.z = pack_half2(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+              w.w = pack_half2(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
+              dst[(cb >> 3) + u] = w;
+            }
+          }
         }
       }
-      const float m_new = fmaxf(m_run, m_tile * c);
-      const float alpha = exp2f(m_run - m_new);
-      // pass 2: probabilities -> fp16 -> swizzled shared memory, row sum
-      float l_tile = 0.f;
-#pragma unroll 1
-      for (int cb = 0; cb < kKvRows; cb += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + kTmemS + cb, v);
-        tmem_ld_wait();
-        float p[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = exp2f(fmaf(__uint_as_float(v[i]), c, -m_new));
-          p[i] = (cb + i < kv_valid) ? e : 0.f;
-          l_tile += p[i];
-        }
-#pragma unroll
-        for (int u4 = 0; u4 < 4; ++u4) {
-          const int u = (cb >> 3) + u4;  // 16-byte unit index along the 128 keys
-          uint4 w;
-          w.x = pack_half2(p[u4 * 8 + 0], p[u4 * 8 + 1]);
-          w.y = pack_half2(p[u4 * 8 + 2], p[u4 * 8 + 3]);
-          w.z = pack_half2(p[u4 * 8 + 4], p[u4 * 8 + 5]);
-          w.w = pack_half2(p[u4 * 8 + 6], p[u4 * 8 + 7]);
-          *reinterpret_cast<uint4*>(p_row + (u >> 3) * (kQRows * 128) + (((u & 7) ^ sw) << 4)) = w;
-        }
-      }
-      if (kv_valid < kKvRows) {
-        // tail tile: blank the V rows of keys that do not belong to this sequence
-        if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-          ok = false;
-          break;
-        }
-        if (r >= kv_valid) {
-          uint4* vr = reinterpret_cast<uint4*>(smem + kSmemV + stage * kTileBytes + r * 128);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-      fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
-
-      if (!mbar_wait_bounded(o_full, jpar, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-#pragma unroll
-      for (int cb = 0; cb < kHeadDim; cb += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + kTmemO + cb, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[cb + i] = fmaf(o_acc[cb + i], alpha, __uint_as_float(v[i]));
-      }
-      l_run = fmaf(l_run, alpha, l_tile);
-      m_run = m_new;
-      if (++stage == kKvStages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-    }
-    tc_fence_before();
-    if (ok && q0 + r < L) {
-      const float inv = 1.0f / l_run;
-      uint4* dst = reinterpret_cast<uint4*>(args.ctx + static_cast<size_t>(seq_start + q0 + r) * args.hidden +
-                                            head * kHeadDim);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        uint4 w;
-        w.x = pack_half2(o_acc[u * 8 + 0] * inv, o_acc[u * 8 + 1] * inv);
-        w.y = pack_half2(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv);
-        w.z = pack_half2(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv);
-        w.w = pack_half2(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv);
-        dst[u] = w;
-      }
     }
   }
 
@@ -299,31 +419,53 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kMhaTmemCols);
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
+template <int TILES>
+cudaError_t launch_tiles(const MhaLaunch& a, const MhaArgs& args, cudaStream_t stream) {
+  using Cfg = MhaCfg<TILES>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(mha_fwd_kernel<TILES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const int rows_per_cta = kQRows * TILES;
+  dim3 grid((a.max_len + rows_per_cta - 1) / rows_per_cta, a.head_num, a.batch);
+  mha_fwd_kernel<TILES><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a.tm_qkv, args);
+  return cudaGetLastError();
+}
+
+long long g_dbg_force_tiles = 0;
 
 }  // namespace
 
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   if (a.batch <= 0 || a.max_len <= 0 || a.head_num <= 0) return cudaErrorInvalidValue;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMhaSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
   MhaArgs args;
   args.ctx = a.ctx;
   args.batch_idx = a.batch_idx;
   args.hidden = a.hidden;
   args.scale_log2e = a.scale_log2e;
   args.status = a.status;
-  dim3 grid((a.max_len + kQRows - 1) / kQRows, a.head_num, a.batch);
-  mha_fwd_kernel<<<grid, kMhaThreads, kMhaSmemBytes, stream>>>(a.tm_qkv, args);
-  return cudaGetLastError();
+  // Measured on B200 (18.9k packed tokens, 12 heads): the one-tile variant with two
+  // co-resident CTAs per SM is faster at every length from 64 to 1024 (404 vs 372
+  // TFLOP/s at 1024), so it is the default; the two-tile variant stays selectable.
+  int tiles = 1;
+  if (g_dbg_force_tiles == 1 || g_dbg_force_tiles == 2) tiles = static_cast<int>(g_dbg_force_tiles);
+  return tiles == 1 ? launch_tiles<1>(a, args, stream) : launch_tiles<2>(a, args, stream);
 }
 
 }  // namespace bt
+
+// Diagnostics hook (not part of the stable ABI): 0 = choose by max length,
+// 1 / 2 = force the short / long attention variant.
+extern "C" int bt_debug_set_mha_tiles(long long tiles) {
+  bt::g_dbg_force_tiles = tiles;
+  return 0;
+}
