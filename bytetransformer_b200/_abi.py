@@ -25,6 +25,7 @@ BT_EPI_BIAS = 1
 BT_EPI_BIAS_GELU = 2
 BT_EPI_BIAS_RESIDUAL = 3
 BT_EPI_BIAS_RESIDUAL_F32OUT = 4
+BT_STATIC_SCRATCH_BYTES = 48 * 1024 * 1024
 
 ERROR_NAMES = {0: "BT_OK", 1: "BT_ERR_INVALID_ARG", 2: "BT_ERR_WORKSPACE", 3: "BT_ERR_CUDA",
                4: "BT_ERR_UNSUPPORTED", 5: "BT_ERR_DEVICE_STATUS"}
@@ -57,6 +58,7 @@ SIGNATURES = {
     "bt_last_error": (C.c_char_p, [_vp]),
     "bt_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "bt_layer_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
+    "bt_layer_forward_padded_static": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "bt_stack_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
     "bt_stack_forward_packed": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "bt_build_offsets": (_i, [_vp, _i, _i, _vp, _vp, _vp]),

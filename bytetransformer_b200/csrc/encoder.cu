@@ -16,6 +16,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -478,6 +479,50 @@ int bt_layer_forward_padded(bt_handle h, int layer, const void* input, const voi
                             void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream) {
   if (!h) return BT_ERR_INVALID_ARG;
   return stack_padded(h, layer, 1, input, attr_mask, out, workspace, workspace_bytes, batch_size, seq_len, stream);
+}
+
+// Scratch of bt_layer_forward_padded_static(): a fixed array in the library's
+// device image instead of a caller-supplied workspace.  Every device that loads
+// the library carries these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[BT_STATIC_SCRATCH_BYTES];
+
+// `g_static_scratch` names a host-side shadow in host code, not device memory, so
+// the address a kernel may use is asked from the runtime once per device, with that
+// device current.
+static int static_scratch_address(int device, void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {};
+  if (device < 0 || device >= 64) return BT_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[device] == nullptr) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) return BT_ERR_CUDA;
+    if (cur != device && cudaSetDevice(device) != cudaSuccess) return BT_ERR_CUDA;
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (cur != device) cudaSetDevice(cur);
+    if (e != cudaSuccess || p == nullptr) return BT_ERR_CUDA;
+    addr[device] = p;
+  }
+  *out = addr[device];
+  return BT_OK;
+}
+
+int bt_layer_forward_padded_static(bt_handle h, int layer, const void* input, const void* attr_mask, void* out,
+                                   int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  size_t need = 0;
+  int rc = bt_workspace_bytes(h, batch_size, seq_len, &need);
+  if (rc != BT_OK) return rc;
+  if (need > static_cast<size_t>(BT_STATIC_SCRATCH_BYTES))
+    return fail(h, BT_ERR_WORKSPACE,
+                "batch_size*seq_len needs more scratch than the built-in BT_STATIC_SCRATCH_BYTES; "
+                "use bt_layer_forward_padded() with a caller workspace");
+  void* scratch = nullptr;
+  rc = static_scratch_address(h->device, &scratch);
+  if (rc != BT_OK) return fail(h, rc, "cudaGetSymbolAddress failed for the built-in scratch array");
+  return stack_padded(h, layer, 1, input, attr_mask, out, scratch, static_cast<size_t>(BT_STATIC_SCRATCH_BYTES),
+                      batch_size, seq_len, stream);
 }
 
 int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const void* attr_mask, void* out,

@@ -113,6 +113,28 @@ int bt_layer_forward_padded(bt_handle h, int layer, const void* input /*[B,S,H]*
                             void* workspace, size_t workspace_bytes, int batch_size, int seq_len,
                             void* stream);
 
+/* No counterpart in the reference.  Same result as bt_layer_forward_padded(), for
+ * callers that have no workspace to hand over and may not allocate one: code that
+ * runs inside another framework's execution callback, under a memory plan that was
+ * fixed beforehand, or in a process whose device-memory budget is frozen once it
+ * is serving.  The scratch is an array of BT_STATIC_SCRATCH_BYTES built into the
+ * library's device image (each GPU that loads the library holds it until the
+ * process ends), so the call performs no cudaMalloc / cudaFree and uses no
+ * allocating helper.
+ *   - Limit: bt_workspace_bytes(batch_size, seq_len) must not exceed
+ *     BT_STATIC_SCRATCH_BYTES (hidden 768: batch_size*seq_len <= 2400 tokens,
+ *     hidden 1024: <= 1800); larger shapes return BT_ERR_WORKSPACE and run nothing.
+ *   - The first call on a device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels may
+ *     overlap on the GPU (different streams) race on it; serialise them.  The array
+ *     keeps the previous call's bytes; nothing in it has to start at zero, every
+ *     region is written by this call before it is read. */
+#define BT_STATIC_SCRATCH_BYTES (48u * 1024u * 1024u)
+int bt_layer_forward_padded_static(bt_handle h, int layer, const void* input /*[B,S,H]*/,
+                                   const void* attr_mask /*[B,S,S]*/, void* out /*[B,S,H]*/,
+                                   int batch_size, int seq_len, void* stream);
+
 /* The reference's `for layer in range(n_layers)` loop
  * (unit_test/python_scripts/bert_transformer_test.py:191-200) as ONE call:
  * offsets + pack once, `n_layers` layers on the packed batch, one scatter. */
