@@ -37,6 +37,10 @@ sys.path.insert(0, ROOT)
 METRIC = "bert_base_12L_packed_tokens_per_sec"
 UNIT = "tokens/s"
 WORKLOAD = "whole_box_1024x1024"
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the four shapes of a layer at an
+# 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_f16_kernel_microbatch18k.txt
+# (algorithmic bytes of the same four launches: 84.6 MB mean).
+GEMM_DRAM_BYTES_PER_LAUNCH = 99.0e6
 WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
 
 
@@ -313,10 +317,7 @@ def main():
     kernels = {}
     if not args.no_kernel_events and gemm_ms > 0:
         achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "gemm_dram_traffic.json")
-        if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+        traffic = GEMM_DRAM_BYTES_PER_LAUNCH if not (args.max_seqs or args.layers) else None
         roofline = {"bound": "tensor", "kernel": "gemm_f16_kernel (4 shapes per layer)", "achieved": achieved,
                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                     "peak_source": peaks["source"] + " sustained bf16 dense", "traffic": traffic,
