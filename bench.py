@@ -39,7 +39,8 @@ UNIT = "tokens/s"
 WORKLOAD = "whole_box_1024x1024"
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the four shapes of a layer at an
 # 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_f16_kernel_microbatch18k.txt
-# (algorithmic bytes of the same four launches: 84.6 MB mean).
+# (algorithmic bytes of the same four launches: 146.7 MB mean; DRAM sees less because outputs of one
+# kernel are still in the 126 MB L2 when the next kernel reads them).
 GEMM_DRAM_BYTES_PER_LAUNCH = 99.0e6
 WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
 
