@@ -205,12 +205,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the encoder path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist_mod.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-        dist = dist_mod
+    from bytetransformer_b200.ranks import Ranks
+    ranks = Ranks(backend="nccl", device=dev)   # barrier / max / sum around the work; no collective on the data path
     n_gpus = world
 
     from bytetransformer_b200.encoder import Encoder
@@ -232,18 +228,8 @@ def main():
     runner = PackedRunner(enc, lengths, mine, token_budget=budget)
     xs, outs = runner.make_device_inputs(seed=rank)
 
-    def barrier():
-        torch.cuda.synchronize(dev)
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def max_over_ranks(ms: float) -> float:
-        if dist is None:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    barrier = ranks.barrier
+    max_over_ranks = ranks.max
 
     # ---- device-resident throughput -------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -299,10 +285,7 @@ def main():
         e1.record()
         barrier()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-        if dist is not None:
-            t = torch.tensor([h2d, d2h], dtype=torch.float64, device=dev)
-            dist.all_reduce(t)
-            h2d, d2h = int(t[0].item()), int(t[1].item())
+        h2d, d2h = (int(v) for v in ranks.sum(h2d, d2h))
         e2e = {"value": total_tokens / (ms_e2e / 1000.0), "unit": UNIT, "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
 
@@ -336,10 +319,7 @@ def main():
                                 "gbs": ln_bytes / (prof["layernorm"][0] / 1000.0) / 1e9 if prof["layernorm"][0] > 0 else None,
                                 "hbm_peak_gbs": peaks["hbm_gbs"]}
     launches = int(sum(v[1] for v in launch_counts.values()))
-    if dist is not None:
-        t = torch.tensor([launches], dtype=torch.float64, device=dev)
-        dist.all_reduce(t)
-        launches = int(t.item())
+    launches = int(ranks.sum(launches)[0])
 
     # ---- CPU baseline (rank 0, N = 1 only) ---------------------------------------------
     cpu = None
@@ -364,9 +344,7 @@ def main():
             "kernels": kernels,
         }
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
     return 0
 
 
