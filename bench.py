@@ -206,7 +206,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     from bytetransformer_b200.ranks import Ranks
-    ranks = Ranks(backend="nccl", device=dev)   # barrier / max / sum around the work; no collective on the data path
+    # barrier / max / sum around the work only; the data path has no collective, so the host-side gloo
+    # backend is enough (and keeps NCCL's banner off stdout, which must carry one JSON line)
+    ranks = Ranks(backend="gloo", device=dev)
     n_gpus = world
 
     from bytetransformer_b200.encoder import Encoder

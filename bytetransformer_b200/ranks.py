@@ -19,6 +19,7 @@ class Ranks:
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         self.device = device
         self.dist = None
+        self.backend = None
         if self.world > 1:
             import torch.distributed as dist
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -28,10 +29,11 @@ class Ranks:
             if backend == "nccl" and device is not None:
                 kw["device_id"] = device
             dist.init_process_group(backend, rank=self.rank, world_size=self.world, **kw)
+            self.backend = backend
             self.dist = dist
 
     def _tensor(self, values):
-        dev = self.device if (self.device is not None and self.device.type == "cuda") else torch.device("cpu")
+        dev = self.device if (self.backend == "nccl" and self.device is not None) else torch.device("cpu")
         return torch.tensor(values, dtype=torch.float64, device=dev)
 
     def barrier(self):
