@@ -3,23 +3,34 @@
 // Replaces the reference's cuBLAS / CUTLASS-2.x calls on the encoder path
 // (bytetransformer/src/gemm.cu:32-39, bytetransformer/src/gemm_bias_act.cu:76-148).
 //
-// Design (one persistent CTA per SM, 320 threads):
-//   warp 0      TMA producer: A tile [128 x 64] (K-major) and W tile [64 x BLOCK_N]
-//               (N contiguous = MN-major for UMMA, so the reference's [in,out]
-//               weight layout is consumed as is, no transposed copy) into a
-//               128B-swizzled shared-memory ring.
-//   warp 1      allocates tensor memory and issues tcgen05.mma (128 x BLOCK_N x 16,
-//               kind::f16) from one elected lane; accumulators are double buffered
-//               in tensor memory (2 x BLOCK_N columns) so the epilogue of tile i
-//               overlaps the main loop of tile i+1.
+// Two persistent kernels share one epilogue:
+//
+//  gemm_f16_kernel<BLOCK_N, EPI>      one CTA per SM, tile 128 x BLOCK_N (256/128/64),
+//                                     tcgen05.mma.cta_group::1.
+//  gemm_f16_pair_kernel<EPI>          clusters of two CTAs on an SM pair, tile 256 x 256:
+//                                     each CTA loads its 128 rows of A and HALF of the W
+//                                     tile (128 of the 256 columns); the leader CTA issues
+//                                     tcgen05.mma.cta_group::2 (M = 256), which feeds both
+//                                     SMs' tensor cores from the two halves.  Per SM this
+//                                     halves the shared-memory fill and the L2 traffic of
+//                                     W and makes room for a 6-stage ring.  Used whenever
+//                                     the problem has enough 256-row tiles.
+//
+// Roles in every CTA (320 threads):
+//   warp 0      TMA producer: A tile [128 x 64] (K-major) and W tile [64 x n] (N contiguous
+//               = MN-major for UMMA, so the reference's [in,out] weight layout is consumed
+//               as is, no transposed copy) into a 128B-swizzled shared-memory ring.
+//   warp 1      allocates tensor memory and (leader only, for the pair kernel) issues the
+//               MMAs from one lane; accumulators are double buffered in tensor memory
+//               (2 x 256 columns) so the epilogue of tile i overlaps the main loop of i+1.
 //   warps 2..9  epilogue: tcgen05.ld -> +bias -> GELU / +residual -> fp16 (or fp32)
 //               -> 128B-swizzled staging rows in shared memory -> TMA bulk store
 //               (full 128-byte lines); a 32-row slab that crosses M falls back to
 //               row-predicated 16-byte stores, so rows >= M are never written.
-// M is read from device memory (the packed token count is only known on the
-// device), so the host never blocks; the grid is sized from the allocated rows.
-// Every mbarrier wait is bounded: on expiry the CTA records a code in the status
-// word and all roles drain to a common exit that frees tensor memory.
+// M is read from device memory (the packed token count is only known on the device), so
+// the host never blocks; the grid is sized from the allocated rows.  Every mbarrier wait
+// is bounded: on expiry the CTA records a code in the status word and all roles drain to
+// a common exit that frees tensor memory.  No TMA load uses cluster multicast.
 #include "common.cuh"
 #include "kernels.h"
 #include "../../include/bt_b200.h"
@@ -48,6 +59,17 @@ struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
+// Pair kernel: per CTA 128 rows of A and 128 of the tile's 256 W columns per stage.
+struct PairCfg {
+  static constexpr int kTileN = 256;
+  static constexpr int kBHalfBytes = 128 * kBlockK * 2;  // 16 KiB
+  static constexpr int kStageBytes = kABytes + kBHalfBytes;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kStagingBytes = kEpiWarps * kStagingBytesPerWarp;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
 struct GemmArgs {
   __half* out;
   const __half* bias;
@@ -65,15 +87,149 @@ struct GemmArgs {
   uint32_t idesc;
 };
 
-// Debug overrides of the shared-memory descriptor fields (0 = use the default).
-long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0;
+// Debug overrides (0 = default): W descriptor fields, forced tile width, pair kernel on/off.
+long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 
+// ------------------------------------------------------------------------------------------
+// Epilogue of one 128 x TILE_N accumulator tile, executed by the 8 epilogue warps of a CTA.
+// The warp owns TMEM lanes (warp_id % 4) * 32 .. +31 (`quarter`) and one half of the tile's
+// columns (`col_half`).  `tm_out` is the store map (box 128 B x 32 rows).
+// ------------------------------------------------------------------------------------------
+template <int TILE_N, int EPI, bool TMA_STORE>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtensorMap* tm_out, uint8_t* stg,
+                                              uint32_t tmem_acc, int m0, int n0, int M, int quarter, int col_half,
+                                              int lane, const uint4* resv) {
+  constexpr int kColsPerWarp = TILE_N / 2;
+  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
+  constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
+  const int row0 = m0 + quarter * 32;
+  const int row = row0 + lane;
+  const bool row_ok = row < M;
+  const bool slab_full = TMA_STORE && (row0 + 32 <= M);  // all 32 rows valid: bulk store, else predicated stores
+  const uint32_t t_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+  for (int c = 0; c < kColsPerWarp; c += kChunk) {
+    const int col = col_half * kColsPerWarp + c;  // column inside the tile
+    const int gcol = n0 + col;
+    float v[kChunk];
+    {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + col, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      if (kChunk == 64) {
+        tmem_ld_32x32(t_row + col + 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[(kChunk == 64 ? 32 : 0) + i] = __uint_as_float(r[i]);
+      }
+    }
+    if (EPI != BT_EPI_NONE) {
+      const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol);
+#pragma unroll
+      for (int q = 0; q < kChunk / 8; ++q) {
+        const uint4 b4 = __ldg(bp + q);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(bh[j]);
+          v[q * 8 + 2 * j] += f.x;
+          v[q * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+    if (EPI == BT_EPI_BIAS_GELU) {
+      if (args.gelu_kind == BT_GELU_TANH) {
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = gelu_tanh(v[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = gelu_erf_fast(v[i]);
+      }
+    }
+    const size_t off = static_cast<size_t>(row) * args.N + gcol;
+    if (kHasResidual) {
+#pragma unroll
+      for (int q = 0; q < kChunk / 8; ++q) {
+        const uint4 r4 = resv[c / 8 + q];
+        const __half2* rh = reinterpret_cast<const __half2*>(&r4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(rh[j]);
+          v[q * 8 + 2 * j] += f.x;
+          v[q * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+    // 8 (or 4) units of 16 bytes per row
+    constexpr int kUnits = kF32Out ? 8 : kChunk / 8;
+    uint4 units[kUnits];
+    if (kF32Out) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        units[q] = make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
+                              __float_as_uint(v[q * 4 + 3]));
+    } else {
+#pragma unroll
+      for (int q = 0; q < kChunk / 8; ++q) {
+        units[q].x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
+        units[q].y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
+        units[q].z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
+        units[q].w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
+      }
+    }
+    if (slab_full) {
+      // the previous bulk store of this warp must have finished reading the staging rows
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+      uint8_t* srow = stg + lane * 128;
+#pragma unroll
+      for (int q = 0; q < kUnits; ++q) *reinterpret_cast<uint4*>(srow + ((q ^ (lane & 7)) << 4)) = units[q];
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tm_out, stg, gcol, row0);
+        tma_store_commit();
+      }
+    } else if (row_ok) {
+      uint4* op = kF32Out ? reinterpret_cast<uint4*>(reinterpret_cast<float*>(args.out) + off)
+                          : reinterpret_cast<uint4*>(args.out + off);
+#pragma unroll
+      for (int q = 0; q < kUnits; ++q) op[q] = units[q];
+    }
+  }
+}
+
+// The residual slice of a thread's row, fetched before the accumulator is waited for so that
+// its latency hides behind the main loop of the tile.
+template <int TILE_N, int EPI>
+__device__ __forceinline__ void prefetch_residual(const GemmArgs& args, int m0, int n0, int M, int quarter,
+                                                  int col_half, int lane, uint4* resv) {
+  constexpr int kColsPerWarp = TILE_N / 2;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  if (kHasResidual) {
+    const int row = m0 + quarter * 32 + lane;
+    const bool row_ok = row < M;
+    const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + n0 +
+                                                     col_half * kColsPerWarp);
+#pragma unroll
+    for (int q = 0; q < kColsPerWarp / 8; ++q) resv[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// One CTA per SM, tile 128 x BLOCK_N.
+// ------------------------------------------------------------------------------------------
 template <int BLOCK_N, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -192,138 +348,26 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue
     const int e = warp - 2;
-    const int quarter = warp & 3;            // TMEM lane quarter this warp may read
-    const int col_half = e >> 2;             // which half of the tile's columns
-    constexpr int kColsPerWarp = BLOCK_N / 2;
-    constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
-    constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
-    // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
-    constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
-    constexpr bool kTmaStore = Cfg::kTmaStore;
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int col_half = e >> 2;   // which half of the tile's columns
     uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;  // 32 rows x 128 B, swizzled
     int it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       const int m0 = (tile / n_tiles) * kBlockM;
       const int n0 = (tile % n_tiles) * BLOCK_N;
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
-      const int row0 = m0 + quarter * 32;
-      const int row = row0 + lane;
-      const bool row_ok = row < M;
-      // The residual slice of this thread's row is fetched before waiting for the
-      // accumulator, so its latency hides behind the main loop of the tile.
-      uint4 resv[kHasResidual ? kColsPerWarp / 8 : 1];
-      if (kHasResidual) {
-        const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + n0 +
-                                                         col_half * kColsPerWarp);
-#pragma unroll
-        for (int q = 0; q < kColsPerWarp / 8; ++q) resv[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
-      }
-      if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) {
-        ok = false;
-        break;
-      }
+      uint4 resv[kHasResidual ? BLOCK_N / 16 : 1];
+      prefetch_residual<BLOCK_N, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
+      if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
-      const bool slab_full = kTmaStore && (row0 + 32 <= M);  // all 32 rows valid: bulk store, else predicated stores
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BLOCK_N;
-#pragma unroll
-      for (int c = 0; c < kColsPerWarp; c += kChunk) {
-        const int col = col_half * kColsPerWarp + c;  // column inside the tile
-        const int gcol = n0 + col;
-        float v[kChunk];
-        {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + col, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (kChunk == 64) {
-            tmem_ld_32x32(t_row + col + 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[(kChunk == 64 ? 32 : 0) + i] = __uint_as_float(r[i]);
-          }
-        }
-        if (EPI != BT_EPI_NONE) {
-          const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol);
-#pragma unroll
-          for (int q = 0; q < kChunk / 8; ++q) {
-            const uint4 b4 = __ldg(bp + q);
-            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __half22float2(bh[j]);
-              v[q * 8 + 2 * j] += f.x;
-              v[q * 8 + 2 * j + 1] += f.y;
-            }
-          }
-        }
-        if (EPI == BT_EPI_BIAS_GELU) {
-          if (args.gelu_kind == BT_GELU_TANH) {
-#pragma unroll
-            for (int i = 0; i < kChunk; ++i) v[i] = gelu_tanh(v[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < kChunk; ++i) v[i] = gelu_erf_fast(v[i]);
-          }
-        }
-        const size_t off = static_cast<size_t>(row) * args.N + gcol;
-        if (kHasResidual) {
-#pragma unroll
-          for (int q = 0; q < kChunk / 8; ++q) {
-            const uint4 r4 = resv[c / 8 + q];
-            const __half2* rh = reinterpret_cast<const __half2*>(&r4);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __half22float2(rh[j]);
-              v[q * 8 + 2 * j] += f.x;
-              v[q * 8 + 2 * j + 1] += f.y;
-            }
-          }
-        }
-        // 8 units of 16 bytes per row
-        uint4 units[8];
-        if (kF32Out) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            units[q] = make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
-                                  __float_as_uint(v[q * 4 + 3]));
-        } else {
-#pragma unroll
-          for (int q = 0; q < kChunk / 8; ++q) {
-            units[q].x = pack_half2(v[q * 8 + 0], v[q * 8 + 1]);
-            units[q].y = pack_half2(v[q * 8 + 2], v[q * 8 + 3]);
-            units[q].z = pack_half2(v[q * 8 + 4], v[q * 8 + 5]);
-            units[q].w = pack_half2(v[q * 8 + 6], v[q * 8 + 7]);
-          }
-        }
-        constexpr int kUnits = kF32Out ? 8 : kChunk / 8;
-        if (slab_full) {
-          // the previous bulk store of this warp must have finished reading the staging rows
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-          uint8_t* srow = stg + lane * 128;
-#pragma unroll
-          for (int q = 0; q < kUnits; ++q) *reinterpret_cast<uint4*>(srow + ((q ^ (lane & 7)) << 4)) = units[q];
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tm_out, stg, gcol, row0);
-            tma_store_commit();
-          }
-        } else if (row_ok) {
-          uint4* op = kF32Out ? reinterpret_cast<uint4*>(reinterpret_cast<float*>(args.out) + off)
-                              : reinterpret_cast<uint4*>(args.out + off);
-#pragma unroll
-          for (int q = 0; q < kUnits; ++q) op[q] = units[q];
-        }
-      }
+      epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
+                                                  col_half, lane, resv);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
     }
-    if (kTmaStore && lane == 0) tma_store_wait_all();  // staging rows must outlive the last bulk store
+    if (Cfg::kTmaStore && lane == 0) tma_store_wait_all();  // staging rows must outlive the last bulk store
   }
 
   // ------------------------------------------------------------------ teardown
@@ -339,6 +383,236 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Two CTAs per cluster (an SM pair), tile 256 x 256, tcgen05.mma.cta_group::2.
+// CTA rank r of the pair owns rows m0 + r*128 .. +127 (its own accumulator in its own tensor
+// memory) and stages W columns n0 + r*128 .. +127.  Barriers:
+//   full[s]      leader's copy only: 1 arrival (leader's expect_tx of BOTH CTAs' bytes); the
+//                peer's TMA completes its bytes on the leader's barrier.
+//   empty[s]     one per CTA, arrived by the leader's commit multicast to both CTAs.
+//   acc_full[a]  one per CTA, same multicast commit.
+//   acc_empty[a] leader's copy only: 16 arrivals (8 epilogue warps of each CTA).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion is counted on a barrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once every
+// tcgen05 operation issued so far has retired.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
+  using Cfg = PairCfg;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kTileN = Cfg::kTileN;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+
+  extern __shared__ uint8_t smem_raw[];
+  // Both CTAs of the pair must use identical shared-memory offsets (the MMA and the multicast
+  // commit address the peer by offset); dynamic shared memory starts at the same offset in
+  // every CTA of a launch, so the same round-up applies to both.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+  uint64_t* full_bar = bars;                    // [kStages]  (leader's copy is the live one)
+  uint64_t* empty_bar = bars + kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;      // [2]
+  uint64_t* acc_empty = bars + 2 * kStages + 2; // [2]        (leader's copy is the live one)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+  const bool leader = cta_rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  int M = args.m_rows;
+  if (args.m_dev != nullptr) {
+    const int md = __ldg(args.m_dev);
+    M = md < M ? md : M;
+  }
+  const int n_tiles = args.N / kTileN;
+  const int m_tiles = (M + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = args.K / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_a);
+      tma_prefetch_desc(&tm_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile / n_tiles) * (2 * kBlockM) + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = (tile % n_tiles) * kTileN + static_cast<int>(cta_rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
+                                 kStatusGemmProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          // the leader announces the bytes of both CTAs; all copies complete on its barrier
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sa, &tm_a, bar, kb * kBlockK, m0);
+          tma_load_2d_pair(sb, &tm_b, bar, n0, kb * kBlockK);
+          tma_load_2d_pair(sb + 64 * kBlockK * 2, &tm_b, bar, n0 + 64, kb * kBlockK);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++it) {
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[as], aphase ^ 1u, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * kTileN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint64_t adesc = smem_desc(args.a_desc_hi, sa + k * args.a_kstep_bytes);
+            const uint64_t bdesc = smem_desc(args.b_desc_hi, sb + k * args.b_kstep_bytes);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, args.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);  // frees the stage in both CTAs
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int e = warp - 2;
+    const int quarter = warp & 3;
+    const int col_half = e >> 2;
+    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;
+    int it = 0;
+    for (int tile = cluster_id; tile < total_tiles; tile += num_clusters, ++it) {
+      const int m0 = (tile / n_tiles) * (2 * kBlockM) + static_cast<int>(cta_rank) * kBlockM;
+      const int n0 = (tile % n_tiles) * kTileN;
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      uint4 resv[kHasResidual ? kTileN / 16 : 1];
+      prefetch_residual<kTileN, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
+      if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+      tc_fence_after();
+      epilogue_tile<kTileN, EPI, true>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M, quarter, col_half,
+                                       lane, resv);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[as]), 0));
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------ launch
 template <int BLOCK_N, int EPI>
 cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N>;
@@ -372,6 +646,68 @@ cudaError_t launch_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   }
 }
 
+// Clusters of two that can be co-resident on a device (one CTA per SM); 0 = not yet asked.
+int g_pair_clusters[64] = {};
+
+template <int EPI>
+cudaError_t launch_pair(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
+  using Cfg = PairCfg;
+  static bool attr_set[64] = {};
+  auto kern = gemm_f16_pair_kernel<EPI>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  if (g_pair_clusters[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (g.num_sms / 2));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = g.num_sms / 2;
+    }
+    g_pair_clusters[dev] = n;
+  }
+  const int n_tiles = g.N / Cfg::kTileN;
+  const int m_tiles = (g.m_rows + 2 * kBlockM - 1) / (2 * kBlockM);
+  long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+  int clusters = static_cast<int>(tiles < g_pair_clusters[dev] ? tiles : g_pair_clusters[dev]);
+  if (clusters < 1) clusters = 1;
+  kern<<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(g.tm_a, g.tm_b, g.tm_out, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pair_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
+  switch (g.epilogue) {
+    case BT_EPI_NONE: return launch_pair<BT_EPI_NONE>(g, a, stream);
+    case BT_EPI_BIAS: return launch_pair<BT_EPI_BIAS>(g, a, stream);
+    case BT_EPI_BIAS_GELU: return launch_pair<BT_EPI_BIAS_GELU>(g, a, stream);
+    case BT_EPI_BIAS_RESIDUAL: return launch_pair<BT_EPI_BIAS_RESIDUAL>(g, a, stream);
+    case BT_EPI_BIAS_RESIDUAL_F32OUT: return launch_pair<BT_EPI_BIAS_RESIDUAL_F32OUT>(g, a, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+// The pair kernel needs N % 256 == 0 and pays off once every SM pair gets at least two
+// 256 x 256 tiles (below that the narrower one-CTA tiles fill the machine better).
+bool use_pair_kernel(const GemmLaunch& g) {
+  if (g_dbg_pair_mode == 1) return g.N % 256 == 0;
+  if (g_dbg_pair_mode == 2 || g_dbg_force_block_n != 0 || g.block_n != 0) return false;
+  if (g.N % 256 != 0) return false;
+  // Measured at 18.9k rows: with a short main loop (K = 768) the GELU and the fp32 +
+  // residual epilogues bound the tile time and the one-CTA kernel is a few percent faster.
+  if (g.epilogue == BT_EPI_BIAS_GELU && g.K < 2048) return false;
+  if ((g.epilogue == BT_EPI_BIAS_RESIDUAL || g.epilogue == BT_EPI_BIAS_RESIDUAL_F32OUT) && g.K < 2048) return false;
+  const long long tiles = static_cast<long long>((g.m_rows + 255) / 256) * (g.N / 256);
+  return tiles >= 2LL * (g.num_sms / 2);
+}
+
 }  // namespace
 
 int gemm_pick_block_n(int m_rows, int N, int num_sms) {
@@ -390,8 +726,7 @@ int gemm_pick_block_n(int m_rows, int N, int num_sms) {
 }
 
 cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
-  int bn = g.block_n != 0 ? g.block_n : gemm_pick_block_n(g.m_rows, g.N, g.num_sms);
-  if (bn == 0 || g.N % bn != 0 || g.K % kBlockK != 0 || g.m_rows <= 0) return cudaErrorInvalidValue;
+  if (g.K % kBlockK != 0 || g.m_rows <= 0) return cudaErrorInvalidValue;
   GemmArgs a;
   a.out = g.out;
   a.bias = g.bias;
@@ -411,6 +746,12 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   const uint32_t sbo = g_dbg_b_sbo ? static_cast<uint32_t>(g_dbg_b_sbo) : 1024u;
   a.b_desc_hi = make_smem_desc_hi(lbo, sbo);
   a.b_kstep_bytes = g_dbg_b_kstep ? static_cast<uint32_t>(g_dbg_b_kstep) : 2048u;
+  if (use_pair_kernel(g)) {
+    a.idesc = make_idesc_f16(256, 256, 0, 1);  // M = 256 across the pair
+    return launch_pair_epi(g, a, stream);
+  }
+  int bn = g.block_n != 0 ? g.block_n : gemm_pick_block_n(g.m_rows, g.N, g.num_sms);
+  if (bn == 0 || g.N % bn != 0) return cudaErrorInvalidValue;
   a.idesc = make_idesc_f16(kBlockM, bn, 0, 1);
   switch (bn) {
     case 256: return launch_epi<256>(g, a, stream);
@@ -425,13 +766,15 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // Diagnostics hook (not part of the stable ABI): overrides descriptor fields of
 // the W operand / the tile width so that encodings can be compared on a device
 // without rebuilding.  key: 1 = LBO bytes, 2 = SBO bytes, 3 = K-step bytes,
-// 4 = forced BLOCK_N.  value 0 restores the default.
+// 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
+// N % 256 == 0, 2 never).  value 0 restores the default.
 extern "C" int bt_debug_set(int key, long long value) {
   switch (key) {
     case 1: bt::g_dbg_b_lbo = value; return 0;
     case 2: bt::g_dbg_b_sbo = value; return 0;
     case 3: bt::g_dbg_b_kstep = value; return 0;
     case 4: bt::g_dbg_force_block_n = value; return 0;
+    case 5: bt::g_dbg_pair_mode = value; return 0;
     default: return 1;
   }
 }

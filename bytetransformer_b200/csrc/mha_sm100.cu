@@ -89,6 +89,85 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Row maximum of S over the valid keys.  The next 32-column chunk is requested from
+// tensor memory before the current one is reduced, so only the first load is exposed.
+template <bool MASKED>
+__device__ __forceinline__ float chunk_max(const uint32_t (&v)[32], int cbase, int kv_valid) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    m0 = fmaxf(m0, (!MASKED || cbase + i < kv_valid) ? __uint_as_float(v[i]) : -INFINITY);
+    m1 = fmaxf(m1, (!MASKED || cbase + i + 1 < kv_valid) ? __uint_as_float(v[i + 1]) : -INFINITY);
+    m2 = fmaxf(m2, (!MASKED || cbase + i + 2 < kv_valid) ? __uint_as_float(v[i + 2]) : -INFINITY);
+    m3 = fmaxf(m3, (!MASKED || cbase + i + 3 < kv_valid) ? __uint_as_float(v[i + 3]) : -INFINITY);
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+template <bool MASKED>
+__device__ __forceinline__ float tile_row_max(uint32_t t_s, int kv_valid) {
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32(t_s, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 32, vb);
+  float mx = chunk_max<MASKED>(va, 0, kv_valid);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, va);
+  mx = fmaxf(mx, chunk_max<MASKED>(vb, 32, kv_valid));
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 96, vb);
+  mx = fmaxf(mx, chunk_max<MASKED>(va, 64, kv_valid));
+  tmem_ld_wait();
+  return fmaxf(mx, chunk_max<MASKED>(vb, 96, kv_valid));
+}
+
+// One 32-column chunk: p = 2^(c*s - m_ref) (0 for masked keys), partial row sums, running
+// raw maximum, fp16 pack and store into the 128B-swizzled P row.
+template <bool MASKED>
+__device__ __forceinline__ void chunk_softmax(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
+                                              uint8_t* p_row, int sw, float (&l)[4], float (&mx)[4]) {
+  float p[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float s = __uint_as_float(v[i]);
+    const float e = ex2_approx(fmaf(s, c, -m_ref));
+    const bool ok = !MASKED || (cbase + i < kv_valid);
+    p[i] = ok ? e : 0.f;
+    mx[i & 3] = fmaxf(mx[i & 3], ok ? s : -INFINITY);
+    l[i & 3] += p[i];
+  }
+#pragma unroll
+  for (int u4 = 0; u4 < 4; ++u4) {
+    const int u = (cbase >> 3) + u4;  // 16-byte unit index along the 128 keys
+    uint4 w;
+    w.x = pack_half2(p[u4 * 8 + 0], p[u4 * 8 + 1]);
+    w.y = pack_half2(p[u4 * 8 + 2], p[u4 * 8 + 3]);
+    w.z = pack_half2(p[u4 * 8 + 4], p[u4 * 8 + 5]);
+    w.w = pack_half2(p[u4 * 8 + 6], p[u4 * 8 + 7]);
+    *reinterpret_cast<uint4*>(p_row + (u >> 3) * (kQRows * 128) + (((u & 7) ^ sw) << 4)) = w;
+  }
+}
+template <bool MASKED>
+__device__ __forceinline__ void tile_softmax(uint32_t t_s, int kv_valid, float c, float m_ref, uint8_t* p_row, int sw,
+                                             float& l_tile, float& mx_tile) {
+  float l[4] = {0.f, 0.f, 0.f, 0.f};
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32(t_s, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 32, vb);  // in flight while chunk 0 is processed
+  chunk_softmax<MASKED>(va, 0, kv_valid, c, m_ref, p_row, sw, l, mx);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, va);
+  chunk_softmax<MASKED>(vb, 32, kv_valid, c, m_ref, p_row, sw, l, mx);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 96, vb);
+  chunk_softmax<MASKED>(va, 64, kv_valid, c, m_ref, p_row, sw, l, mx);
+  tmem_ld_wait();
+  chunk_softmax<MASKED>(vb, 96, kv_valid, c, m_ref, p_row, sw, l, mx);
+  l_tile = (l[0] + l[1]) + (l[2] + l[3]);
+  mx_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
 template <int TILES>
 __global__ void __launch_bounds__(MhaCfg<TILES>::kThreads, MhaCfg<TILES>::kMinBlocks)
 mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
@@ -270,37 +349,18 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           break;
         }
         tc_fence_after();
-        // pass 1: row maximum over the valid keys (two loads in flight, four
-        // independent running maxima so that no long dependent chain forms)
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-        for (int cb = 0; cb < kKvRows; cb += 64) {
-          uint32_t va[32], vb[32];
-          tmem_ld_32x32(t_s + cb, va);
-          tmem_ld_32x32(t_s + cb + 32, vb);
-          tmem_ld_wait();
-          if (full_tile) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              mx0 = fmaxf(mx0, fmaxf(__uint_as_float(va[i]), __uint_as_float(vb[i])));
-              mx1 = fmaxf(mx1, fmaxf(__uint_as_float(va[i + 1]), __uint_as_float(vb[i + 1])));
-              mx2 = fmaxf(mx2, fmaxf(__uint_as_float(va[i + 2]), __uint_as_float(vb[i + 2])));
-              mx3 = fmaxf(mx3, fmaxf(__uint_as_float(va[i + 3]), __uint_as_float(vb[i + 3])));
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              mx0 = fmaxf(mx0, (cb + i < kv_valid) ? __uint_as_float(va[i]) : -INFINITY);
-              mx1 = fmaxf(mx1, (cb + 32 + i < kv_valid) ? __uint_as_float(vb[i]) : -INFINITY);
-            }
-          }
-        }
-        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        mx *= c;
-        if (j == 0) {
-          m_ref = mx;
-        } else {
-          const float m_new = fmaxf(m_ref, mx);
+        // The exponent reference m_ref is known from earlier key tiles (for the first
+        // tile it is this tile's own row maximum), so one pass over S suffices: it
+        // computes 2^(c*s - m_ref), the row sum AND the row maximum.  Only if the maximum
+        // outgrew m_ref by more than 2^8 is the O row rescaled and the pass repeated.
+        if (j == 0) m_ref = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
+        float l_tile, mx_tile;
+        if (full_tile)
+          tile_softmax<false>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
+        else
+          tile_softmax<true>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
+        if (j > 0) {
+          const float m_new = fmaxf(m_ref, mx_tile * c);
           const bool need = (m_new - m_ref) > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
             // the PV of the previous key tile has retired (S of this tile was issued after it)
@@ -317,51 +377,12 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
             tmem_st_wait();
             l_run *= f;
             m_ref = m_new;
+            if (full_tile)
+              tile_softmax<false>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
+            else
+              tile_softmax<true>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
           }
         }
-        // pass 2: probabilities -> fp16 -> swizzled shared memory, row sum
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll 1
-        for (int cb = 0; cb < kKvRows; cb += 64) {
-          uint32_t va[32], vb[32];
-          tmem_ld_32x32(t_s + cb, va);
-          tmem_ld_32x32(t_s + cb + 32, vb);
-          tmem_ld_wait();
-#pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            uint32_t(&v)[32] = hb == 0 ? va : vb;
-            const int cbase = cb + hb * 32;
-            float p[32];
-            if (full_tile) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(v[i]), c, -m_ref));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const float e = ex2_approx(fmaf(__uint_as_float(v[i]), c, -m_ref));
-                p[i] = (cbase + i < kv_valid) ? e : 0.f;
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              l0 += p[i];
-              l1 += p[i + 1];
-              l2 += p[i + 2];
-              l3 += p[i + 3];
-            }
-#pragma unroll
-            for (int u4 = 0; u4 < 4; ++u4) {
-              const int u = (cbase >> 3) + u4;  // 16-byte unit index along the 128 keys
-              uint4 w;
-              w.x = pack_half2(p[u4 * 8 + 0], p[u4 * 8 + 1]);
-              w.y = pack_half2(p[u4 * 8 + 2], p[u4 * 8 + 3]);
-              w.z = pack_half2(p[u4 * 8 + 4], p[u4 * 8 + 5]);
-              w.w = pack_half2(p[u4 * 8 + 6], p[u4 * 8 + 7]);
-              *reinterpret_cast<uint4*>(p_row + (u >> 3) * (kQRows * 128) + (((u & 7) ^ sw) << 4)) = w;
-            }
-          }
-        }
-        const float l_tile = (l0 + l1) + (l2 + l3);
         l_run += l_tile;
         if (!full_tile && t == 0) {
           // tail tile: blank the V rows of keys that do not belong to this sequence

@@ -288,3 +288,51 @@ def test_gemm_fp32_out_feeds_layernorm(enc, cuda_device):
     out = add_bias_residual_layernorm(pre, None, None, gamma.to(cuda_device), beta.to(cuda_device), eps=1e-6)
     want = torch.nn.functional.layer_norm(want_pre, (N,), gamma.float(), beta.float(), eps=1e-6)
     assert_close_fp16(out, want, "gemm->ln", max_abs=3e-3, mean_abs=3e-4)
+
+
+@pytest.mark.parametrize("M,N,K,epi", [
+    (256, 256, 64, 0), (300, 768, 768, 1), (1000, 2304, 768, 1), (777, 3072, 768, 2),
+    (2049, 768, 3072, 3), (4500, 768, 768, 4), (18944, 768, 3072, 4), (129, 256, 128, 0),
+])
+def test_gemm_pair_kernel(enc, cuda_device, M, N, K, epi):
+    """The two-CTA (cta_group::2, 256x256 tile) kernel, forced on for every shape."""
+    from bytetransformer_b200 import _abi
+    lib = _abi.load()
+    lib.bt_debug_set(5, 1)
+    try:
+        if epi == 4:
+            g = torch.Generator().manual_seed(M + N)
+            a = torch.randn(M, K, generator=g).half()
+            w = (torch.randn(K, N, generator=g) * 0.05).half()
+            bias = torch.empty(N).uniform_(-0.4, 0.4, generator=g).half()
+            res = torch.randn(M, N, generator=g).half()
+            got = enc.gemm(a.to(cuda_device), w.to(cuda_device), bias.to(cuda_device), res.to(cuda_device),
+                           epilogue=_abi.BT_EPI_BIAS_RESIDUAL_F32OUT)
+            want = a.float() @ w.float() + bias.float() + res.float()
+            assert (got.cpu() - want).abs().max().item() < 1e-3
+        else:
+            _gemm_case(enc, cuda_device, M, N, K, epi)
+        _gemm_case(enc, cuda_device, M, N, K, _abi.BT_EPI_BIAS, m_valid=max(0, M - 131))
+    finally:
+        lib.bt_debug_set(5, 0)
+    assert enc.device_status() == 0
+
+
+def test_gemm_pair_twice_bit_identical_and_equal_to_single(enc, cuda_device):
+    from bytetransformer_b200 import _abi
+    lib = _abi.load()
+    g = torch.Generator().manual_seed(19)
+    a = torch.randn(5000, 768, generator=g).half().to(cuda_device)
+    w = (torch.randn(768, 2304, generator=g) * 0.05).half().to(cuda_device)
+    lib.bt_debug_set(5, 1)
+    try:
+        o1 = enc.gemm(a, w)
+        o2 = enc.gemm(a, w)
+    finally:
+        lib.bt_debug_set(5, 2)
+    try:
+        o3 = enc.gemm(a, w)
+    finally:
+        lib.bt_debug_set(5, 0)
+    assert torch.equal(o1, o2)
+    assert torch.equal(o1, o3)          # same accumulation order: K is walked identically
