@@ -66,7 +66,8 @@ struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBHalfBytes;
   static constexpr int kStages = 6;
   static constexpr int kTmemCols = 512;
-  static constexpr int kStagingBytes = kEpiWarps * kStagingBytesPerWarp;
+  static constexpr int kStagingBufs = 1;  // per epilogue warp (two were measured: no gain, and they cost a stage)
+  static constexpr int kStagingBytes = kStagingBufs * kEpiWarps * kStagingBytesPerWarp;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
@@ -95,7 +96,15 @@ long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block
 // The warp owns TMEM lanes (warp_id % 4) * 32 .. +31 (`quarter`) and one half of the tile's
 // columns (`col_half`).  `tm_out` is the store map (box 128 B x 32 rows).
 // ------------------------------------------------------------------------------------------
-template <int TILE_N, int EPI, bool TMA_STORE>
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read_n() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// STG_BUFS staging buffers of 32 rows x 128 B per warp are used in turn, so a bulk store
+// only has to wait for the store issued STG_BUFS chunks earlier.  The accumulator chunk
+// c+1 is requested from tensor memory before chunk c is processed.
+template <int TILE_N, int EPI, bool TMA_STORE, int STG_BUFS>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtensorMap* tm_out, uint8_t* stg,
                                               uint32_t tmem_acc, int m0, int n0, int M, int quarter, int col_half,
                                               int lane, const uint4* resv) {
@@ -104,29 +113,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
   constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
   // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
   constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
+  constexpr int kNChunks = kColsPerWarp / kChunk;
+  constexpr int kHalves = kChunk / 32;  // tcgen05.ld x32 per chunk
   const int row0 = m0 + quarter * 32;
   const int row = row0 + lane;
   const bool row_ok = row < M;
   const bool slab_full = TMA_STORE && (row0 + 32 <= M);  // all 32 rows valid: bulk store, else predicated stores
-  const uint32_t t_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+  const uint32_t t_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + col_half * kColsPerWarp;
+  uint32_t raw[2][kHalves][32];
 #pragma unroll
-  for (int c = 0; c < kColsPerWarp; c += kChunk) {
+  for (int h = 0; h < kHalves; ++h) tmem_ld_32x32(t_row + h * 32, raw[0][h]);
+  tmem_ld_wait();
+#pragma unroll
+  for (int ci = 0; ci < kNChunks; ++ci) {
+    const int c = ci * kChunk;
     const int col = col_half * kColsPerWarp + c;  // column inside the tile
     const int gcol = n0 + col;
-    float v[kChunk];
-    {
-      uint32_t r[32];
-      tmem_ld_32x32(t_row + col, r);
-      tmem_ld_wait();
+    if (ci + 1 < kNChunks) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-      if (kChunk == 64) {
-        tmem_ld_32x32(t_row + col + 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[(kChunk == 64 ? 32 : 0) + i] = __uint_as_float(r[i]);
-      }
+      for (int h = 0; h < kHalves; ++h) tmem_ld_32x32(t_row + c + kChunk + h * 32, raw[(ci + 1) & 1][h]);
     }
+    float v[kChunk];
+#pragma unroll
+    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[h * 32 + i] = __uint_as_float(raw[ci & 1][h][i]);
     if (EPI != BT_EPI_NONE) {
       const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol);
 #pragma unroll
@@ -182,16 +193,17 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
       }
     }
     if (slab_full) {
-      // the previous bulk store of this warp must have finished reading the staging rows
-      if (lane == 0) tma_store_wait_read();
+      // the bulk store that last used this staging buffer must have finished reading it
+      if (lane == 0) tma_store_wait_read_n<STG_BUFS - 1>();
       __syncwarp();
-      uint8_t* srow = stg + lane * 128;
+      uint8_t* sbuf = stg + (STG_BUFS == 2 ? (ci & 1) * kStagingBytesPerWarp : 0);
+      uint8_t* srow = sbuf + lane * 128;
 #pragma unroll
       for (int q = 0; q < kUnits; ++q) *reinterpret_cast<uint4*>(srow + ((q ^ (lane & 7)) << 4)) = units[q];
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(tm_out, stg, gcol, row0);
+        tma_store_2d(tm_out, sbuf, gcol, row0);
         tma_store_commit();
       }
     } else if (row_ok) {
@@ -200,6 +212,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
 #pragma unroll
       for (int q = 0; q < kUnits; ++q) op[q] = units[q];
     }
+    if (ci + 1 < kNChunks) tmem_ld_wait();
   }
 }
 
@@ -361,7 +374,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       prefetch_residual<BLOCK_N, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
-      epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
+      epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore, 1>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
                                                   col_half, lane, resv);
       tc_fence_before();
       __syncwarp();
@@ -578,7 +591,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const int e = warp - 2;
     const int quarter = warp & 3;
     const int col_half = e >> 2;
-    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;
+    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * (Cfg::kStagingBufs * kStagingBytesPerWarp);
     int it = 0;
     for (int tile = cluster_id; tile < total_tiles; tile += num_clusters, ++it) {
       const int m0 = (tile / n_tiles) * (2 * kBlockM) + static_cast<int>(cta_rank) * kBlockM;
@@ -589,7 +602,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       prefetch_residual<kTileN, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
-      epilogue_tile<kTileN, EPI, true>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M, quarter, col_half,
+      epilogue_tile<kTileN, EPI, true, Cfg::kStagingBufs>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M, quarter, col_half,
                                        lane, resv);
       tc_fence_before();
       __syncwarp();
