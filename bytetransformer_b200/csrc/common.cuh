@@ -42,6 +42,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// Every kernel of the library starts with pdl_launch_dependents() (the next kernel of the
+// stream may be launched as soon as all CTAs of this one have started) and calls
+// pdl_wait() before its first access to global memory that an earlier kernel may have
+// written or may still read: the wait returns once the preceding kernel has completed
+// and its writes are visible.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -80,6 +80,8 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
                       const __half* __restrict__ residual, const void* __restrict__ gamma,
                       const void* __restrict__ beta, __half* __restrict__ out, const int* __restrict__ m_dev,
                       int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * kLnWarps + warp;
@@ -178,9 +180,8 @@ cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, cons
                            const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps) {
 #define BT_LN_CASE(NV)                                                                                        \
   case NV:                                                                                                    \
-    layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV><<<grid, kLnWarps * 32, 0, stream>>>(                          \
-        x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps);                       \
-    break;
+    return launch_pdl(layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV>, grid, dim3(kLnWarps * 32), 0, stream,  \
+                      x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps);
   switch (nvec_needed) {
     BT_LN_CASE(1)
     BT_LN_CASE(2)
@@ -195,6 +196,8 @@ cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, cons
 __global__ void __launch_bounds__(256)
 add_bias_gelu_kernel(uint4* __restrict__ x, const uint4* __restrict__ bias, const int* __restrict__ m_dev,
                      int m_rows, int nvec, int gelu_kind) {
+  pdl_launch_dependents();
+  pdl_wait();
   int M = m_rows;
   if (m_dev != nullptr) {
     const int md = __ldg(m_dev);
@@ -224,6 +227,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(128)
 masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ mask, int B, int nh, int S,
                       float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * 4 + warp;
@@ -353,10 +358,8 @@ cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev
   long long g = (total + 256 * 2 - 1) / (256 * 2);
   if (g < 1) g = 1;
   if (g > 148 * 16) g = 148 * 16;
-  add_bias_gelu_kernel<<<static_cast<int>(g), 256, 0, stream>>>(reinterpret_cast<uint4*>(x),
-                                                                reinterpret_cast<const uint4*>(bias), m_dev, m_rows,
-                                                                nvec, gelu_kind);
-  return cudaGetLastError();
+  return launch_pdl(add_bias_gelu_kernel, dim3(static_cast<unsigned>(g)), dim3(256), 0, stream,
+                    reinterpret_cast<uint4*>(x), reinterpret_cast<const uint4*>(bias), m_dev, m_rows, nvec, gelu_kind);
 }
 
 cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int nh, int S, float scale,
@@ -364,11 +367,8 @@ cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int
   if (S <= 0 || S > 1024 || B <= 0 || nh <= 0) return cudaErrorInvalidValue;
   const long long rows = static_cast<long long>(B) * nh * S;
   dim3 grid(static_cast<unsigned>((rows + 3) / 4));
-  if (S % 8 == 0)
-    masked_softmax_kernel<true><<<grid, 128, 0, stream>>>(logits, mask, B, nh, S, scale);
-  else
-    masked_softmax_kernel<false><<<grid, 128, 0, stream>>>(logits, mask, B, nh, S, scale);
-  return cudaGetLastError();
+  if (S % 8 == 0) return launch_pdl(masked_softmax_kernel<true>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
+  return launch_pdl(masked_softmax_kernel<false>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
 }
 
 }  // namespace bt

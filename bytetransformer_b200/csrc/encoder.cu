@@ -28,6 +28,10 @@ namespace bt {
 
 __device__ int g_status_word = 0;
 
+static bool g_pdl_on = true;
+bool pdl_enabled() { return g_pdl_on; }
+void set_pdl_enabled(bool on) { g_pdl_on = on; }
+
 int* device_status_word() {
   int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;

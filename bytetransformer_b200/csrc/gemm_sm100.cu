@@ -257,15 +257,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  int M = args.m_rows;
-  if (args.m_dev != nullptr) {
-    const int md = __ldg(args.m_dev);
-    M = md < M ? md : M;
-  }
-  const int n_tiles = args.N / BLOCK_N;
-  const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = args.K / kBlockK;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -283,16 +275,32 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_out);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched only this CTA's own resources; from here on global memory
+  // written by earlier kernels is read (the row count first of all).
+  pdl_wait();
+  int M = args.m_rows;
+  if (args.m_dev != nullptr) {
+    const int md = __ldg(args.m_dev);
+    M = md < M ? md : M;
+  }
+  const int n_tiles = args.N / BLOCK_N;
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = args.K / kBlockK;
+
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tm_a);
-      tma_prefetch_desc(&tm_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -481,15 +489,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
 
-  int M = args.m_rows;
-  if (args.m_dev != nullptr) {
-    const int md = __ldg(args.m_dev);
-    M = md < M ? md : M;
-  }
-  const int n_tiles = args.N / kTileN;
-  const int m_tiles = (M + 2 * kBlockM - 1) / (2 * kBlockM);
-  const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = args.K / kBlockK;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -514,6 +514,17 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // see gemm_f16_kernel
+  int M = args.m_rows;
+  if (args.m_dev != nullptr) {
+    const int md = __ldg(args.m_dev);
+    M = md < M ? md : M;
+  }
+  const int n_tiles = args.N / kTileN;
+  const int m_tiles = (M + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = args.K / kBlockK;
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -643,8 +654,7 @@ cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   long long tiles = static_cast<long long>(n_tiles) * m_tiles;
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(g.tm_a, g.tm_b, g.tm_out, a);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
 }
 
 template <int BLOCK_N>
@@ -692,8 +702,7 @@ cudaError_t launch_pair(const GemmLaunch& g, const GemmArgs& a, cudaStream_t str
   long long tiles = static_cast<long long>(n_tiles) * m_tiles;
   int clusters = static_cast<int>(tiles < g_pair_clusters[dev] ? tiles : g_pair_clusters[dev]);
   if (clusters < 1) clusters = 1;
-  kern<<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(g.tm_a, g.tm_b, g.tm_out, a);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
 }
 
 cudaError_t launch_pair_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
@@ -780,7 +789,8 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // the W operand / the tile width so that encodings can be compared on a device
 // without rebuilding.  key: 1 = LBO bytes, 2 = SBO bytes, 3 = K-step bytes,
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
-// N % 256 == 0, 2 never).  value 0 restores the default.
+// N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0).
+// value 0 restores the default for keys 1-5.
 extern "C" int bt_debug_set(int key, long long value) {
   switch (key) {
     case 1: bt::g_dbg_b_lbo = value; return 0;
@@ -788,6 +798,7 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 3: bt::g_dbg_b_kstep = value; return 0;
     case 4: bt::g_dbg_force_block_n = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
+    case 6: bt::set_pdl_enabled(value != 0); return 0;
     default: return 1;
   }
 }

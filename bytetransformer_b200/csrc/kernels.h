@@ -8,7 +8,29 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace bt {
+
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait() in
+// common.cuh); `pdl_enabled()` can be switched off for A/B measurements.
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
+}
 
 // ---- tensor maps -----------------------------------------------------------
 // Encodes a 2-D fp16 (elem_bytes 2) or fp32 (elem_bytes 4) row-major tensor [rows, cols] (row stride `ld` elements)

@@ -175,6 +175,8 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   constexpr int kStages = Cfg::kStages;
   extern __shared__ __align__(1024) uint8_t smem[];
 
+  pdl_launch_dependents();
+  pdl_wait();  // batch_idx and the QKV buffer come from earlier kernels
   const int b = blockIdx.z;
   const int head = blockIdx.y;
   const int seq_start = __ldg(args.batch_idx + b);
@@ -458,8 +460,7 @@ cudaError_t launch_tiles(const MhaLaunch& a, const MhaArgs& args, cudaStream_t s
   }
   const int rows_per_cta = kQRows * TILES;
   dim3 grid((a.max_len + rows_per_cta - 1) / rows_per_cta, a.head_num, a.batch);
-  mha_fwd_kernel<TILES><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(a.tm_qkv, args);
-  return cudaGetLastError();
+  return launch_pdl(mha_fwd_kernel<TILES>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
 }
 
 long long g_dbg_force_tiles = 0;

@@ -25,6 +25,8 @@ build_offsets_kernel(const __half* __restrict__ mask, int B, int S, int* __restr
                      int* __restrict__ word_idx) {
   __shared__ int warp_sums[32];
   __shared__ int carry_s;
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -102,6 +104,8 @@ build_offsets_kernel(const __half* __restrict__ mask, int B, int S, int* __restr
 __global__ void __launch_bounds__(256)
 pack_rows_kernel(const uint4* __restrict__ padded, uint4* __restrict__ packed, const int* __restrict__ batch_idx,
                  int S, int vec_per_row) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.y;
   const int off = __ldg(batch_idx + b);
   const int len = __ldg(batch_idx + b + 1) - off;
@@ -116,6 +120,8 @@ pack_rows_kernel(const uint4* __restrict__ padded, uint4* __restrict__ packed, c
 __global__ void __launch_bounds__(256)
 restore_rows_kernel(const uint4* __restrict__ packed, uint4* __restrict__ padded, const int* __restrict__ batch_idx,
                     int S, int vec_per_row) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.y;
   const int off = __ldg(batch_idx + b);
   const int len = __ldg(batch_idx + b + 1) - off;
@@ -140,26 +146,23 @@ inline int copy_grid_x(int S, int vec_per_row) {
 
 cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_idx, int* word_idx,
                                  cudaStream_t stream) {
-  build_offsets_kernel<<<1, kOffThreads, 0, stream>>>(mask, B, S, batch_idx, word_idx);
-  return cudaGetLastError();
+  return launch_pdl(build_offsets_kernel, dim3(1), dim3(kOffThreads), 0, stream, mask, B, S, batch_idx, word_idx);
 }
 
 cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S, int hidden,
                              cudaStream_t stream) {
   const int vec = hidden / 8;
   dim3 grid(copy_grid_x(S, vec), B);
-  pack_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(padded),
-                                             reinterpret_cast<uint4*>(packed), batch_idx, S, vec);
-  return cudaGetLastError();
+  return launch_pdl(pack_rows_kernel, grid, dim3(256), 0, stream, reinterpret_cast<const uint4*>(padded),
+                    reinterpret_cast<uint4*>(packed), batch_idx, S, vec);
 }
 
 cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int* batch_idx, int B, int S,
                                 int hidden, cudaStream_t stream) {
   const int vec = hidden / 8;
   dim3 grid(copy_grid_x(S, vec), B);
-  restore_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(packed),
-                                                reinterpret_cast<uint4*>(padded), batch_idx, S, vec);
-  return cudaGetLastError();
+  return launch_pdl(restore_rows_kernel, grid, dim3(256), 0, stream, reinterpret_cast<const uint4*>(packed),
+                    reinterpret_cast<uint4*>(padded), batch_idx, S, vec);
 }
 
 }  // namespace bt

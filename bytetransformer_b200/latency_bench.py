@@ -1,0 +1,122 @@
+"""Latency sweep over the reference's published configurations.
+
+Mirrors the reference's own benchmark loop (benchmark/bert_bench.sh:21-56): BERT-base,
+12 layers, 12 heads x 64, fp16, average valid length 0.6 x max_seq, one padded
+`[B,S,H]` batch with a `[B,S,S]` mask through the drop-in API — here the one-call stack
+`bt_stack_forward_padded` (and, with --per-layer-op, the reference's per-layer operator
+loop).  Prints one JSON line per (batch, max_seq) with milliseconds per 12-layer forward,
+valid tokens/s, algorithmic TFLOP/s and the number the reference publishes for the same
+point on an A100 (README.md:30-71) where there is one.
+
+  python -m bytetransformer_b200.latency_bench --batch 1 --seqs 64,128,...,1024
+  python -m bytetransformer_b200.latency_bench --batch 16 --seqs 512
+
+Timing: CUDA events around each forward, L2 flushed (256 MB memset) before every timed
+iteration, median of --iters after --warmup.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+# ms per 12-layer forward published by the reference (A100, README.md:30-71)
+README_MS = {
+    1: {64: 0.90, 128: 0.97, 192: 1.36, 256: 1.43, 320: 1.69, 384: 1.72, 448: 1.86, 512: 2.00, 576: 2.19,
+        640: 2.23, 704: 2.47, 768: 2.51, 832: 2.80, 896: 2.86, 960: 3.12, 1024: 3.16},
+    16: {64: 2.09, 128: 3.18, 192: 5.08, 256: 6.85, 320: 7.49, 384: 8.44, 448: 8.89, 512: 9.22, 576: 10.15,
+         640: 12.04, 704: 13.55, 768: 16.3, 832: 16.92, 896: 20.67, 960: 23.27, 1024: 24.70},
+}
+
+
+def lengths(batch: int, seq: int, seed: int):
+    """batch 1: exactly round(0.6*S); otherwise uniform in [2*avg-S, S] with avg = 0.6*S,
+    the reference's recipe (unit_test/python_scripts/bert_transformer_test.py:93-94)."""
+    avg = int(round(0.6 * seq))
+    if batch == 1:
+        return torch.tensor([avg])
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(max(1, 2 * avg - seq), seq + 1, (batch,), generator=g)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--seqs", default="512")
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--per-layer-op", action="store_true", help="call the one-layer operator 12 times, as the reference's loop")
+    ap.add_argument("--graph", action="store_true", help="replay the forward from a CUDA graph")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B)")
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    from .encoder import Encoder
+    from .workloads import BERT_BASE, attention_flops_per_layer, gemm_flops_per_layer, make_weights
+    dev = torch.device("cuda:0")
+    enc = Encoder(BERT_BASE.head_num, 64, make_weights(BERT_BASE, seed=7, device=dev))
+    if args.no_pdl:
+        from . import _abi
+        _abi.load().bt_debug_set(6, 0)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
+    H = BERT_BASE.hidden
+    for S in [int(s) for s in args.seqs.split(",")]:
+        B = args.batch
+        lens = lengths(B, S, seed=S)
+        T = int(lens.sum())
+        g = torch.Generator().manual_seed(S + 1)
+        x = torch.randn(B, S, H, generator=g).half().to(dev)
+        mask = (torch.arange(S)[None, :] < lens[:, None]).unsqueeze(1).expand(B, S, S).contiguous().half().to(dev)
+
+        def fwd():
+            if args.per_layer_op:
+                h = x
+                for l in range(BERT_BASE.layers):
+                    h = enc.forward_layer(l, h, mask)
+                return h
+            return enc.forward(x, mask)
+
+        graph = None
+        if args.graph:
+            fwd()
+            torch.cuda.synchronize()
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                fwd()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=s):
+                    out_static = fwd()
+            torch.cuda.synchronize()
+        times = []
+        for i in range(args.warmup + args.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if graph is not None:
+                graph.replay()
+            else:
+                fwd()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        fl = BERT_BASE.layers * (gemm_flops_per_layer(T, H) + attention_flops_per_layer(lens.numpy(), H))
+        ref = README_MS.get(B, {}).get(S)
+        print(json.dumps({
+            "metric": "ms_per_12_layer_forward", "batch": B, "max_seq": S, "valid_tokens": T, "value": ms,
+            "unit": "ms", "min_ms": min(times), "tokens_per_s": T / ms * 1e3, "algorithmic_tflops": fl / ms / 1e9,
+            "higher_is_better": False, "reference_a100_ms": ref, "speedup_vs_reference_a100": (ref / ms) if ref else None,
+            "api": ("per-layer operator x12" if args.per_layer_op else "one-call padded stack") + (", CUDA graph" if graph else "") + (", no PDL" if args.no_pdl else ""),
+            "l2": "flushed before every timed iteration", "data": "synthetic", "dtype": "f16"}), flush=True)
+    if enc.device_status() != 0:
+        print("device status non-zero", file=sys.stderr)
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
