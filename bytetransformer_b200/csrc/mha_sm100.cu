@@ -5,11 +5,10 @@
 // bytetransformer/src/attention_fused_long.cu:171-312 and the grouped-GEMM path
 // of bytetransformer/src/cutlass_attention.cu:150-210 for long ones).  One
 // templated kernel, two instantiations:
-//   TILES = 1  short sequences (max length <= 128): 128 query rows per CTA,
-//              192 threads, two CTAs per SM overlap each other's phases;
-//   TILES = 2  long sequences: 256 query rows per CTA as two 128-row tiles that
-//              ping-pong on the tensor core (while one tile's softmax runs, the
-//              other tile's QK^T / PV MMAs execute), 320 threads, one CTA per SM.
+//   TILES = 1  128 query rows per CTA, 192 threads, two CTAs per SM overlap each
+//              other's phases (the default: fastest at every length 64..1024);
+//   TILES = 2  256 query rows per CTA as two 128-row tiles that ping-pong on the
+//              tensor core, 320 threads, one CTA per SM (selectable).
 // Both run an online softmax over 128-key tiles, so no S x S logits ever reach
 // HBM and any length works.
 //
@@ -22,14 +21,20 @@
 //
 // Roles: warp 0 TMA loads, warp 1 tcgen05.mma issue (+ tensor-memory allocation),
 // then one warpgroup of 4 softmax warps per query tile (one query row per thread).
-//   S = Q K^T      128x128x64  -> tensor memory, 128 columns per tile
-//   P = 2^(c*S-m)  fp16, written into 128B-swizzled shared memory (A operand)
-//   O += P V       128x64x128  -> tensor memory, 64 columns per tile; V is
-//                  consumed MN-major exactly as it lies in the QKV buffer
-// O stays in tensor memory across key tiles.  The exponent reference m only
-// moves when the running maximum grows by more than 2^8 (then the O row is
-// rescaled in tensor memory); otherwise P simply grows up to 2^8, which fp16
-// holds, and the final division by the row sum makes the result exact.
+//   S = Q K^T      128x128x64, both operands from shared memory -> tensor memory,
+//                  128 fp32 columns per tile
+//   P = 2^(c*S-m)  fp16 pairs written back into tensor memory over the upper half of
+//                  S (columns 64..127, key k in cell 64 + k/2) with tcgen05.st; the
+//                  softmax walks S from the last 32-column chunk to the first, so a
+//                  cell is only overwritten after it was read
+//   O += P V       128x64x128 with the A operand (P) read from tensor memory and V
+//                  consumed MN-major from shared memory exactly as it lies in the QKV
+//                  buffer -> 64 fp32 columns per tile
+// P never touches shared memory.  O stays in tensor memory across key tiles.  The
+// exponent reference m only moves when the running maximum grows by more than a
+// threshold (then the O row is rescaled in tensor memory); otherwise P simply grows
+// up to 2^threshold, which fp16 holds, and the final division by the row sum makes
+// the result exact.
 // Keys beyond the sequence end are masked by selection (never by arithmetic on
 // the fetched values) and their V rows are zeroed in shared memory, so rows of
 // neighbouring sequences or never-written workspace cannot leak in.
@@ -44,21 +49,19 @@ constexpr int kQRows = 128;
 constexpr int kKvRows = 128;
 constexpr int kHeadDim = 64;
 constexpr int kTileBytes = 128 * kHeadDim * 2;  // 16 KiB: Q, K or V tile
-constexpr int kPBytes = kQRows * kKvRows * 2;   // 32 KiB
-constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 template <int TILES>
 struct MhaCfg {
-  static constexpr int kStages = TILES == 2 ? 3 : 2;
+  static constexpr int kStages = 3;
   static constexpr int kThreads = 64 + 128 * TILES;
   static constexpr int kSmemQ = 0;
   static constexpr int kSmemK = kSmemQ + TILES * kTileBytes;
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  static constexpr int kSmemP = kSmemV + kStages * kTileBytes;
-  static constexpr int kSmemBar = kSmemP + TILES * kPBytes;
+  static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
   static constexpr int kSmemBytes = kSmemBar + 256;
   static constexpr int kTmemCols = TILES == 2 ? 512 : 256;
   static constexpr uint32_t kTmemO = TILES * 128;  // S tiles first, then O tiles
+  static constexpr uint32_t kTmemPOff = 64;        // P aliases columns 64..127 of its S tile
   static constexpr int kMinBlocks = TILES == 2 ? 1 : 2;
 };
 
@@ -68,12 +71,24 @@ struct MhaArgs {
   int hidden;
   float scale_log2e;
   int* status;
+  long long* timing;  // diagnostics: per CTA and key-tile step, clock64 stamps (null = off)
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// two exponentials per special-function op, fp16 in / fp16 out
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -87,21 +102,48 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P, fp16 pairs) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // Row maximum of S over the valid keys.  The next 32-column chunk is requested from
 // tensor memory before the current one is reduced, so only the first load is exposed.
 template <bool MASKED>
 __device__ __forceinline__ float chunk_max(const uint32_t (&v)[32], int cbase, int kv_valid) {
-  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+  float m0 = -INFINITY, m1 = -INFINITY;
+  if (MASKED) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    m0 = fmaxf(m0, (!MASKED || cbase + i < kv_valid) ? __uint_as_float(v[i]) : -INFINITY);
-    m1 = fmaxf(m1, (!MASKED || cbase + i + 1 < kv_valid) ? __uint_as_float(v[i + 1]) : -INFINITY);
-    m2 = fmaxf(m2, (!MASKED || cbase + i + 2 < kv_valid) ? __uint_as_float(v[i + 2]) : -INFINITY);
-    m3 = fmaxf(m3, (!MASKED || cbase + i + 3 < kv_valid) ? __uint_as_float(v[i + 3]) : -INFINITY);
+    for (int i = 0; i < 32; i += 2) {
+      m0 = fmaxf(m0, (cbase + i < kv_valid) ? __uint_as_float(v[i]) : -INFINITY);
+      m1 = fmaxf(m1, (cbase + i + 1 < kv_valid) ? __uint_as_float(v[i + 1]) : -INFINITY);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+    }
   }
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  return fmaxf(m0, m1);
 }
 template <bool MASKED>
 __device__ __forceinline__ float tile_row_max(uint32_t t_s, int kv_valid) {
@@ -120,59 +162,91 @@ __device__ __forceinline__ float tile_row_max(uint32_t t_s, int kv_valid) {
   return fmaxf(mx, chunk_max<MASKED>(vb, 96, kv_valid));
 }
 
-// One 32-column chunk: p = 2^(c*s - m_ref) (0 for masked keys), partial row sums, running
-// raw maximum, fp16 pack and store into the 128B-swizzled P row.
-template <bool MASKED>
-__device__ __forceinline__ void chunk_softmax(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
-                                              uint8_t* p_row, int sw, float (&l)[4], float (&mx)[4]) {
-  float p[32];
+// One 32-column chunk of S -> 16 cells of fp16 pairs, plus this chunk's row sum.
+//   EXP16 = false: 2^x in fp32 (one special-function op per key), fp32 row sum.
+//   EXP16 = true : x is rounded to fp16 first and two exponentials share one op; the row
+//                  sum is formed from the fp16 results (pairwise tree, then fp32).
+template <bool MASKED, bool EXP16>
+__device__ __forceinline__ float chunk_probs(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
+                                             uint32_t (&out)[16]) {
+  if (EXP16) {
+    __half2 acc[4];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float s = __uint_as_float(v[i]);
-    const float e = ex2_approx(fmaf(s, c, -m_ref));
-    const bool ok = !MASKED || (cbase + i < kv_valid);
-    p[i] = ok ? e : 0.f;
-    mx[i & 3] = fmaxf(mx[i & 3], ok ? s : -INFINITY);
-    l[i & 3] += p[i];
-  }
+    for (int i = 0; i < 16; ++i) {
+      float x0 = fmaf(__uint_as_float(v[2 * i]), c, -m_ref);
+      float x1 = fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref);
+      if (MASKED) {
+        // 2^-inf = 0 for keys that do not exist
+        x0 = (cbase + 2 * i < kv_valid) ? x0 : -INFINITY;
+        x1 = (cbase + 2 * i + 1 < kv_valid) ? x1 : -INFINITY;
+      }
+      out[i] = ex2_f16x2(pack_half2(x0, x1));
+      const __half2 h = *reinterpret_cast<const __half2*>(&out[i]);
+      acc[i & 3] = (i < 4) ? h : __hadd2(acc[i & 3], h);
+    }
+    const float2 s01 = __half22float2(__hadd2(acc[0], acc[1]));
+    const float2 s23 = __half22float2(__hadd2(acc[2], acc[3]));
+    return (s01.x + s01.y) + (s23.x + s23.y);
+  } else {
+    float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-  for (int u4 = 0; u4 < 4; ++u4) {
-    const int u = (cbase >> 3) + u4;  // 16-byte unit index along the 128 keys
-    uint4 w;
-    w.x = pack_half2(p[u4 * 8 + 0], p[u4 * 8 + 1]);
-    w.y = pack_half2(p[u4 * 8 + 2], p[u4 * 8 + 3]);
-    w.z = pack_half2(p[u4 * 8 + 4], p[u4 * 8 + 5]);
-    w.w = pack_half2(p[u4 * 8 + 6], p[u4 * 8 + 7]);
-    *reinterpret_cast<uint4*>(p_row + (u >> 3) * (kQRows * 128) + (((u & 7) ^ sw) << 4)) = w;
+    for (int i = 0; i < 16; ++i) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -m_ref));
+      float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref));
+      if (MASKED) {
+        p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
+        p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
+      }
+      l0 += p0;
+      l1 += p1;
+      out[i] = pack_half2(p0, p1);
+    }
+    return l0 + l1;
   }
-}
-template <bool MASKED>
-__device__ __forceinline__ void tile_softmax(uint32_t t_s, int kv_valid, float c, float m_ref, uint8_t* p_row, int sw,
-                                             float& l_tile, float& mx_tile) {
-  float l[4] = {0.f, 0.f, 0.f, 0.f};
-  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-  uint32_t va[32], vb[32];
-  tmem_ld_32x32(t_s, va);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 32, vb);  // in flight while chunk 0 is processed
-  chunk_softmax<MASKED>(va, 0, kv_valid, c, m_ref, p_row, sw, l, mx);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 64, va);
-  chunk_softmax<MASKED>(vb, 32, kv_valid, c, m_ref, p_row, sw, l, mx);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 96, vb);
-  chunk_softmax<MASKED>(va, 64, kv_valid, c, m_ref, p_row, sw, l, mx);
-  tmem_ld_wait();
-  chunk_softmax<MASKED>(vb, 96, kv_valid, c, m_ref, p_row, sw, l, mx);
-  l_tile = (l[0] + l[1]) + (l[2] + l[3]);
-  mx_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-template <int TILES>
+// Second pass over one S tile, from the last chunk to the first; P chunk c lands in cells
+// [64 + 16c, 64 + 16c + 16) of the same tile, which lie in chunks that were already read.
+template <bool MASKED, bool EXP16>
+__device__ __forceinline__ float tile_probs(uint32_t t_s, int kv_valid, float c, float m_ref) {
+  const uint32_t t_p = t_s + 64;
+  uint32_t va[32], vb[32], pk[16];
+  float l = 0.f;
+  tmem_ld_32x32(t_s + 96, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, vb);  // in flight while chunk 3 is processed
+  l += chunk_probs<MASKED, EXP16>(va, 96, kv_valid, c, m_ref, pk);
+  tmem_ld_wait();               // chunk 2 is in registers: its cells may now be overwritten
+  tmem_st_32x16(t_p + 48, pk);
+  tmem_ld_32x32(t_s + 32, va);
+  l += chunk_probs<MASKED, EXP16>(vb, 64, kv_valid, c, m_ref, pk);
+  tmem_ld_wait();
+  tmem_st_32x16(t_p + 32, pk);
+  tmem_ld_32x32(t_s, vb);
+  l += chunk_probs<MASKED, EXP16>(va, 32, kv_valid, c, m_ref, pk);
+  tmem_ld_wait();
+  tmem_st_32x16(t_p + 16, pk);
+  l += chunk_probs<MASKED, EXP16>(vb, 0, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p, pk);
+  tmem_st_wait();
+  return l;
+}
+
+__device__ __forceinline__ void stamp(long long* timing, int j, int slot) {
+  if (timing != nullptr && j < 8) {
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < 4096) timing[(static_cast<size_t>(cta) * 8 + j) * 8 + slot] = clock64();
+  }
+}
+
+template <int TILES, bool EXP16>
 __global__ void __launch_bounds__(MhaCfg<TILES>::kThreads, MhaCfg<TILES>::kMinBlocks)
 mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   using Cfg = MhaCfg<TILES>;
   constexpr int kStages = Cfg::kStages;
+  // With fp16 exponents the reference may lag the running maximum by at most 2^1 (keeps the
+  // rounding of the exponent small); with fp32 exponents by 2^8.
+  constexpr float kRescaleThreshold = EXP16 ? 1.0f : 8.0f;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   pdl_launch_dependents();
@@ -258,7 +332,7 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      // K-major operands (Q, K, P): 8-row groups 1024 B apart.
+      // K-major operands (Q, K): 8-row groups 1024 B apart.
       constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
       // V: MN-major, one 64-wide chunk (LBO unused), 8-key groups 1024 B apart.
       constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
@@ -267,7 +341,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
       const uint32_t s_q = smem_u32(smem + Cfg::kSmemQ);
       const uint32_t s_k = smem_u32(smem + Cfg::kSmemK);
       const uint32_t s_v = smem_u32(smem + Cfg::kSmemV);
-      const uint32_t s_p = smem_u32(smem + Cfg::kSmemP);
       auto issue_s = [&](int t, int stage) {
         const uint32_t sq = s_q + t * kTileBytes;
         const uint32_t sk = s_k + stage * kTileBytes;
@@ -278,14 +351,12 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t sp = s_p + t * kPBytes;
+        const uint32_t tp = tmem_base + t * 128 + Cfg::kTmemPOff;  // 8 cells (16 keys) per MMA
         const uint32_t sv = s_v + stage * kTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < kKvRows / 16; ++kk) {
-          const uint32_t pa = sp + (kk >> 2) * (kQRows * 128) + (kk & 3) * 32;
-          umma_f16_ss(tmem_base + Cfg::kTmemO + t * 64, smem_desc(kDescK, pa), smem_desc(kDescV, sv + kk * 2048),
-                      kIdescO, (accumulate || kk != 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kKvRows / 16; ++kk)
+          umma_f16_ts(tmem_base + Cfg::kTmemO + t * 64, tp + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
+                      (accumulate || kk != 0) ? 1u : 0u);
       };
       bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t)
@@ -302,8 +373,10 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         const int st_n = (st + 1 == kStages) ? 0 : st + 1;
         const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
         const bool more = j + 1 < n_kv;
-        // ---- tile 0: O0 += P0 V(j), then S0(j+1)
+        // ---- tile 0: O0 += P0 V(j), then S0(j+1).  The MMAs of one thread execute in issue
+        // order, so S0(j+1) cannot overwrite P0(j) (same columns) before PV0(j) has read it.
         if (!mbar_wait_bounded(&p_full[0], jpar, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+        stamp(args.timing, j, 4);
         if (!mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
         tc_fence_after();
         issue_pv(0, st, j > 0);
@@ -320,6 +393,7 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         }
         umma_commit(&kv_empty[st]);  // every MMA that reads K/V stage `st` has been issued
         if (n_tiles == 2 && more) issue_s(1, st_n);
+        stamp(args.timing, j, 5);
         st = st_n;
         ph = ph_n;
       }
@@ -337,8 +411,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
       const float c = args.scale_log2e;
       float m_ref = -INFINITY;  // exponent reference, in log2 units
       float l_run = 0.f;
-      uint8_t* p_row = smem + Cfg::kSmemP + t * kPBytes + r * 128;
-      const int sw = r & 7;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -351,18 +423,13 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           break;
         }
         tc_fence_after();
-        // The exponent reference m_ref is known from earlier key tiles (for the first
-        // tile it is this tile's own row maximum), so one pass over S suffices: it
-        // computes 2^(c*s - m_ref), the row sum AND the row maximum.  Only if the maximum
-        // outgrew m_ref by more than 2^8 is the O row rescaled and the pass repeated.
-        if (j == 0) m_ref = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
-        float l_tile, mx_tile;
-        if (full_tile)
-          tile_softmax<false>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
-        else
-          tile_softmax<true>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
-        if (j > 0) {
-          const float m_new = fmaxf(m_ref, mx_tile * c);
+        if (warp == 2 && lane == 0) stamp(args.timing, j, 0);
+        // pass 1: row maximum (scaled to log2 units)
+        const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
+        if (j == 0) {
+          m_ref = mx;
+        } else {
+          const float m_new = fmaxf(m_ref, mx);
           const bool need = (m_new - m_ref) > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
             // the PV of the previous key tile has retired (S of this tile was issued after it)
@@ -376,16 +443,14 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
               for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
               tmem_st_32x32(t_o + cb, v);
             }
-            tmem_st_wait();
             l_run *= f;
             m_ref = m_new;
-            if (full_tile)
-              tile_softmax<false>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
-            else
-              tile_softmax<true>(t_s, kv_valid, c, m_ref, p_row, sw, l_tile, mx_tile);
           }
         }
-        l_run += l_tile;
+        if (warp == 2 && lane == 0) stamp(args.timing, j, 1);
+        // pass 2: probabilities -> fp16 pairs -> tensor memory (over S), row sum
+        l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
+                           : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
         if (!full_tile && t == 0) {
           // tail tile: blank the V rows of keys that do not belong to this sequence
           // (tile 0's PV is issued before tile 1's, so tile 0's warpgroup does it for both)
@@ -398,8 +463,9 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
           }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
+        if (warp == 2 && lane == 0) stamp(args.timing, j, 2);
         tc_fence_before();
         mbar_arrive(&p_full[t]);
         if (++stage == kStages) {
@@ -446,24 +512,27 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   }
 }
 
-template <int TILES>
+template <int TILES, bool EXP16>
 cudaError_t launch_tiles(const MhaLaunch& a, const MhaArgs& args, cudaStream_t stream) {
   using Cfg = MhaCfg<TILES>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(mha_fwd_kernel<TILES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(mha_fwd_kernel<TILES, EXP16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
   const int rows_per_cta = kQRows * TILES;
   dim3 grid((a.max_len + rows_per_cta - 1) / rows_per_cta, a.head_num, a.batch);
-  return launch_pdl(mha_fwd_kernel<TILES>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
+  return launch_pdl(mha_fwd_kernel<TILES, EXP16>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
 }
 
 long long g_dbg_force_tiles = 0;
+long long* g_dbg_timing = nullptr;
+constexpr int kTimingCtas = 4096, kTimingSteps = 8, kTimingSlots = 8;
+long long g_dbg_exp16 = 0;  // 0 = default (fp32 exponentials), 1 = fp16x2 exponentials
 
 }  // namespace
 
@@ -475,19 +544,31 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.hidden = a.hidden;
   args.scale_log2e = a.scale_log2e;
   args.status = a.status;
+  args.timing = g_dbg_timing;
   // Measured on B200 (18.9k packed tokens, 12 heads): the one-tile variant with two
-  // co-resident CTAs per SM is faster at every length from 64 to 1024 (404 vs 372
-  // TFLOP/s at 1024), so it is the default; the two-tile variant stays selectable.
+  // co-resident CTAs per SM is faster at every length from 64 to 1024, so it is the
+  // default; the two-tile variant stays selectable.
   int tiles = 1;
   if (g_dbg_force_tiles == 1 || g_dbg_force_tiles == 2) tiles = static_cast<int>(g_dbg_force_tiles);
-  return tiles == 1 ? launch_tiles<1>(a, args, stream) : launch_tiles<2>(a, args, stream);
+  const bool exp16 = g_dbg_exp16 == 1;
+  if (tiles == 1) return exp16 ? launch_tiles<1, true>(a, args, stream) : launch_tiles<1, false>(a, args, stream);
+  return exp16 ? launch_tiles<2, true>(a, args, stream) : launch_tiles<2, false>(a, args, stream);
 }
 
 }  // namespace bt
 
-// Diagnostics hook (not part of the stable ABI): 0 = choose by max length,
-// 1 / 2 = force the short / long attention variant.
+// Diagnostics hooks (not part of the stable ABI): attention variant (0 = default,
+// 1 / 2 = one / two query tiles per CTA) and exponential flavour (0 = fp32, 1 = fp16x2).
 extern "C" int bt_debug_set_mha_tiles(long long tiles) {
   bt::g_dbg_force_tiles = tiles;
+  return 0;
+}
+// Device buffer of 4096 CTAs x 8 steps x 8 slots of long long for clock64 stamps (null = off).
+extern "C" int bt_debug_set_mha_timing(long long* device_buffer) {
+  bt::g_dbg_timing = device_buffer;
+  return 0;
+}
+extern "C" int bt_debug_set_mha_exp16(long long on) {
+  bt::g_dbg_exp16 = on;
   return 0;
 }

@@ -336,3 +336,29 @@ def test_gemm_pair_twice_bit_identical_and_equal_to_single(enc, cuda_device):
         lib.bt_debug_set(5, 0)
     assert torch.equal(o1, o2)
     assert torch.equal(o1, o3)          # same accumulation order: K is walked identically
+
+
+@pytest.mark.parametrize("tiles,exp16", [(1, 0), (2, 0), (1, 1), (2, 1)])
+def test_attention_variants(enc, cuda_device, tiles, exp16):
+    """Both tilings (one / two query tiles per CTA) and both exponential flavours (fp32, and
+    fp16x2 where two exponentials share one special-function op) against the oracle."""
+    from bytetransformer_b200 import _abi
+    from oracle.bert_oracle import attention_packed
+    lib = _abi.load()
+    lens = [300, 1, 128, 77, 513, 129, 1024, 64]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T = int(cu[-1])
+    g = torch.Generator().manual_seed(4242)
+    qkv = (torch.randn(T, 3 * enc.hidden, generator=g) * 1.5).half()   # logits with std ~ 2.8: sharp softmax
+    want = attention_packed(qkv.float(), cu.tolist(), enc.head_num, enc.head_size)
+    lib.bt_debug_set_mha_tiles(tiles)
+    lib.bt_debug_set_mha_exp16(exp16)
+    try:
+        got = enc.attention(qkv.to(cuda_device), torch.from_numpy(cu).to(cuda_device), max(lens))
+        got2 = enc.attention(qkv.to(cuda_device), torch.from_numpy(cu).to(cuda_device), max(lens))
+    finally:
+        lib.bt_debug_set_mha_tiles(0)
+        lib.bt_debug_set_mha_exp16(0)
+    assert torch.equal(got, got2)
+    mx, mn = assert_close_fp16(got, want, f"attention tiles{tiles} exp16={exp16}", max_abs=8e-3, mean_abs=4e-4)
+    print(f"attention tiles{tiles} exp16={exp16}: max-abs {mx:.3e} mean-abs {mn:.3e}")
