@@ -25,6 +25,7 @@ BT_EPI_BIAS = 1
 BT_EPI_BIAS_GELU = 2
 BT_EPI_BIAS_RESIDUAL = 3
 BT_EPI_BIAS_RESIDUAL_F32OUT = 4
+BT_EPI_BIAS_RESIDUAL_LAYERNORM = 5
 BT_STATIC_SCRATCH_BYTES = 48 * 1024 * 1024
 
 ERROR_NAMES = {0: "BT_OK", 1: "BT_ERR_INVALID_ARG", 2: "BT_ERR_WORKSPACE", 3: "BT_ERR_CUDA",
@@ -65,6 +66,7 @@ SIGNATURES = {
     "bt_pack_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_restore_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "bt_gemm_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_add_bias_residual_layernorm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _vp]),
     "bt_add_bias_residual_layernorm_restore": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp]),

@@ -81,6 +81,13 @@ struct GemmArgs {
   int K;
   int gelu_kind;
   int* status;
+  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is the fp32 scratch of the
+  // pre-normalisation sum, `out_ln` the fp16 result
+  __half* out_ln;
+  const void* gamma;
+  const void* beta;
+  int gb_fp32;
+  float eps;
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
   uint32_t a_kstep_bytes;
@@ -107,10 +114,11 @@ __device__ __forceinline__ void tma_store_wait_read_n() {
 template <int TILE_N, int EPI, bool TMA_STORE, int STG_BUFS>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtensorMap* tm_out, uint8_t* stg,
                                               uint32_t tmem_acc, int m0, int n0, int M, int quarter, int col_half,
-                                              int lane, const uint4* resv) {
+                                              int lane, const uint4* resv, float& rsum, float& rsq) {
   constexpr int kColsPerWarp = TILE_N / 2;
-  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kLn = (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
+  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
   // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
   constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
   constexpr int kNChunks = kColsPerWarp / kChunk;
@@ -175,6 +183,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
         }
       }
     }
+    if (kLn) {
+      // running row statistics of the pre-normalisation sum (this thread's columns)
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) {
+        rsum += v[i];
+        rsq = fmaf(v[i], v[i], rsq);
+      }
+    }
     // 8 (or 4) units of 16 bytes per row
     constexpr int kUnits = kF32Out ? 8 : kChunk / 8;
     uint4 units[kUnits];
@@ -222,7 +238,8 @@ template <int TILE_N, int EPI>
 __device__ __forceinline__ void prefetch_residual(const GemmArgs& args, int m0, int n0, int M, int quarter,
                                                   int col_half, int lane, uint4* resv) {
   constexpr int kColsPerWarp = TILE_N / 2;
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT ||
+                                 EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
   if (kHasResidual) {
     const int row = m0 + quarter * 32 + lane;
     const bool row_ok = row < M;
@@ -242,7 +259,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kLn = (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -297,6 +315,23 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = args.K / kBlockK;
+  // The li-th tile of this CTA.  Normally tiles go round-robin over the CTAs; with the fused
+  // LayerNorm a CTA takes whole 128-row tiles and walks all their column tiles in a row, so
+  // that it sees complete rows and needs no exchange with other CTAs for the statistics.
+  auto tile_at = [&](int li, int& m0, int& n0) -> bool {
+    if (kLn) {
+      const int mt = static_cast<int>(blockIdx.x) + (li / n_tiles) * static_cast<int>(gridDim.x);
+      if (mt >= m_tiles) return false;
+      m0 = mt * kBlockM;
+      n0 = (li % n_tiles) * BLOCK_N;
+      return true;
+    }
+    const int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
+    if (tile >= total_tiles) return false;
+    m0 = (tile / n_tiles) * kBlockM;
+    n0 = (tile % n_tiles) * BLOCK_N;
+    return true;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -304,9 +339,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * kBlockM;
-        const int n0 = (tile % n_tiles) * BLOCK_N;
+      int m0 = 0, n0 = 0;
+      for (int li = 0; ok && tile_at(li, m0, n0); ++li) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
                                  kStatusGemmProducerTimeout)) {
@@ -332,9 +366,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      int m0 = 0, n0 = 0;
+      for (int it = 0; ok && tile_at(it, m0, n0); ++it) {
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait_bounded(&acc_empty[as], aphase ^ 1u, abort_flag, args.status, kStatusGemmMmaTimeout)) {
@@ -372,10 +406,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int col_half = e >> 2;   // which half of the tile's columns
     uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;  // 32 rows x 128 B, swizzled
-    int it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      const int m0 = (tile / n_tiles) * kBlockM;
-      const int n0 = (tile % n_tiles) * BLOCK_N;
+    float rsum = 0.f, rsq = 0.f;  // fused LayerNorm: statistics of this thread's row over the tiles seen so far
+    int m0 = 0, n0 = 0;
+    for (int it = 0; tile_at(it, m0, n0); ++it) {
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       uint4 resv[kHasResidual ? BLOCK_N / 16 : 1];
@@ -383,10 +416,89 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
       epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore, 1>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
-                                                  col_half, lane, resv);
+                                                  col_half, lane, resv, rsum, rsq);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
+      if (kLn && n0 + BLOCK_N == args.N) {
+        // ---- LayerNorm of the 128 rows just completed.  The fp32 sums were written to the
+        // scratch tensor a moment ago (they are read back from L2), the row statistics are
+        // exchanged through the warps' staging buffers.
+        if (lane == 0) {
+          tma_store_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        __syncwarp();
+        reinterpret_cast<float2*>(stg)[lane] = make_float2(rsum, rsq);
+        rsum = 0.f;
+        rsq = 0.f;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int N = args.N;
+        const int nvec = N >> 2;                      // float4 per row
+        constexpr int kMaxIt = 8;                     // N <= 1024
+        const float inv_n = 1.0f / static_cast<float>(N);
+        const uint8_t* stg0 = smem + kStages * Cfg::kStageBytes;
+        // one row per pass keeps the kernel inside its 168-register budget (320 threads are
+        // allocated like 384); more rows in flight were measured too: no gain.
+        constexpr int kRowsPerPass = 1;
+        for (int rr = 0; rr < 16; rr += kRowsPerPass) {
+          float4 x[kRowsPerPass][kMaxIt];
+          float mean[kRowsPerPass], rstd[kRowsPerPass];
+#pragma unroll
+          for (int k = 0; k < kRowsPerPass; ++k) {
+            const int rt = e * 16 + rr + k;  // row inside the 128-row tile
+            const int grow = m0 + rt;
+            // the two warps that own this row's TMEM lane quarter (left / right column half)
+            const int ew = (((rt >> 5) + 2) & 3);
+            const float2 s0 = reinterpret_cast<const float2*>(stg0 + ew * kStagingBytesPerWarp)[rt & 31];
+            const float2 s1 = reinterpret_cast<const float2*>(stg0 + (ew + 4) * kStagingBytesPerWarp)[rt & 31];
+            mean[k] = (s0.x + s1.x) * inv_n;
+            const float var = fmaxf((s0.y + s1.y) * inv_n - mean[k] * mean[k], 0.f);
+            rstd[k] = rsqrtf(var + args.eps);
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(args.out) +
+                                                                static_cast<size_t>(grow) * N);
+#pragma unroll
+            for (int q = 0; q < kMaxIt; ++q) {
+              const int v = q * 32 + lane;
+              if (v < nvec && grow < M) x[k][q] = __ldcg(src + v);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < kMaxIt; ++q) {
+            const int v = q * 32 + lane;
+            if (v < nvec) {
+              float g[4], bt_[4];  // gamma / beta of these four columns
+              if (args.gb_fp32) {
+                const float4 a = __ldg(reinterpret_cast<const float4*>(args.gamma) + v);
+                const float4 b = __ldg(reinterpret_cast<const float4*>(args.beta) + v);
+                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+                bt_[0] = b.x; bt_[1] = b.y; bt_[2] = b.z; bt_[3] = b.w;
+              } else {
+                const uint2 a = __ldg(reinterpret_cast<const uint2*>(args.gamma) + v);
+                const uint2 b = __ldg(reinterpret_cast<const uint2*>(args.beta) + v);
+                const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x));
+                const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+                const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x));
+                const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
+                g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
+                bt_[0] = b0.x; bt_[1] = b0.y; bt_[2] = b1.x; bt_[3] = b1.y;
+              }
+#pragma unroll
+              for (int k = 0; k < kRowsPerPass; ++k) {
+                const int grow = m0 + e * 16 + rr + k;
+                if (grow < M) {
+                  const float4 xv = x[k][q];
+                  uint2 o;
+                  o.x = pack_half2(fmaf((xv.x - mean[k]) * rstd[k], g[0], bt_[0]), fmaf((xv.y - mean[k]) * rstd[k], g[1], bt_[1]));
+                  o.y = pack_half2(fmaf((xv.z - mean[k]) * rstd[k], g[2], bt_[2]), fmaf((xv.w - mean[k]) * rstd[k], g[3], bt_[3]));
+                  reinterpret_cast<uint2*>(args.out_ln + static_cast<size_t>(grow) * N)[v] = o;
+                }
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // staging buffers may be reused
+      }
     }
     if (Cfg::kTmaStore && lane == 0) tma_store_wait_all();  // staging rows must outlive the last bulk store
   }
@@ -613,8 +725,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       prefetch_residual<kTileN, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
-      epilogue_tile<kTileN, EPI, true, Cfg::kStagingBufs>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M, quarter, col_half,
-                                       lane, resv);
+      float unused_sum = 0.f, unused_sq = 0.f;
+      epilogue_tile<kTileN, EPI, true, Cfg::kStagingBufs>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M,
+                                                          quarter, col_half, lane, resv, unused_sum, unused_sq);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[as]), 0));
@@ -652,6 +765,7 @@ cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   const int n_tiles = g.N / BLOCK_N;
   const int m_tiles = (g.m_rows + kBlockM - 1) / kBlockM;
   long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+  if (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM) tiles = m_tiles;  // a CTA owns whole row tiles
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
   return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
@@ -719,6 +833,7 @@ cudaError_t launch_pair_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t
 // The pair kernel needs N % 256 == 0 and pays off once every SM pair gets at least two
 // 256 x 256 tiles (below that the narrower one-CTA tiles fill the machine better).
 bool use_pair_kernel(const GemmLaunch& g) {
+  if (g.epilogue == BT_EPI_BIAS_RESIDUAL_LAYERNORM) return false;
   if (g_dbg_pair_mode == 1) return g.N % 256 == 0;
   if (g_dbg_pair_mode == 2 || g_dbg_force_block_n != 0 || g.block_n != 0) return false;
   if (g.N % 256 != 0) return false;
@@ -759,6 +874,11 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.K = g.K;
   a.gelu_kind = g.gelu_kind;
   a.status = g.status;
+  a.out_ln = g.out_ln;
+  a.gamma = g.gamma;
+  a.beta = g.beta;
+  a.gb_fp32 = g.gb_fp32 ? 1 : 0;
+  a.eps = g.eps;
   // A: K-major, 128B swizzle, 8-row groups 1024 B apart; 16 K-elements = 32 B.
   a.a_desc_hi = make_smem_desc_hi(16, 1024);
   a.a_kstep_bytes = 32;
@@ -771,6 +891,12 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   if (use_pair_kernel(g)) {
     a.idesc = make_idesc_f16(256, 256, 0, 1);  // M = 256 across the pair
     return launch_pair_epi(g, a, stream);
+  }
+  if (g.epilogue == BT_EPI_BIAS_RESIDUAL_LAYERNORM) {
+    // whole rows per CTA: 256-wide tiles, N <= 1024 (row statistics and gamma/beta live in registers)
+    if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta) return cudaErrorInvalidValue;
+    a.idesc = make_idesc_f16(kBlockM, 256, 0, 1);
+    return launch_one<256, BT_EPI_BIAS_RESIDUAL_LAYERNORM>(g, a, stream);
   }
   int bn = g.block_n != 0 ? g.block_n : gemm_pick_block_n(g.m_rows, g.N, g.num_sms);
   if (bn == 0 || g.N % bn != 0) return cudaErrorInvalidValue;

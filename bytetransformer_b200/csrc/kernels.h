@@ -59,6 +59,12 @@ struct GemmLaunch {
   int m_rows;        // rows allocated in A / out / residual (upper bound of M)
   int N;
   int K;
+  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is the fp32 scratch [m_rows, N]
+  __half* out_ln = nullptr;
+  const void* gamma = nullptr;
+  const void* beta = nullptr;
+  bool gb_fp32 = false;
+  float eps = 1e-6f;
   int epilogue;      // BT_EPI_*
   int gelu_kind;     // BT_GELU_*
   int block_n;       // 64, 128 or 256; 0 = choose from the shape

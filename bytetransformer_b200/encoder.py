@@ -202,6 +202,18 @@ class Encoder:
                    _stream_ptr(a.device))
         return out
 
+    def gemm_layernorm(self, a, w, bias, residual, gamma, beta, eps=1e-6, m_dev=None) -> torch.Tensor:
+        """LayerNorm(a @ w + bias + residual) * gamma + beta in one kernel (bt_gemm_layernorm)."""
+        M, K = a.shape
+        N = w.shape[1]
+        scratch = torch.empty(M, N, dtype=torch.float32, device=a.device)
+        out = torch.zeros(M, N, dtype=torch.float16, device=a.device)
+        self._call("bt_gemm_layernorm", self._h, a.data_ptr(), w.data_ptr(), bias.data_ptr(), residual.data_ptr(),
+                   gamma.data_ptr(), beta.data_ptr(), int(gamma.dtype == torch.float32), float(eps),
+                   scratch.data_ptr(), out.data_ptr(), m_dev.data_ptr() if m_dev is not None else None,
+                   int(M), int(N), int(K), _stream_ptr(a.device))
+        return out
+
     def attention(self, qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int) -> torch.Tensor:
         _check(qkv, "qkv", torch.float16)
         _check(cu_seqlens, "cu_seqlens", torch.int32)

@@ -45,6 +45,7 @@ extern "C" {
 #define BT_EPI_BIAS_GELU 2     /* out = gelu(A*W + bias)            */
 #define BT_EPI_BIAS_RESIDUAL 3 /* out = A*W + bias + residual       */
 #define BT_EPI_BIAS_RESIDUAL_F32OUT 4 /* same, but `out` is float[M,N]: the pre-LayerNorm sum keeps fp32 */
+#define BT_EPI_BIAS_RESIDUAL_LAYERNORM 5 /* LN(A*W + bias + residual): only through bt_gemm_layernorm() */
 
 typedef struct bt_encoder_s* bt_handle;
 
@@ -181,6 +182,17 @@ int bt_restore_rows(const void* packed, void* padded, const int* batch_idx, int 
 int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bias,
             const void* residual, const int* m_dev, int m_rows, int N, int K, int epilogue,
             int gelu_kind, void* stream);
+
+/* The attention-output / FFN-output step as ONE kernel: `dense_layer_kernel_launcher`
+ * followed by `add_bias_input_layernorm_kernel_launcher`
+ * (bytetransformer/src/bert_transformer.cu:102-109 and :115-129):
+ * out[M,N] = LayerNorm(A[M,K] * W[K,N] + bias + residual) * gamma + beta.
+ * `scratch_f32` is float[m_rows, N] (the pre-normalisation sum in fp32, written and read
+ * back by the same CTA).  N % 256 == 0, N <= 1024, K % 64 == 0. */
+int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bias, const void* residual,
+                      const void* gamma, const void* beta, int gamma_beta_fp32, float eps,
+                      void* scratch_f32, void* out, const int* m_dev, int m_rows, int N, int K,
+                      void* stream);
 
 /* `Attention<HALF>::infer` (bytetransformer/include/attention.h:124-139; packed
  * kernels src/attention_fused.cu:295-414, src/attention_fused_long.cu:171-312):

@@ -163,7 +163,10 @@ def test_packed_entry_matches_padded(cuda_device):
     xp = pack_rows(x, bi)[:T].contiguous()
     outp = enc.forward_packed(xp, bi, max(lens))
     v = _valid(lens, S)
-    assert torch.equal(outp.cpu(), padded.cpu()[v])
+    # same kernels except the last LayerNorm (padded: separate kernel with scatter, two-pass variance;
+    # packed: may be fused into the GEMM, one-pass variance): equal up to an fp16 ulp or two
+    d = (outp.cpu().float() - padded.cpu()[v].float()).abs()
+    assert d.max().item() <= 4e-3 and d.mean().item() <= 2e-5, (d.max().item(), d.mean().item())
     assert enc.device_status() == 0
     enc.close()
 

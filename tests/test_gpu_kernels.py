@@ -362,3 +362,32 @@ def test_attention_variants(enc, cuda_device, tiles, exp16):
     assert torch.equal(got, got2)
     mx, mn = assert_close_fp16(got, want, f"attention tiles{tiles} exp16={exp16}", max_abs=8e-3, mean_abs=4e-4)
     print(f"attention tiles{tiles} exp16={exp16}: max-abs {mx:.3e} mean-abs {mn:.3e}")
+
+
+@pytest.mark.parametrize("M,N,K,gb32,m_valid", [
+    (128, 256, 64, False, None), (333, 768, 768, False, None), (1000, 768, 3072, True, None),
+    (18944, 768, 768, False, None), (700, 1024, 1024, True, 555), (40000, 768, 768, False, 39999), (130, 512, 128, False, 0),
+])
+def test_gemm_with_fused_layernorm(enc, cuda_device, M, N, K, gb32, m_valid):
+    """bt_gemm_layernorm: GEMM + bias + residual + LayerNorm in one kernel (a CTA owns whole rows)."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(K, N, generator=g) * 0.05).half()
+    bias = torch.empty(N).uniform_(-0.4, 0.4, generator=g).half()
+    res = (torch.randn(M, N, generator=g) + 0.5).half()          # non-zero mean exercises the one-pass variance
+    gamma = torch.empty(N).uniform_(0.5, 1.5, generator=g)
+    beta = torch.empty(N).uniform_(-0.4, 0.4, generator=g)
+    gd, bd = (gamma, beta) if gb32 else (gamma.half(), beta.half())
+    m_dev = None if m_valid is None else torch.tensor([m_valid], dtype=torch.int32, device=cuda_device)
+    args = [t.to(cuda_device) for t in (a, w, bias, res, gd, bd)]
+    got = enc.gemm_layernorm(*args, eps=1e-6, m_dev=m_dev)
+    got2 = enc.gemm_layernorm(*args, eps=1e-6, m_dev=m_dev)
+    assert torch.equal(got, got2)
+    mv = M if m_valid is None else m_valid
+    rows = slice(0, mv) if mv <= 4096 else torch.cat([torch.arange(0, 2048), torch.arange(mv - 2048, mv)])
+    pre = a[rows].float() @ w.float() + bias.float() + res[rows].float()
+    want = torch.nn.functional.layer_norm(pre, (N,), gd.float(), bd.float(), eps=1e-6)
+    assert_close_fp16(got.cpu()[rows], want, f"gemm+ln {M}x{N}x{K}", max_abs=6e-3, mean_abs=4e-4)
+    if mv < M:
+        assert got[mv:].abs().max().item() == 0.0
+    assert enc.device_status() == 0
