@@ -512,6 +512,339 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Persistent variant: each CTA (192 threads, two per SM) walks a static list of work items
+// (sequence, 128-row query tile, head), item n going to CTA n mod gridDim.x.  Barriers,
+// tensor memory and the launch are paid once per CTA instead of once per item, and the
+// loader runs ahead: the next item's Q/K/V tiles are requested while the current item's last
+// key tiles are still being processed.  Per item the work is exactly that of
+// mha_fwd_kernel<1> (same tile_row_max / tile_probs, same MMAs).
+// ------------------------------------------------------------------------------------------
+struct MhaPersistentArgs {
+  __half* ctx;
+  const int* batch_idx;
+  int batch;
+  int heads;
+  int hidden;
+  float scale_log2e;
+  int* status;
+};
+
+// Finds item n = (sequence b, query tile qt, head h); items are numbered sequence by
+// sequence, inside a sequence query tile by query tile, heads fastest.  `cur_b` / `cur_first`
+// is the caller's cursor (first item index of sequence cur_b); n never decreases.
+__device__ __forceinline__ bool decode_item(const int* __restrict__ batch_idx, int B, int heads, int n, int& cur_b,
+                                            int& cur_first, int& seq_start, int& L, int& qt, int& h) {
+  while (cur_b < B) {
+    seq_start = __ldg(batch_idx + cur_b);
+    L = __ldg(batch_idx + cur_b + 1) - seq_start;
+    const int items = ((L + kQRows - 1) / kQRows) * heads;
+    if (n < cur_first + items) {
+      const int r = n - cur_first;
+      qt = r / heads;
+      h = r - qt * heads;
+      return true;
+    }
+    cur_first += items;
+    ++cur_b;
+  }
+  return false;
+}
+
+template <bool EXP16>
+__global__ void __launch_bounds__(192, 2)
+mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {
+  constexpr int kStages = 3;
+  constexpr int kSmemQ = 0;
+  constexpr int kSmemK = kSmemQ + kTileBytes;
+  constexpr int kSmemV = kSmemK + kStages * kTileBytes;
+  constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+  constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 128;
+  constexpr float kRescaleThreshold = EXP16 ? 1.0f : 8.0f;
+  extern __shared__ __align__(1024) uint8_t smem[];
+
+  pdl_launch_dependents();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* k_full = bars + 2;                  // [kStages]
+  uint64_t* v_full = bars + 2 + kStages;        // [kStages]
+  uint64_t* kv_empty = bars + 2 + 2 * kStages;  // [kStages]
+  uint64_t* s_full = bars + 2 + 3 * kStages;
+  uint64_t* p_full = bars + 3 + 3 * kStages;
+  uint64_t* o_done = bars + 4 + 3 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + 3 * kStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool smem_ok = (smem_u32(smem) & 1023u) == 0u;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = smem_ok ? 0 : 1;
+    fence_mbar_init();
+    if (!smem_ok && args.status != nullptr) atomicCAS(args.status, 0, kStatusMhaLoadTimeout + 0x10);
+    tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // batch_idx and the QKV buffer come from earlier kernels
+
+  const int B = args.batch, heads = args.heads;
+  int cur_b = 0, cur_first = 0, seq_start = 0, L = 0, qt = 0, head = 0;
+
+  if (!smem_ok) {
+    // fall through to the teardown
+  } else if (warp == 0) {
+    // ------------------------------------------------------------------ loads
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t item = 0;
+      bool ok = true;
+      for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
+           n += gridDim.x, ++item) {
+        const int n_kv = (L + kKvRows - 1) / kKvRows;
+        if (!mbar_wait_bounded(q_empty, (item & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) break;
+        mbar_arrive_expect_tx(q_full, kTileBytes);
+        tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, head * kHeadDim, seq_start + qt * kQRows);
+        for (int j = 0; j < n_kv; ++j) {
+          if (!mbar_wait_bounded(&kv_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
+            ok = false;
+            break;
+          }
+          const int row = seq_start + j * kKvRows;
+          mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
+          tma_load_2d(smem + kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], args.hidden + head * kHeadDim, row);
+          mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
+          tma_load_2d(smem + kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], 2 * args.hidden + head * kHeadDim,
+                      row);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
+      constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
+      constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
+      constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
+      const uint32_t s_q = smem_u32(smem + kSmemQ);
+      const uint32_t s_k = smem_u32(smem + kSmemK);
+      const uint32_t s_v = smem_u32(smem + kSmemV);
+      auto issue_s = [&](int stage) {
+        const uint32_t sk = s_k + stage * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < kHeadDim / 16; ++k)
+          umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
+                      k != 0 ? 1u : 0u);
+        umma_commit(s_full);
+      };
+      int st = 0;
+      uint32_t ph = 0;
+      uint32_t step = 0, item = 0;
+      bool ok = true;
+      for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
+           n += gridDim.x, ++item) {
+        const int n_kv = (L + kKvRows - 1) / kKvRows;
+        if (!mbar_wait_bounded(q_full, item & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+        if (!mbar_wait_bounded(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+        tc_fence_after();
+        issue_s(st);
+        if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
+        for (int j = 0; j < n_kv; ++j, ++step) {
+          const int st_n = (st + 1 == kStages) ? 0 : st + 1;
+          const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
+          // P of this step is ready; it also tells that the softmax warps have finished the
+          // previous item's O read-out, so the first PV of an item may overwrite O.
+          if (!mbar_wait_bounded(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
+              !mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sv = s_v + st * kTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < kKvRows / 16; ++kk)
+            umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
+                        (j > 0 || kk != 0) ? 1u : 0u);
+          if (j + 1 < n_kv) {
+            if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(st_n);  // executes after the PV above (issue order), so P is not overwritten early
+            if (j + 2 == n_kv) umma_commit(q_empty);
+          }
+          umma_commit(&kv_empty[st]);
+          st = st_n;
+          ph = ph_n;
+        }
+        if (ok) umma_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t t_s = t_lane + kTmemS;
+    const uint32_t t_o = t_lane + kTmemO;
+    const float c = args.scale_log2e;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t step = 0, item = 0;
+    bool ok = true;
+    for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
+         n += gridDim.x, ++item) {
+      const int n_kv = (L + kKvRows - 1) / kKvRows;
+      float m_ref = -INFINITY;
+      float l_run = 0.f;
+      for (int j = 0; j < n_kv; ++j, ++step) {
+        const int kv_valid = min(kKvRows, L - j * kKvRows);
+        const bool full_tile = kv_valid == kKvRows;
+        if (!mbar_wait_bounded(s_full, step & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
+        if (j == 0) {
+          m_ref = mx;
+        } else {
+          const float m_new = fmaxf(m_ref, mx);
+          const bool need = (m_new - m_ref) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float f = ex2_approx(m_ref - m_new);
+#pragma unroll
+            for (int cb = 0; cb < kHeadDim; cb += 32) {
+              uint32_t v[32];
+              tmem_ld_32x32(t_o + cb, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+              tmem_st_32x32(t_o + cb, v);
+            }
+            l_run *= f;
+            m_ref = m_new;
+          }
+        }
+        l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
+                           : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
+        if (!full_tile) {
+          // tail tile: blank the V rows of keys that do not belong to this sequence
+          if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+            ok = false;
+            break;
+          }
+          if (r >= kv_valid) {
+            uint4* vr = reinterpret_cast<uint4*>(smem + kSmemV + stage * kTileBytes + r * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async_smem();
+        }
+        tc_fence_before();
+        mbar_arrive(p_full);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok || !mbar_wait_bounded(o_done, item & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int q_row = qt * kQRows + r;
+      const float inv = 1.0f / l_run;
+      uint4* dst = reinterpret_cast<uint4*>(args.ctx + static_cast<size_t>(seq_start + q_row) * args.hidden +
+                                            head * kHeadDim);
+#pragma unroll
+      for (int cb = 0; cb < kHeadDim; cb += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_o + cb, v);
+        tmem_ld_wait();
+        if (q_row < L) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_half2(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+            w.y = pack_half2(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+            w.z = pack_half2(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+            w.w = pack_half2(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
+            dst[(cb >> 3) + u] = w;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+template <bool EXP16>
+cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
+  constexpr int kSmemBytes = 7 * kTileBytes + 256;
+  static bool attr_set[64] = {};
+  static int sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(mha_persistent_kernel<EXP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)
+      sms[dev] = 148;
+    attr_set[dev] = true;
+  }
+  MhaPersistentArgs args;
+  args.ctx = a.ctx;
+  args.batch_idx = a.batch_idx;
+  args.batch = a.batch;
+  args.heads = a.head_num;
+  args.hidden = a.hidden;
+  args.scale_log2e = a.scale_log2e;
+  args.status = a.status;
+  const long long items_max =
+      static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);  // upper bound
+  long long grid = 2LL * sms[dev];
+  if (grid > items_max) grid = items_max;
+  if (grid < 1) grid = 1;
+  return launch_pdl(mha_persistent_kernel<EXP16>, dim3(static_cast<unsigned>(grid)), dim3(192), kSmemBytes, stream,
+                    a.tm_qkv, args);
+}
+
 template <int TILES, bool EXP16>
 cudaError_t launch_tiles(const MhaLaunch& a, const MhaArgs& args, cudaStream_t stream) {
   using Cfg = MhaCfg<TILES>;
@@ -548,17 +881,24 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   // Measured on B200 (18.9k packed tokens, 12 heads): the one-tile variant with two
   // co-resident CTAs per SM is faster at every length from 64 to 1024, so it is the
   // default; the two-tile variant stays selectable.
+  const bool exp16 = g_dbg_exp16 == 1;
+  // Default: the persistent kernel once sequences span more than two key tiles (measured at
+  // 18.9k tokens: +4..7 % at lengths 384..1024, +12 % on lengths uniform in [16,1024]); for
+  // short sequences one CTA per item is faster (lengths 64 / 128: 77 vs 89 us, 40 vs 47 us).
+  if (g_dbg_force_tiles == 0 && a.max_len > 256)
+    return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
+  if (g_dbg_force_tiles == 3) return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
   int tiles = 1;
   if (g_dbg_force_tiles == 1 || g_dbg_force_tiles == 2) tiles = static_cast<int>(g_dbg_force_tiles);
-  const bool exp16 = g_dbg_exp16 == 1;
   if (tiles == 1) return exp16 ? launch_tiles<1, true>(a, args, stream) : launch_tiles<1, false>(a, args, stream);
   return exp16 ? launch_tiles<2, true>(a, args, stream) : launch_tiles<2, false>(a, args, stream);
 }
 
 }  // namespace bt
 
-// Diagnostics hooks (not part of the stable ABI): attention variant (0 = default,
-// 1 / 2 = one / two query tiles per CTA) and exponential flavour (0 = fp32, 1 = fp16x2).
+// Diagnostics hooks (not part of the stable ABI): attention variant (0 = default: persistent
+// for max_len > 256, else one CTA per item; 1 / 2 = one CTA per item with one / two query
+// tiles; 3 = always persistent) and exponential flavour (0 = fp32, 1 = fp16x2).
 extern "C" int bt_debug_set_mha_tiles(long long tiles) {
   bt::g_dbg_force_tiles = tiles;
   return 0;
