@@ -84,11 +84,18 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
   pdl_wait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long row = static_cast<long long>(blockIdx.x) * kLnWarps + warp;
   const int nvec = hidden / 8;
+  // Rows are walked with a grid stride (the grid is capped at a few waves of the machine), so
+  // a warp keeps streaming instead of paying a block launch per row.
+  long long row_limit = m_rows;
+  if (!RESTORE && m_dev != nullptr) {
+    const int md = __ldg(m_dev);
+    row_limit = md < m_rows ? md : m_rows;
+  }
+  for (long long row = static_cast<long long>(blockIdx.x) * kLnWarps + warp; row < row_limit;
+       row += static_cast<long long>(gridDim.x) * kLnWarps) {
   long long src_row = row;
   if (RESTORE) {
-    if (row >= m_rows) return;  // m_rows = B*S here
     const int b = static_cast<int>(row / S);
     const int i = static_cast<int>(row - static_cast<long long>(b) * S);
     const int off = __ldg(batch_idx + b);
@@ -96,16 +103,9 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
     if (i >= len) {
       uint4* o4 = reinterpret_cast<uint4*>(out + row * hidden);
       for (int v = lane; v < nvec; v += 32) o4[v] = make_uint4(0u, 0u, 0u, 0u);
-      return;
+      continue;
     }
     src_row = off + i;
-  } else {
-    int M = m_rows;
-    if (m_dev != nullptr) {
-      const int md = __ldg(m_dev);
-      M = md < M ? md : M;
-    }
-    if (row >= M) return;
   }
 
   const uint4* x4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(x_v) + src_row * hidden);
@@ -172,6 +172,7 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
       o4[v] = pack8(o);
     }
   }
+  }  // row loop
 }
 
 template <bool RESTORE, bool GB_FP32, bool X_FP32>
@@ -309,6 +310,12 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
 
 }  // namespace
 
+// at most 16 resident blocks (64 warps) per SM on 148 SMs
+static unsigned ln_grid(long long blocks_needed) {
+  const long long cap = 148LL * 16;
+  return static_cast<unsigned>(blocks_needed < cap ? (blocks_needed < 1 ? 1 : blocks_needed) : cap);
+}
+
 template <bool RESTORE>
 static cudaError_t launch_ln_dispatch(bool gb_fp32, bool x_fp32, int nv, dim3 grid, cudaStream_t stream, const void* x,
                                       const __half* bias, const __half* residual, const void* gamma, const void* beta,
@@ -333,7 +340,7 @@ cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, con
                              int m_rows, int hidden, float eps, cudaStream_t stream) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || m_rows <= 0) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
-  dim3 grid((m_rows + kLnWarps - 1) / kLnWarps);
+  dim3 grid(ln_grid((m_rows + kLnWarps - 1) / kLnWarps));
   return launch_ln_dispatch<false>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev,
                                    m_rows, nullptr, 0, hidden, eps);
 }
@@ -345,7 +352,7 @@ cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* b
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || B <= 0 || S <= 0) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   const long long rows = static_cast<long long>(B) * S;
-  dim3 grid(static_cast<unsigned>((rows + kLnWarps - 1) / kLnWarps));
+  dim3 grid(ln_grid((rows + kLnWarps - 1) / kLnWarps));
   return launch_ln_dispatch<true>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out_padded,
                                   nullptr, static_cast<int>(rows), batch_idx, S, hidden, eps);
 }

@@ -88,6 +88,7 @@ struct GemmArgs {
   const void* beta;
   int gb_fp32;
   float eps;
+  long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
   uint32_t a_kstep_bytes;
@@ -96,6 +97,10 @@ struct GemmArgs {
 };
 
 // Debug overrides (0 = default): W descriptor fields, forced tile width, pair kernel on/off.
+long long* g_dbg_gemm_timing = nullptr;  // [148 CTAs][16 tiles][4 slots]
+__device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
+  if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 4 + slot] = clock64();
+}
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 
 // ------------------------------------------------------------------------------------------
@@ -376,6 +381,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           break;
         }
         tc_fence_after();
+        gstamp(args.timing, it, 0);
         const uint32_t d_tmem = tmem_base + as * BLOCK_N;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, args.status, kStatusGemmMmaTimeout)) {
@@ -398,6 +404,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           }
         }
         if (ok) umma_commit(&acc_full[as]);
+        gstamp(args.timing, it, 1);
       }
     }
   } else {
@@ -415,8 +422,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       prefetch_residual<BLOCK_N, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
       epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore, 1>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
                                                   col_half, lane, resv, rsum, rsq);
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
@@ -685,6 +694,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
           break;
         }
         tc_fence_after();
+        gstamp(args.timing, it, 0);
         const uint32_t d_tmem = tmem_base + as * kTileN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, args.status, kStatusGemmMmaTimeout)) {
@@ -707,6 +717,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
           }
         }
         if (ok) umma_commit_pair(&acc_full[as]);
+        gstamp(args.timing, it, 1);
       }
     }
   } else {
@@ -726,8 +737,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
       float unused_sum = 0.f, unused_sq = 0.f;
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
       epilogue_tile<kTileN, EPI, true, Cfg::kStagingBufs>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M,
                                                           quarter, col_half, lane, resv, unused_sum, unused_sq);
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[as]), 0));
@@ -879,6 +892,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.beta = g.beta;
   a.gb_fp32 = g.gb_fp32 ? 1 : 0;
   a.eps = g.eps;
+  a.timing = g_dbg_gemm_timing;
   // A: K-major, 128B swizzle, 8-row groups 1024 B apart; 16 K-elements = 32 B.
   a.a_desc_hi = make_smem_desc_hi(16, 1024);
   a.a_kstep_bytes = 32;
@@ -917,6 +931,11 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
 // N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0).
 // value 0 restores the default for keys 1-5.
+// Device buffer of 148 x 16 x 4 long long for clock64 stamps of the one-CTA kernel (null = off).
+extern "C" int bt_debug_set_gemm_timing(long long* device_buffer) {
+  bt::g_dbg_gemm_timing = device_buffer;
+  return 0;
+}
 extern "C" int bt_debug_set(int key, long long value) {
   switch (key) {
     case 1: bt::g_dbg_b_lbo = value; return 0;
