@@ -99,6 +99,9 @@ def load(path: str | None = None) -> C.CDLL:
     if hasattr(lib, "bt_debug_set"):
         lib.bt_debug_set.restype = _i
         lib.bt_debug_set.argtypes = [_i, C.c_longlong]
+    if hasattr(lib, "bt_debug_set_fused_layernorm"):
+        lib.bt_debug_set_fused_layernorm.restype = _i
+        lib.bt_debug_set_fused_layernorm.argtypes = [_vp, _i]
     if path is None:
         _lib = lib
     return lib

@@ -107,11 +107,10 @@ struct bt_encoder_s {
   // launch accounting / optional per-kernel event timing (bt_profile_*)
   long long launches[BT_PROF_KINDS] = {};
   bool prof_on = false;
-  // LayerNorm inside the attention-output / FFN2 GEMM kernel.  Off by default: measured on B200 at
-  // 18.9k rows the fused kernel takes 91 us (K=768) / 138 us (K=3072) against 47 / 91 us for GEMM +
-  // row kernel — eight epilogue warps per SM cannot hide the read-back latency that the row kernel's
-  // 64 warps per SM hide.
-  bool fused_ln = false;
+  // LayerNorm inside the attention-output / FFN2 GEMM kernel (bt_debug_set_fused_layernorm):
+  // 0 never, 1 from `fused_ln_min_tiles` 128-row tiles upwards, 2 always.
+  int fused_ln = 0;
+  int fused_ln_min_tiles = 24;
   std::vector<cudaEvent_t> ev_pool;
   size_t ev_used = 0;
   struct Span { int kind; cudaEvent_t beg, end; };
@@ -188,7 +187,9 @@ struct Workspace {
   int* batch_idx;
   int* word_idx;
   __half *xa, *xb, *qkv, *ctx, *y, *mid;
-  float* pre;  // pre-LayerNorm sum, kept in fp32
+  float* pre;  // pre-LayerNorm sum, kept in fp32 (LayerNorm as its own kernel), or the row-statistics partials
+  unsigned int* ln_sync;  // two counters per 128-row tile for LayerNorm inside the GEMM kernel (zero between launches)
+  size_t ln_sync_bytes;
   size_t bytes;
 };
 
@@ -212,11 +213,14 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   w.pre = reinterpret_cast<float*>(take(2 * rh));
   w.y = reinterpret_cast<__half*>(take(rh));
   w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
+  w.ln_sync_bytes = 8 * ((rows + 127) / 128);
+  w.ln_sync = reinterpret_cast<unsigned int*>(take(w.ln_sync_bytes));
   w.bytes = off + 1024;  // slack so that an unaligned base can be rounded up
   return w;
 }
 
 struct LnArgs {
+  unsigned int* sync = nullptr;
   __half* out_ln = nullptr;
   const void* gamma = nullptr;
   const void* beta = nullptr;
@@ -229,8 +233,13 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
                     cudaStream_t stream, const LnArgs* ln = nullptr) {
   const CUtensorMap* ta = h->tmap(A, m_rows, K, 64, 128);
   const CUtensorMap* tb = h->tmap(W, K, N, 64, 64);
-  const bool f32out = epi == BT_EPI_BIAS_RESIDUAL_F32OUT || epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM;
-  const CUtensorMap* to = f32out ? h->tmap(out, m_rows, N, 32, 32, 4) : h->tmap(out, m_rows, N, 64, 32, 2);
+  const CUtensorMap* to;
+  if (epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM)  // `out` is only the statistics scratch; the store map is the fp16 result's
+    to = ln ? h->tmap(ln->out_ln, m_rows, N, 64, 32, 2) : nullptr;
+  else if (epi == BT_EPI_BIAS_RESIDUAL_F32OUT)
+    to = h->tmap(out, m_rows, N, 32, 32, 4);
+  else
+    to = h->tmap(out, m_rows, N, 64, 32, 2);
   if (!ta || !tb || !to)
     return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
   GemmLaunch g;
@@ -250,6 +259,7 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
   g.status = h->status;
   g.num_sms = h->num_sms;
   if (ln != nullptr) {
+    g.ln_sync = ln->sync;
     g.out_ln = ln->out_ln;
     g.gamma = ln->gamma;
     g.beta = ln->beta;
@@ -288,6 +298,23 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   return BT_OK;
 }
 
+// LayerNorm rides in the attention-output / FFN2 GEMM kernel once there are enough 128-row tiles
+// to occupy the machine with 256-column tiles; below that the narrow-tile GEMM followed by the
+// row kernel spreads the few rows over more SMs.
+static bool want_fused_ln(bt_handle h, long long rows) {
+  const int H = h->hidden;
+  const long long row_tiles = (rows + 127) / 128;
+  return (H % 256 == 0) && H <= 1024 && (h->fused_ln == 2 || (h->fused_ln == 1 && row_tiles >= h->fused_ln_min_tiles));
+}
+
+// The tile counters of the fused LayerNorm must be zero before the first layer; the kernels
+// leave them zero, but the caller's workspace starts out with arbitrary contents.
+static int prepare_ln_sync(bt_handle h, const Workspace& ws, long long rows, cudaStream_t stream) {
+  if (!want_fused_ln(h, rows)) return BT_OK;
+  cudaError_t e = cudaMemsetAsync(ws.ln_sync, 0, ws.ln_sync_bytes, stream);
+  return e == cudaSuccess ? BT_OK : fail_cuda(h, e, "memset of the LayerNorm tile counters");
+}
+
 // One layer on packed rows.  `x_in` -> `x_out` (packed) unless restore_to != null,
 // in which case the last LayerNorm scatters into the padded tensor.
 static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, __half* restore_to,
@@ -304,12 +331,13 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
                      stream)) != BT_OK)
     return rc;
   if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream)) != BT_OK) return rc;
-  // LayerNorm can ride in the GEMM kernel when a CTA can hold whole rows (H % 256 == 0, H <= 1024)
-  // and there are enough 128-row tiles to give every SM one; see `fused_ln` for why it is optional.
-  const bool fuse_ln = h->fused_ln && (H % 256 == 0) && H <= 1024 && (rows + 127) / 128 >= h->num_sms;
+  // LayerNorm rides in the GEMM kernel (clusters of H/256 CTAs per 128-row tile) once there are
+  // enough row tiles to occupy the machine that way; below that the narrow-tile GEMM followed by
+  // the row kernel spreads the few rows over more SMs.
+  const bool fuse_ln = want_fused_ln(h, rows);
   cudaError_t e = cudaSuccess;
   if (fuse_ln) {
-    LnArgs ln{ws.y, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta, gb32, h->cfg.ln_eps};
+    LnArgs ln{ws.ln_sync, ws.y, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta, gb32, h->cfg.ln_eps};
     if ((rc = run_gemm(h, BT_PROF_GEMM_ATTN_OUT, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre),
                        w.attr_output_bias, x_in, m_dev, rows, H, H, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0, stream, &ln)) !=
         BT_OK)
@@ -329,7 +357,7 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
                      h->cfg.gelu_kind, stream)) != BT_OK)
     return rc;
   if (fuse_ln && restore_to == nullptr) {
-    LnArgs ln{x_out, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, h->cfg.ln_eps};
+    LnArgs ln{ws.ln_sync, x_out, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, h->cfg.ln_eps};
     return run_gemm(h, BT_PROF_GEMM_FFN2, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias,
                     ws.y, m_dev, rows, H, F, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0, stream, &ln);
   }
@@ -369,6 +397,7 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
   void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
   Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
 
+  if ((rc = prepare_ln_sync(h, ws, static_cast<long long>(rows), stream)) != BT_OK) return rc;
   cudaError_t e;
   {
     LaunchScope scope(h, BT_PROF_OFFSETS, stream);
@@ -584,6 +613,10 @@ int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, con
   if (workspace_bytes < need.bytes) return fail(h, BT_ERR_WORKSPACE, "workspace smaller than bt_workspace_bytes_packed()");
   void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
   Workspace ws = carve(base, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0);
+  {
+    const int rc = prepare_ln_sync(h, ws, total_tokens, stream);
+    if (rc != BT_OK) return rc;
+  }
   const __half* cur = reinterpret_cast<const __half*>(x_packed);
   for (int l = 0; l < n_layers; ++l) {
     const bool last = (l == n_layers - 1);
@@ -645,17 +678,29 @@ int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bia
     return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (m_rows <= 0 || N <= 0 || K <= 0 || N % 256 != 0 || N > 1024 || K % 64 != 0)
     return fail(h, BT_ERR_INVALID_ARG, "bt_gemm_layernorm needs m_rows > 0, N % 256 == 0, N <= 1024, K % 64 == 0");
-  LnArgs ln{reinterpret_cast<__half*>(out), gamma, beta, gamma_beta_fp32 != 0, eps};
+  // scratch: [m_rows][N/128] partials of 8 bytes, then the tile counters
+  const size_t sync_off = align_up(static_cast<size_t>(m_rows) * (N / 128) * 8, 16);
+  unsigned int* sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(scratch_f32) + sync_off);
+  cudaError_t me = cudaMemsetAsync(sync, 0, 8 * ((static_cast<size_t>(m_rows) + 127) / 128),
+                                   reinterpret_cast<cudaStream_t>(stream));
+  if (me != cudaSuccess) return fail_cuda(h, me, "memset of the LayerNorm tile counters");
+  LnArgs ln{sync, reinterpret_cast<__half*>(out), gamma, beta, gamma_beta_fp32 != 0, eps};
   return run_gemm(h, BT_PROF_GEMM_OTHER, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(scratch_f32),
                   bias, reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0,
                   reinterpret_cast<cudaStream_t>(stream), &ln);
 }
 
-// Diagnostics hook: 1 = run LayerNorm inside the attention-output / FFN2 GEMM kernels, 0 = as its
-// own row kernel (default).
+// Diagnostics hook: LayerNorm inside the attention-output / FFN2 GEMM kernels: 0 = never (row
+// kernel), 1 = when the call has enough 128-row tiles (default), 2 = always; values above 2
+// keep mode 1 and set the tile threshold to that value.
 int bt_debug_set_fused_layernorm(bt_handle h, int on) {
   if (!h) return BT_ERR_INVALID_ARG;
-  h->fused_ln = on != 0;
+  if (on > 2) {
+    h->fused_ln = 1;
+    h->fused_ln_min_tiles = on;
+  } else {
+    h->fused_ln = on < 0 ? 0 : on;
+  }
   return BT_OK;
 }
 

@@ -81,13 +81,14 @@ struct GemmArgs {
   int K;
   int gelu_kind;
   int* status;
-  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is the fp32 scratch of the
-  // pre-normalisation sum, `out_ln` the fp16 result
+  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is the scratch for the row
+  // statistics partials (8 * N/128 bytes per row), `out_ln` the fp16 result
   __half* out_ln;
   const void* gamma;
   const void* beta;
   int gb_fp32;
   float eps;
+  unsigned int* ln_sync;  // fused LayerNorm: two zero-initialised counters per 128-row tile
   long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
@@ -97,9 +98,9 @@ struct GemmArgs {
 };
 
 // Debug overrides (0 = default): W descriptor fields, forced tile width, pair kernel on/off.
-long long* g_dbg_gemm_timing = nullptr;  // [148 CTAs][16 tiles][4 slots]
+long long* g_dbg_gemm_timing = nullptr;  // [148 CTAs][16 tiles][8 slots]
 __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
-  if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 4 + slot] = clock64();
+  if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 8 + slot] = clock64();
 }
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 
@@ -119,11 +120,10 @@ __device__ __forceinline__ void tma_store_wait_read_n() {
 template <int TILE_N, int EPI, bool TMA_STORE, int STG_BUFS>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtensorMap* tm_out, uint8_t* stg,
                                               uint32_t tmem_acc, int m0, int n0, int M, int quarter, int col_half,
-                                              int lane, const uint4* resv, float& rsum, float& rsq) {
+                                              int lane, const uint4* resv) {
   constexpr int kColsPerWarp = TILE_N / 2;
-  constexpr bool kLn = (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
-  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
+  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
   // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
   constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
   constexpr int kNChunks = kColsPerWarp / kChunk;
@@ -186,14 +186,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
           v[q * 8 + 2 * j] += f.x;
           v[q * 8 + 2 * j + 1] += f.y;
         }
-      }
-    }
-    if (kLn) {
-      // running row statistics of the pre-normalisation sum (this thread's columns)
-#pragma unroll
-      for (int i = 0; i < kChunk; ++i) {
-        rsum += v[i];
-        rsq = fmaf(v[i], v[i], rsq);
       }
     }
     // 8 (or 4) units of 16 bytes per row
@@ -264,8 +256,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
-  constexpr bool kLn = (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kLn;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -320,17 +311,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = args.K / kBlockK;
-  // The li-th tile of this CTA.  Normally tiles go round-robin over the CTAs; with the fused
-  // LayerNorm a CTA takes whole 128-row tiles and walks all their column tiles in a row, so
-  // that it sees complete rows and needs no exchange with other CTAs for the statistics.
+  // The li-th tile of this CTA: tiles go round-robin over the CTAs.
   auto tile_at = [&](int li, int& m0, int& n0) -> bool {
-    if (kLn) {
-      const int mt = static_cast<int>(blockIdx.x) + (li / n_tiles) * static_cast<int>(gridDim.x);
-      if (mt >= m_tiles) return false;
-      m0 = mt * kBlockM;
-      n0 = (li % n_tiles) * BLOCK_N;
-      return true;
-    }
     const int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
     if (tile >= total_tiles) return false;
     m0 = (tile / n_tiles) * kBlockM;
@@ -413,7 +395,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int col_half = e >> 2;   // which half of the tile's columns
     uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;  // 32 rows x 128 B, swizzled
-    float rsum = 0.f, rsq = 0.f;  // fused LayerNorm: statistics of this thread's row over the tiles seen so far
     int m0 = 0, n0 = 0;
     for (int it = 0; tile_at(it, m0, n0); ++it) {
       const int as = it & 1;
@@ -424,90 +405,11 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       tc_fence_after();
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
       epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore, 1>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
-                                                  col_half, lane, resv, rsum, rsq);
+                                                  col_half, lane, resv);
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
-      if (kLn && n0 + BLOCK_N == args.N) {
-        // ---- LayerNorm of the 128 rows just completed.  The fp32 sums were written to the
-        // scratch tensor a moment ago (they are read back from L2), the row statistics are
-        // exchanged through the warps' staging buffers.
-        if (lane == 0) {
-          tma_store_wait_all();
-          asm volatile("fence.proxy.async;" ::: "memory");
-        }
-        __syncwarp();
-        reinterpret_cast<float2*>(stg)[lane] = make_float2(rsum, rsq);
-        rsum = 0.f;
-        rsq = 0.f;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const int N = args.N;
-        const int nvec = N >> 2;                      // float4 per row
-        constexpr int kMaxIt = 8;                     // N <= 1024
-        const float inv_n = 1.0f / static_cast<float>(N);
-        const uint8_t* stg0 = smem + kStages * Cfg::kStageBytes;
-        // one row per pass keeps the kernel inside its 168-register budget (320 threads are
-        // allocated like 384); more rows in flight were measured too: no gain.
-        constexpr int kRowsPerPass = 1;
-        for (int rr = 0; rr < 16; rr += kRowsPerPass) {
-          float4 x[kRowsPerPass][kMaxIt];
-          float mean[kRowsPerPass], rstd[kRowsPerPass];
-#pragma unroll
-          for (int k = 0; k < kRowsPerPass; ++k) {
-            const int rt = e * 16 + rr + k;  // row inside the 128-row tile
-            const int grow = m0 + rt;
-            // the two warps that own this row's TMEM lane quarter (left / right column half)
-            const int ew = (((rt >> 5) + 2) & 3);
-            const float2 s0 = reinterpret_cast<const float2*>(stg0 + ew * kStagingBytesPerWarp)[rt & 31];
-            const float2 s1 = reinterpret_cast<const float2*>(stg0 + (ew + 4) * kStagingBytesPerWarp)[rt & 31];
-            mean[k] = (s0.x + s1.x) * inv_n;
-            const float var = fmaxf((s0.y + s1.y) * inv_n - mean[k] * mean[k], 0.f);
-            rstd[k] = rsqrtf(var + args.eps);
-            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(args.out) +
-                                                                static_cast<size_t>(grow) * N);
-#pragma unroll
-            for (int q = 0; q < kMaxIt; ++q) {
-              const int v = q * 32 + lane;
-              if (v < nvec && grow < M) x[k][q] = __ldcg(src + v);
-            }
-          }
-#pragma unroll
-          for (int q = 0; q < kMaxIt; ++q) {
-            const int v = q * 32 + lane;
-            if (v < nvec) {
-              float g[4], bt_[4];  // gamma / beta of these four columns
-              if (args.gb_fp32) {
-                const float4 a = __ldg(reinterpret_cast<const float4*>(args.gamma) + v);
-                const float4 b = __ldg(reinterpret_cast<const float4*>(args.beta) + v);
-                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
-                bt_[0] = b.x; bt_[1] = b.y; bt_[2] = b.z; bt_[3] = b.w;
-              } else {
-                const uint2 a = __ldg(reinterpret_cast<const uint2*>(args.gamma) + v);
-                const uint2 b = __ldg(reinterpret_cast<const uint2*>(args.beta) + v);
-                const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x));
-                const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
-                const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x));
-                const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
-                g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
-                bt_[0] = b0.x; bt_[1] = b0.y; bt_[2] = b1.x; bt_[3] = b1.y;
-              }
-#pragma unroll
-              for (int k = 0; k < kRowsPerPass; ++k) {
-                const int grow = m0 + e * 16 + rr + k;
-                if (grow < M) {
-                  const float4 xv = x[k][q];
-                  uint2 o;
-                  o.x = pack_half2(fmaf((xv.x - mean[k]) * rstd[k], g[0], bt_[0]), fmaf((xv.y - mean[k]) * rstd[k], g[1], bt_[1]));
-                  o.y = pack_half2(fmaf((xv.z - mean[k]) * rstd[k], g[2], bt_[2]), fmaf((xv.w - mean[k]) * rstd[k], g[3], bt_[3]));
-                  reinterpret_cast<uint2*>(args.out_ln + static_cast<size_t>(grow) * N)[v] = o;
-                }
-              }
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // staging buffers may be reused
-      }
     }
     if (Cfg::kTmaStore && lane == 0) tma_store_wait_all();  // staging rows must outlive the last bulk store
   }
@@ -736,10 +638,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       prefetch_residual<kTileN, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
-      float unused_sum = 0.f, unused_sq = 0.f;
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
       epilogue_tile<kTileN, EPI, true, Cfg::kStagingBufs>(args, &tm_out, stg, tmem_base + as * kTileN, m0, n0, M,
-                                                          quarter, col_half, lane, resv, unused_sum, unused_sq);
+                                                          quarter, col_half, lane, resv);
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
@@ -762,6 +663,387 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// GEMM + bias + residual + LayerNorm in one kernel:  y = LN(A*W + bias + residual)*gamma + beta.
+// Same tiles, schedule and main loop as gemm_f16_kernel<256, .>: tile t = (row tile t / C,
+// column tile t % C), C = N/256, tiles round-robin over the CTAs, so the C column tiles of a
+// row tile are worked on by C neighbouring CTAs at about the same time.  The fp32 sums stay
+// in tensor memory; the pre-normalisation tensor never goes to HBM.  Every epilogue thread
+// owns one row and 128 of its columns:
+//   1. v = accumulator + bias + residual, written back to tensor memory, with the sum and
+//      sum of squares of v - s (s = the thread's first value: shifted one-pass statistics);
+//   2. the partial (mean_i, M2_i) goes to a global scratch row (it stays in L2), then lane 0
+//      of the warp adds 1 to the row tile's `published` counter (after a device-scope fence);
+//   3. lane 0 polls the counter (acquire, bounded) until the 8*C warps that cover these rows
+//      have published; the 2*C partials of the row are merged (equal counts):
+//         mean = avg(mean_i),  M2 = sum(M2_i) + 128 * sum((mean_i - mean)^2);
+//      the last of the 8*C warps to have read them resets the two counters of the row tile;
+//   4. second read of tensor memory: normalise, gamma / beta, fp16, staging, TMA store.
+// Accumulators are double buffered, so 1-4 of a tile overlap the main loop of the CTA's next
+// tile.  A CTA only ever waits for CTAs working on the same row tile, which never wait for
+// anything but that row tile in turn, so there is no circular wait whatever subset of the
+// grid is resident; the wait is bounded like every other wait of the library.
+// `sync` (two counters per row tile) must be zero when the kernel starts.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_counter_bounded(const unsigned int* ctr, uint32_t target, volatile int* abort_flag,
+                                                     int* status, int code) {
+  if (ld_acquire_gpu(ctr) >= target) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    if (ld_acquire_gpu(ctr) >= target) return true;
+    if ((++polls & 63u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > (1ll << 31)) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                   const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
+  constexpr int kTileN = 256;
+  using Cfg = GemmCfg<kTileN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kColsPerThread = kTileN / 2;  // 128
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+  uint64_t* full_bar = bars;                    // [kStages]
+  uint64_t* empty_bar = bars + kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;      // [2]
+  uint64_t* acc_empty = bars + 2 * kStages + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  pdl_launch_dependents();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_out);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // see gemm_f16_kernel
+  int M = args.m_rows;
+  if (args.m_dev != nullptr) {
+    const int md = __ldg(args.m_dev);
+    M = md < M ? md : M;
+  }
+  const int n_tiles = args.N / kTileN;
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = args.K / kBlockK;
+  auto tile_at = [&](int li, int& m0, int& n0) -> bool {
+    const int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
+    if (tile >= total_tiles) return false;
+    m0 = (tile / n_tiles) * kBlockM;
+    n0 = (tile % n_tiles) * kTileN;
+    return true;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int m0 = 0, n0 = 0;
+      for (int li = 0; ok && tile_at(li, m0, n0); ++li) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
+                                 kStatusGemmProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, &tm_a, &full_bar[stage], kb * kBlockK, m0);
+#pragma unroll
+          for (int c = 0; c < kTileN / 64; ++c)
+            tma_load_2d(sb + c * (64 * kBlockK * 2), &tm_b, &full_bar[stage], n0 + c * 64, kb * kBlockK);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int m0 = 0, n0 = 0;
+      for (int it = 0; ok && tile_at(it, m0, n0); ++it) {
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[as], aphase ^ 1u, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        gstamp(args.timing, it, 0);
+        const uint32_t d_tmem = tmem_base + as * kTileN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint64_t adesc = smem_desc(args.a_desc_hi, sa + k * args.a_kstep_bytes);
+            const uint64_t bdesc = smem_desc(args.b_desc_hi, sb + k * args.b_kstep_bytes);
+            umma_f16_ss(d_tmem, adesc, bdesc, args.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&acc_full[as]);
+        gstamp(args.timing, it, 1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int e = warp - 2;
+    const int quarter = warp & 3;
+    const int col_half = e >> 2;
+    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;
+    const int parts = 2 * n_tiles;                        // partials per row
+    const uint32_t target = static_cast<uint32_t>(n_tiles * kEpiWarps);
+    float2* stats = reinterpret_cast<float2*>(args.out);  // scratch: [row][parts] (mean_i, M2_i)
+    const float inv_n = 1.0f / static_cast<float>(args.N);
+    int m0 = 0, n0 = 0;
+    for (int it = 0; tile_at(it, m0, n0); ++it) {
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const int row0 = m0 + quarter * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < M;
+      const int gcol0 = n0 + col_half * kColsPerThread;  // first of this thread's 128 columns
+      const int part = 2 * (n0 / kTileN) + col_half;
+      unsigned int* ctr = args.ln_sync + 2 * (m0 / kBlockM);  // [0] published, [1] read
+      // residual of this thread's row, 32 columns at a time, one chunk ahead of its use
+      const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + gcol0);
+      uint4 rnext[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
+      if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+      tc_fence_after();
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
+      const uint32_t t_row = tmem_base + as * kTileN + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             col_half * kColsPerThread;
+      // ---- 1. v = acc + bias + residual -> tensor memory; shifted sums
+      float sd = 0.f, sdd = 0.f, shift0 = 0.f;
+      {
+        uint32_t raw[2][32];
+        tmem_ld_32x32(t_row, raw[0]);
+#pragma unroll
+        for (int ci = 0; ci < kColsPerThread / 32; ++ci) {
+          const int c = ci * 32;
+          uint4 rcur[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) rcur[q] = rnext[q];
+          tmem_ld_wait();
+          if (ci + 1 < kColsPerThread / 32) {
+            tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + (c + 32) / 8 + q) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol0 + c);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 b4 = __ldg(bp + q);
+            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+            const __half2* rh = reinterpret_cast<const __half2*>(&rcur[q]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 fb = __half22float2(bh[j]);
+              const float2 fr = __half22float2(rh[j]);
+              const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
+              const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
+              if (ci == 0 && q == 0 && j == 0) shift0 = v0;
+              const float d0 = v0 - shift0, d1 = v1 - shift0;
+              sd += d0 + d1;
+              sdd = fmaf(d0, d0, sdd);
+              sdd = fmaf(d1, d1, sdd);
+              raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
+              raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
+            }
+          }
+          tmem_st_32x32(t_row + c, raw[ci & 1]);
+        }
+      }
+      const float lmean = shift0 + sd * (1.0f / kColsPerThread);
+      const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 4);
+      // ---- 2. publish the partial
+      if (row_ok) __stcg(&stats[static_cast<size_t>(row) * parts + part], make_float2(lmean, m2));
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(ctr, 1u);
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
+      // ---- 3. wait for the other owners of these rows, merge
+      int okw = 1;
+      if (lane == 0) okw = wait_counter_bounded(ctr, target, abort_flag, args.status, kStatusGemmEpilogueTimeout) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) break;
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
+      float mean = 0.f, rstd = 0.f;
+      if (row_ok) {
+        float2 pv[8];  // N <= 1024: at most 8 partials per row
+        const float2* sp = stats + static_cast<size_t>(row) * parts;
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < parts) {
+            pv[p] = __ldcg(sp + p);
+            mean += pv[p].x;
+          }
+        mean *= 1.0f / static_cast<float>(parts);
+        float M2 = 0.f;
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < parts) {
+            const float d = pv[p].x - mean;
+            M2 += pv[p].y + static_cast<float>(kColsPerThread) * d * d;
+          }
+        rstd = rsqrtf(M2 * inv_n + args.eps);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        // the last warp to have read the partials of this row tile leaves the counters at zero
+        if (atomicAdd(ctr + 1, 1u) == target - 1u) {
+          ctr[0] = 0u;
+          ctr[1] = 0u;
+        }
+      }
+      const float shift = -mean * rstd;
+      tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
+      // ---- 4. normalise, gamma / beta, fp16, store (64 columns = 128 B per row at a time)
+      const bool slab_full = row0 + 32 <= M;
+      {
+        uint32_t raw[2][32];
+        tmem_ld_32x32(t_row, raw[0]);
+#pragma unroll
+        for (int ci = 0; ci < kColsPerThread / 32; ++ci) {
+          const int c = ci * 32;
+          const int hh = ci & 1;  // which half of the current 64-column store chunk
+          uint8_t* srow = stg + lane * 128;
+          if (hh == 0 && slab_full) {
+            if (lane == 0) tma_store_wait_read_n<0>();  // the previous bulk store has read the staging rows
+            __syncwarp();
+          }
+          tmem_ld_wait();
+          if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int col8 = gcol0 + c + q * 8;  // first of these 8 columns
+            float g[8], b[8];
+            if (args.gb_fp32) {
+              const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2));
+              const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2) + 1);
+              const float4 b0 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2));
+              const float4 b1 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2) + 1);
+              g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+              b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+            } else {
+              const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(args.gamma) + (col8 >> 3));
+              const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(args.beta) + (col8 >> 3));
+              const __half2* gh = reinterpret_cast<const __half2*>(&g4);
+              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 fg = __half22float2(gh[j]);
+                const float2 fb = __half22float2(bh[j]);
+                g[2 * j] = fg.x; g[2 * j + 1] = fg.y;
+                b[2 * j] = fb.x; b[2 * j + 1] = fb.y;
+              }
+            }
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              y[i] = fmaf(fmaf(__uint_as_float(raw[ci & 1][q * 8 + i]), rstd, shift), g[i], b[i]);
+            uint4 u;
+            u.x = pack_half2(y[0], y[1]);
+            u.y = pack_half2(y[2], y[3]);
+            u.z = pack_half2(y[4], y[5]);
+            u.w = pack_half2(y[6], y[7]);
+            const int unit = hh * 4 + q;  // 16-byte unit inside the 128-byte row
+            if (slab_full)
+              *reinterpret_cast<uint4*>(srow + ((unit ^ (lane & 7)) << 4)) = u;
+            else if (row_ok)
+              *reinterpret_cast<uint4*>(args.out_ln + static_cast<size_t>(row) * args.N + col8) = u;
+          }
+          if (hh == 1 && slab_full) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tm_out, stg, gcol0 + c - 32, row0);
+              tma_store_commit();
+            }
+          }
+        }
+      }
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ launch
 template <int BLOCK_N, int EPI>
 cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
@@ -778,7 +1060,6 @@ cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   const int n_tiles = g.N / BLOCK_N;
   const int m_tiles = (g.m_rows + kBlockM - 1) / kBlockM;
   long long tiles = static_cast<long long>(n_tiles) * m_tiles;
-  if (EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM) tiles = m_tiles;  // a CTA owns whole row tiles
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
   return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
@@ -843,6 +1124,26 @@ cudaError_t launch_pair_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t
   }
 }
 
+cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
+  using Cfg = GemmCfg<256>;
+  static bool attr_set[64] = {};
+  auto kern = gemm_f16_ln_kernel;
+  if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || !g.ln_sync)
+    return cudaErrorInvalidValue;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const int m_tiles = (g.m_rows + kBlockM - 1) / kBlockM;
+  const long long tiles = static_cast<long long>(m_tiles) * (g.N / 256);
+  int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
+  if (grid < 1) grid = 1;
+  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
+}
+
 // The pair kernel needs N % 256 == 0 and pays off once every SM pair gets at least two
 // 256 x 256 tiles (below that the narrower one-CTA tiles fill the machine better).
 bool use_pair_kernel(const GemmLaunch& g) {
@@ -892,6 +1193,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.beta = g.beta;
   a.gb_fp32 = g.gb_fp32 ? 1 : 0;
   a.eps = g.eps;
+  a.ln_sync = g.ln_sync;
   a.timing = g_dbg_gemm_timing;
   // A: K-major, 128B swizzle, 8-row groups 1024 B apart; 16 K-elements = 32 B.
   a.a_desc_hi = make_smem_desc_hi(16, 1024);
@@ -907,10 +1209,8 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     return launch_pair_epi(g, a, stream);
   }
   if (g.epilogue == BT_EPI_BIAS_RESIDUAL_LAYERNORM) {
-    // whole rows per CTA: 256-wide tiles, N <= 1024 (row statistics and gamma/beta live in registers)
-    if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta) return cudaErrorInvalidValue;
     a.idesc = make_idesc_f16(kBlockM, 256, 0, 1);
-    return launch_one<256, BT_EPI_BIAS_RESIDUAL_LAYERNORM>(g, a, stream);
+    return launch_ln_gemm(g, a, stream);
   }
   int bn = g.block_n != 0 ? g.block_n : gemm_pick_block_n(g.m_rows, g.N, g.num_sms);
   if (bn == 0 || g.N % bn != 0) return cudaErrorInvalidValue;
@@ -931,7 +1231,9 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
 // N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0).
 // value 0 restores the default for keys 1-5.
-// Device buffer of 148 x 16 x 4 long long for clock64 stamps of the one-CTA kernel (null = off).
+// Device buffer of 148 x 16 x 8 long long for clock64 stamps of the GEMM kernels (null = off):
+// slots 0/1 MMA warp (accumulator free, last commit), 2/3 epilogue warp 2 (accumulator ready, tile
+// done), 4..6 LayerNorm kernel only (sums written back, partial published, partials of all peers seen).
 extern "C" int bt_debug_set_gemm_timing(long long* device_buffer) {
   bt::g_dbg_gemm_timing = device_buffer;
   return 0;

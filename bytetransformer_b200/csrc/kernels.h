@@ -59,8 +59,10 @@ struct GemmLaunch {
   int m_rows;        // rows allocated in A / out / residual (upper bound of M)
   int N;
   int K;
-  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is the fp32 scratch [m_rows, N]
+  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is a scratch of 8 * N/128 bytes per row for
+  // the row-statistics partials, `ln_sync` two zeroed counters per 128-row tile (the kernel leaves them zero)
   __half* out_ln = nullptr;
+  unsigned int* ln_sync = nullptr;
   const void* gamma = nullptr;
   const void* beta = nullptr;
   bool gb_fp32 = false;

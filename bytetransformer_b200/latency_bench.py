@@ -51,6 +51,8 @@ def main():
     ap.add_argument("--per-layer-op", action="store_true", help="call the one-layer operator 12 times, as the reference's loop")
     ap.add_argument("--graph", action="store_true", help="replay the forward from a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B)")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
@@ -106,12 +108,23 @@ def main():
         ms = statistics.median(times)
         fl = BERT_BASE.layers * (gemm_flops_per_layer(T, H) + attention_flops_per_layer(lens.numpy(), H))
         ref = README_MS.get(B, {}).get(S)
+        breakdown = None
+        if args.breakdown and graph is None:
+            reps = 10
+            enc.profile_enable(True)
+            for _ in range(reps):
+                fwd()
+            torch.cuda.synchronize()
+            breakdown = {k: {"us_per_forward": round(v[0] * 1e3 / reps, 2), "launches_per_forward": v[1] // reps}
+                         for k, v in enc.profile_read().items() if v[1]}
+            enc.profile_enable(False)
         print(json.dumps({
             "metric": "ms_per_12_layer_forward", "batch": B, "max_seq": S, "valid_tokens": T, "value": ms,
             "unit": "ms", "min_ms": min(times), "tokens_per_s": T / ms * 1e3, "algorithmic_tflops": fl / ms / 1e9,
             "higher_is_better": False, "reference_a100_ms": ref, "speedup_vs_reference_a100": (ref / ms) if ref else None,
             "api": ("per-layer operator x12" if args.per_layer_op else "one-call padded stack") + (", CUDA graph" if graph else "") + (", no PDL" if args.no_pdl else ""),
-            "l2": "flushed before every timed iteration", "data": "synthetic", "dtype": "f16"}), flush=True)
+            "l2": "flushed before every timed iteration", "data": "synthetic", "dtype": "f16",
+            **({"breakdown": breakdown} if breakdown else {})}), flush=True)
     if enc.device_status() != 0:
         print("device status non-zero", file=sys.stderr)
         return 1

@@ -26,7 +26,8 @@ def _valid(lens, S):
     return torch.arange(S)[None, :] < torch.as_tensor(lens)[:, None]
 
 
-def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf", eps=1e-6, per_layer_op=False):
+def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf", eps=1e-6, per_layer_op=False,
+              fused_ln=None):
     from bytetransformer_b200.encoder import Encoder, bert_transformer
     from oracle.bert_oracle import build_attr_mask
     H = nh * 64
@@ -45,6 +46,9 @@ def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf
         got = h
     else:
         enc = Encoder(nh, 64, dl, ln_eps=eps, gelu=gelu)
+        if fused_ln is not None:  # 0 = LayerNorm as its own kernel, 2 = always inside the GEMM kernel
+            from bytetransformer_b200 import _abi
+            assert _abi.load().bt_debug_set_fused_layernorm(enc._h, fused_ln) == 0
         got = enc.forward(xd, md)
         assert enc.device_status() == 0
         enc.close()
@@ -130,6 +134,16 @@ def test_config3_b16_s512_12_layers(cuda_device):
     g = torch.Generator().manual_seed(303)
     lens = torch.randint(1, 513, (16,), generator=g).tolist()
     _run_case(cuda_device, 16, 512, 12, 12, lens, "normal", seed=4)
+
+
+@pytest.mark.parametrize("fused_ln", [0, 2])
+@pytest.mark.parametrize("nh,gb32", [(12, False), (16, True), (4, False)])
+def test_layernorm_inside_gemm_or_separate(cuda_device, nh, gb32, fused_ln):
+    """Both placements of LayerNorm (row kernel / inside the GEMM kernel by clusters of hidden/256
+    CTAs) against the oracle, hidden 768 / 1024 / 256, ragged last row tile, 3 layers."""
+    g = torch.Generator().manual_seed(77 + nh)
+    lens = torch.randint(1, 301, (6,), generator=g).tolist()
+    _run_case(cuda_device, 6, 300, nh, 3, lens, "normal", seed=21, gb32=gb32, fused_ln=fused_ln)
 
 
 @pytest.mark.parametrize("S", [64, 320, 1024])
