@@ -268,8 +268,9 @@ def main():
         prof = enc.profile_read()
         enc.profile_enable(False)
     clocks = sampler.stop() if sampler else None
-    if enc.device_status() != 0:
-        raise SystemExit("a kernel reported a device-side error status")
+    st = enc.device_status()
+    if st != 0:
+        raise SystemExit("a kernel reported a device-side error status (0x%x)" % st)
     ms_per_step = ms_total / args.steps
     value = total_tokens / (ms_per_step / 1000.0)
 

@@ -18,6 +18,7 @@
 
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "common.cuh"
@@ -83,6 +84,16 @@ struct TmapKey {
            elem_bytes == o.elem_bytes;
   }
 };
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 1315423911ull + (h << 6) + (h >> 2));
+    h ^= ((static_cast<uint64_t>(k.box_cols) << 40) | (static_cast<uint64_t>(k.box_rows) << 8) |
+          static_cast<uint64_t>(k.elem_bytes)) + (h << 6) + (h >> 2);
+    return static_cast<size_t>(h);
+  }
+};
 
 struct LayerState {
   bt_layer_weights w;
@@ -100,16 +111,16 @@ struct bt_encoder_s {
   int* status = nullptr;
   std::string err;
   std::vector<bt::LayerState> layers;
-  // small cache of encoded tensor maps (activations and weights)
-  std::vector<std::pair<bt::TmapKey, CUtensorMap>> tmaps;
-  size_t tmap_next = 0;
+  // cache of encoded tensor maps (activations and weights), emptied when it has grown to kTmapCap entries
+  std::unordered_map<bt::TmapKey, CUtensorMap, bt::TmapKeyHash> tmaps;
+  static constexpr size_t kTmapCap = 8192;
 
   // launch accounting / optional per-kernel event timing (bt_profile_*)
   long long launches[BT_PROF_KINDS] = {};
   bool prof_on = false;
   // LayerNorm inside the attention-output / FFN2 GEMM kernel (bt_debug_set_fused_layernorm):
   // 0 never, 1 from `fused_ln_min_tiles` 128-row tiles upwards, 2 always.
-  int fused_ln = 0;
+  int fused_ln = 1;
   int fused_ln_min_tiles = 24;
   std::vector<cudaEvent_t> ev_pool;
   size_t ev_used = 0;
@@ -125,22 +136,20 @@ struct bt_encoder_s {
     return ev_pool[ev_used++];
   }
 
-  const CUtensorMap* tmap(const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows,
-                          int elem_bytes = 2) {
+  // Copies the tensor map of a row-major [rows, cols] tensor with the given box into `*out` (a copy, so
+  // that later look-ups, which may empty the cache, cannot invalidate it).
+  bool tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows,
+            int elem_bytes = 2) {
     bt::TmapKey k{base, rows, cols, box_cols, box_rows, elem_bytes};
-    for (auto& e : tmaps)
-      if (e.first == k) return &e.second;
-    CUtensorMap m;
-    if (!bt::make_tmap_2d(&m, base, rows, cols, cols, box_cols, box_rows, elem_bytes)) return nullptr;
-    const size_t cap = 256;
-    if (tmaps.size() < cap) {
-      tmaps.emplace_back(k, m);
-      return &tmaps.back().second;
+    auto it = tmaps.find(k);
+    if (it != tmaps.end()) {
+      *out = it->second;
+      return true;
     }
-    tmaps[tmap_next] = std::make_pair(k, m);
-    const CUtensorMap* r = &tmaps[tmap_next].second;
-    tmap_next = (tmap_next + 1) % cap;
-    return r;
+    if (!bt::make_tmap_2d(out, base, rows, cols, cols, box_cols, box_rows, elem_bytes)) return false;
+    if (tmaps.size() >= kTmapCap) tmaps.clear();
+    tmaps.emplace(k, *out);
+    return true;
   }
 };
 
@@ -231,21 +240,15 @@ struct LnArgs {
 static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __half* out, const void* bias,
                     const __half* residual, const int* m_dev, int m_rows, int N, int K, int epi, int gelu_kind,
                     cudaStream_t stream, const LnArgs* ln = nullptr) {
-  const CUtensorMap* ta = h->tmap(A, m_rows, K, 64, 128);
-  const CUtensorMap* tb = h->tmap(W, K, N, 64, 64);
-  const CUtensorMap* to;
-  if (epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM)  // `out` is only the statistics scratch; the store map is the fp16 result's
-    to = ln ? h->tmap(ln->out_ln, m_rows, N, 64, 32, 2) : nullptr;
-  else if (epi == BT_EPI_BIAS_RESIDUAL_F32OUT)
-    to = h->tmap(out, m_rows, N, 32, 32, 4);
-  else
-    to = h->tmap(out, m_rows, N, 64, 32, 2);
-  if (!ta || !tb || !to)
-    return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
   GemmLaunch g;
-  g.tm_a = *ta;
-  g.tm_b = *tb;
-  g.tm_out = *to;
+  bool ok = h->tmap(&g.tm_a, A, m_rows, K, 64, 128) && h->tmap(&g.tm_b, W, K, N, 64, 64);
+  if (epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM)  // `out` is only the statistics scratch; the store map is the fp16 result's
+    ok = ok && ln != nullptr && h->tmap(&g.tm_out, ln->out_ln, m_rows, N, 64, 32, 2);
+  else if (epi == BT_EPI_BIAS_RESIDUAL_F32OUT)
+    ok = ok && h->tmap(&g.tm_out, out, m_rows, N, 32, 32, 4);
+  else
+    ok = ok && h->tmap(&g.tm_out, out, m_rows, N, 64, 32, 2);
+  if (!ok) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointer alignment / driver entry point)");
   g.out = out;
   g.bias = reinterpret_cast<const __half*>(bias);
   g.residual = residual;
@@ -277,10 +280,9 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
 
 static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch_idx, int B, int max_len, int rows,
                    cudaStream_t stream) {
-  const CUtensorMap* tq = h->tmap(qkv, rows, 3 * static_cast<uint64_t>(h->hidden), 64, 128);
-  if (!tq) return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed for qkv");
   MhaLaunch a;
-  a.tm_qkv = *tq;
+  if (!h->tmap(&a.tm_qkv, qkv, rows, 3 * static_cast<uint64_t>(h->hidden), 64, 128))
+    return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed for qkv");
   a.ctx = ctx;
   a.batch_idx = batch_idx;
   a.batch = B;
@@ -457,7 +459,6 @@ int bt_create(const bt_config* cfg, bt_handle* out) {
   h->device = dev;
   h->num_sms = prop.multiProcessorCount;
   h->status = status;
-  h->tmaps.reserve(256);  // pointers into the cache stay valid while it fills
   *out = h;
   return BT_OK;
 }

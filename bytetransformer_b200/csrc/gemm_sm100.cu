@@ -88,7 +88,7 @@ struct GemmArgs {
   const void* beta;
   int gb_fp32;
   float eps;
-  unsigned int* ln_sync;  // fused LayerNorm: two zero-initialised counters per 128-row tile
+  unsigned int* ln_sync;  // fused LayerNorm: one counter per 128-row tile (see gemm_f16_ln_kernel)
   long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
@@ -102,6 +102,7 @@ long long* g_dbg_gemm_timing = nullptr;  // [148 CTAs][16 tiles][8 slots]
 __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
   if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 8 + slot] = clock64();
 }
+long long g_dbg_ln_variant = 0;
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 
 // ------------------------------------------------------------------------------------------
@@ -673,17 +674,18 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 //   1. v = accumulator + bias + residual, written back to tensor memory, with the sum and
 //      sum of squares of v - s (s = the thread's first value: shifted one-pass statistics);
 //   2. the partial (mean_i, M2_i) goes to a global scratch row (it stays in L2), then lane 0
-//      of the warp adds 1 to the row tile's `published` counter (after a device-scope fence);
+//      of the warp adds 1 to the row tile's counter (after a device-scope fence);
 //   3. lane 0 polls the counter (acquire, bounded) until the 8*C warps that cover these rows
 //      have published; the 2*C partials of the row are merged (equal counts):
 //         mean = avg(mean_i),  M2 = sum(M2_i) + 128 * sum((mean_i - mean)^2);
-//      the last of the 8*C warps to have read them resets the two counters of the row tile;
+//      a counter grows by exactly 8*C per launch, so it is never reset: a launch waits for
+//      the next multiple of 8*C above the value it found;
 //   4. second read of tensor memory: normalise, gamma / beta, fp16, staging, TMA store.
 // Accumulators are double buffered, so 1-4 of a tile overlap the main loop of the CTA's next
 // tile.  A CTA only ever waits for CTAs working on the same row tile, which never wait for
 // anything but that row tile in turn, so there is no circular wait whatever subset of the
 // grid is resident; the wait is bounded like every other wait of the library.
-// `sync` (two counters per row tile) must be zero when the kernel starts.
+// `ln_sync` (one counter per row tile) must be a multiple of 8*C, e.g. zero, when the kernel starts.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
   uint32_t v;
@@ -723,8 +725,12 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   uint64_t* empty_bar = bars + kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;      // [2]
   uint64_t* acc_empty = bars + 2 * kStages + 2; // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* vec_full = bars + 2 * kStages + 4;   // bias / gamma / beta of the tile's columns are in shared memory
+  uint64_t* vec_empty = bars + 2 * kStages + 5;  // all epilogue warps are done with them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // fp16 vectors of the current tile's 256 columns: bias | gamma | beta (gamma / beta only when they are fp16)
+  uint4* vec_s = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -740,6 +746,8 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], kEpiWarps);
     }
+    mbar_init(vec_full, 1);
+    mbar_init(vec_empty, kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -863,7 +871,23 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       const bool row_ok = row < M;
       const int gcol0 = n0 + col_half * kColsPerThread;  // first of this thread's 128 columns
       const int part = 2 * (n0 / kTileN) + col_half;
-      unsigned int* ctr = args.ln_sync + 2 * (m0 / kBlockM);  // [0] published, [1] read
+      unsigned int* ctr = args.ln_sync + (m0 / kBlockM);  // warps that have published partials of this row tile
+      // The first epilogue warp brings the tile's bias / gamma / beta slices into shared memory (every
+      // thread re-reads them, and the residual loads below keep evicting them from L1).
+      if (e == 0) {
+        uint4 vb = __ldg(reinterpret_cast<const uint4*>(args.bias + n0) + lane);
+        uint4 vg = make_uint4(0u, 0u, 0u, 0u), vt = vg;
+        if (!args.gb_fp32) {
+          vg = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.gamma) + n0) + lane);
+          vt = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.beta) + n0) + lane);
+        }
+        if (!mbar_wait_bounded(vec_empty, (it & 1u) ^ 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+        vec_s[lane] = vb;
+        vec_s[32 + lane] = vg;
+        vec_s[64 + lane] = vt;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(vec_full);
+      }
       // residual of this thread's row, 32 columns at a time, one chunk ahead of its use
       const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + gcol0);
       uint4 rnext[4];
@@ -871,7 +895,11 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
+      if (!mbar_wait_bounded(vec_full, it & 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
+      const uint4* sbias = vec_s + col_half * (kColsPerThread / 8);
+      const uint4* sgamma = vec_s + 32 + col_half * (kColsPerThread / 8);
+      const uint4* sbeta = vec_s + 64 + col_half * (kColsPerThread / 8);
       const uint32_t t_row = tmem_base + as * kTileN + (static_cast<uint32_t>(quarter * 32) << 16) +
                              col_half * kColsPerThread;
       // ---- 1. v = acc + bias + residual -> tensor memory; shifted sums
@@ -891,10 +919,9 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 #pragma unroll
             for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + (c + 32) / 8 + q) : make_uint4(0u, 0u, 0u, 0u);
           }
-          const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol0 + c);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const uint4 b4 = __ldg(bp + q);
+            const uint4 b4 = sbias[c / 8 + q];
             const __half2* bh = reinterpret_cast<const __half2*>(&b4);
             const __half2* rh = reinterpret_cast<const __half2*>(&rcur[q]);
 #pragma unroll
@@ -922,11 +949,16 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if (row_ok) __stcg(&stats[static_cast<size_t>(row) * parts + part], make_float2(lmean, m2));
       __threadfence();
       __syncwarp();
-      if (lane == 0) atomicAdd(ctr, 1u);
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
-      // ---- 3. wait for the other owners of these rows, merge
+      // The counter only ever grows by `target` per launch that touches this row tile, so the value
+      // this launch has to reach follows from the value found.
       int okw = 1;
-      if (lane == 0) okw = wait_counter_bounded(ctr, target, abort_flag, args.status, kStatusGemmEpilogueTimeout) ? 1 : 0;
+      if (lane == 0) {
+        const uint32_t found = atomicAdd(ctr, 1u);
+        gstamp(warp == 2 ? args.timing : nullptr, it, 5);
+        // ---- 3. wait for the other owners of these rows
+        okw = wait_counter_bounded(ctr, (found / target + 1u) * target, abort_flag, args.status,
+                                   kStatusGemmEpilogueTimeout) ? 1 : 0;
+      }
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) break;
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
@@ -949,14 +981,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             M2 += pv[p].y + static_cast<float>(kColsPerThread) * d * d;
           }
         rstd = rsqrtf(M2 * inv_n + args.eps);
-      }
-      __syncwarp();
-      if (lane == 0) {
-        // the last warp to have read the partials of this row tile leaves the counters at zero
-        if (atomicAdd(ctr + 1, 1u) == target - 1u) {
-          ctr[0] = 0u;
-          ctr[1] = 0u;
-        }
       }
       const float shift = -mean * rstd;
       tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
@@ -988,8 +1012,8 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
               g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
               b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
             } else {
-              const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(args.gamma) + (col8 >> 3));
-              const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(args.beta) + (col8 >> 3));
+              const uint4 g4 = sgamma[c / 8 + q];
+              const uint4 b4 = sbeta[c / 8 + q];
               const __half2* gh = reinterpret_cast<const __half2*>(&g4);
               const __half2* bh = reinterpret_cast<const __half2*>(&b4);
 #pragma unroll
@@ -1028,7 +1052,10 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[as]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[as]);
+        mbar_arrive(vec_empty);
+      }
     }
     if (lane == 0) tma_store_wait_all();
   }
@@ -1124,8 +1151,13 @@ cudaError_t launch_pair_epi(const GemmLaunch& g, const GemmArgs& a, cudaStream_t
   }
 }
 
+struct LnGemmCfg {
+  static constexpr int kSmemBytes = GemmCfg<256>::kSmemBytes + 1536;  // + bias / gamma / beta slices of a tile
+};
+static_assert(LnGemmCfg::kSmemBytes <= 227 * 1024, "shared memory of the GEMM + LayerNorm kernel");
+
 cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
-  using Cfg = GemmCfg<256>;
+  using Cfg = LnGemmCfg;
   static bool attr_set[64] = {};
   auto kern = gemm_f16_ln_kernel;
   if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || !g.ln_sync)
@@ -1191,7 +1223,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.out_ln = g.out_ln;
   a.gamma = g.gamma;
   a.beta = g.beta;
-  a.gb_fp32 = g.gb_fp32 ? 1 : 0;
+  a.gb_fp32 = g_dbg_ln_variant ? static_cast<int>(g_dbg_ln_variant) : (g.gb_fp32 ? 1 : 0);
   a.eps = g.eps;
   a.ln_sync = g.ln_sync;
   a.timing = g_dbg_gemm_timing;
@@ -1246,6 +1278,7 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 4: bt::g_dbg_force_block_n = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
     case 6: bt::set_pdl_enabled(value != 0); return 0;
+    case 7: bt::g_dbg_ln_variant = value; return 0;
     default: return 1;
   }
 }
