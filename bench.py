@@ -191,6 +191,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--token-budget", type=int, default=0)
+    ap.add_argument("--fused-ln", type=int, default=-1,
+                    help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
     ap.add_argument("--max-seqs", type=int, default=0,
                     help="profiling aid: keep only the first N sequences of the workload (small ncu captures)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only the first L layers")
@@ -226,6 +228,9 @@ def main():
     shards = lpt_shards(lengths, n_gpus, BERT_BASE.hidden)
     mine = shards[rank]
     enc = Encoder(BERT_BASE.head_num, 64, make_weights(BERT_BASE, seed=7, device=dev), ln_eps=1e-6, gelu="erf")
+    if args.fused_ln >= 0:
+        from bytetransformer_b200 import _abi
+        _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
     budget = args.token_budget or DEFAULT_TOKEN_BUDGET
     runner = PackedRunner(enc, lengths, mine, token_budget=budget)
     xs, outs = runner.make_device_inputs(seed=rank)

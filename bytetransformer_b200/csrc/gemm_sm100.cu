@@ -102,7 +102,6 @@ long long* g_dbg_gemm_timing = nullptr;  // [148 CTAs][16 tiles][8 slots]
 __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
   if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 8 + slot] = clock64();
 }
-long long g_dbg_ln_variant = 0;
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 
 // ------------------------------------------------------------------------------------------
@@ -1223,7 +1222,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.out_ln = g.out_ln;
   a.gamma = g.gamma;
   a.beta = g.beta;
-  a.gb_fp32 = g_dbg_ln_variant ? static_cast<int>(g_dbg_ln_variant) : (g.gb_fp32 ? 1 : 0);
+  a.gb_fp32 = g.gb_fp32 ? 1 : 0;
   a.eps = g.eps;
   a.ln_sync = g.ln_sync;
   a.timing = g_dbg_gemm_timing;
@@ -1278,7 +1277,6 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 4: bt::g_dbg_force_block_n = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
     case 6: bt::set_pdl_enabled(value != 0); return 0;
-    case 7: bt::g_dbg_ln_variant = value; return 0;
     default: return 1;
   }
 }

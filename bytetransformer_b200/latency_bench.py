@@ -51,6 +51,8 @@ def main():
     ap.add_argument("--per-layer-op", action="store_true", help="call the one-layer operator 12 times, as the reference's loop")
     ap.add_argument("--graph", action="store_true", help="replay the forward from a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B)")
+    ap.add_argument("--fused-ln", type=int, default=-1,
+                    help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
@@ -60,6 +62,9 @@ def main():
     from .workloads import BERT_BASE, attention_flops_per_layer, gemm_flops_per_layer, make_weights
     dev = torch.device("cuda:0")
     enc = Encoder(BERT_BASE.head_num, 64, make_weights(BERT_BASE, seed=7, device=dev))
+    if args.fused_ln >= 0:
+        from . import _abi
+        _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
     if args.no_pdl:
         from . import _abi
         _abi.load().bt_debug_set(6, 0)
