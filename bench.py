@@ -37,11 +37,11 @@ sys.path.insert(0, ROOT)
 METRIC = "bert_base_12L_packed_tokens_per_sec"
 UNIT = "tokens/s"
 WORKLOAD = "whole_box_1024x1024"
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the four shapes of a layer at an
-# 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_f16_kernel_microbatch18k.txt
-# (algorithmic bytes of the same four launches: 146.7 MB mean; DRAM sees less because outputs of one
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the four GEMMs of a layer at an
+# 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_kernels_microbatch18k.txt
+# (algorithmic bytes of the same four launches: 132.4 MB mean; DRAM sees less because outputs of one
 # kernel are still in the 126 MB L2 when the next kernel reads them).
-GEMM_DRAM_BYTES_PER_LAUNCH = 99.0e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 93.9e6
 WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
 
 
@@ -310,7 +310,7 @@ def main():
     if not args.no_kernel_events and gemm_ms > 0:
         achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
         traffic = GEMM_DRAM_BYTES_PER_LAUNCH if not (args.max_seqs or args.layers) else None
-        roofline = {"bound": "tensor", "kernel": "gemm_f16_kernel (4 shapes per layer)", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": "the four GEMMs of a layer: gemm_f16_pair_kernel (QKV), gemm_f16_ln_kernel (attention output and FFN2, with LayerNorm), gemm_f16_kernel (FFN1 + GELU)", "achieved": achieved,
                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                     "peak_source": peaks["source"] + " sustained bf16 dense", "traffic": traffic,
                     "launches": int(gemm_launches), "avg_launch_ms": gemm_ms / max(1, gemm_launches)}
@@ -326,6 +326,8 @@ def main():
         kernels["layernorm"] = {"ms": prof["layernorm"][0], "launches": int(prof["layernorm"][1]),
                                 "gbs": ln_bytes / (prof["layernorm"][0] / 1000.0) / 1e9 if prof["layernorm"][0] > 0 else None,
                                 "hbm_peak_gbs": peaks["hbm_gbs"]}
+        if prof["layernorm"][1] == 0:
+            kernels["layernorm"]["note"] = "LayerNorm ran inside the gemm_attn_out / gemm_ffn2 kernels (no separate launch)"
     launches = int(sum(v[1] for v in launch_counts.values()))
     launches = int(ranks.sum(launches)[0])
 
