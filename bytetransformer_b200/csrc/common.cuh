@@ -24,6 +24,7 @@ enum StatusCode : int {
   kStatusMhaMmaTimeout = 0x202,
   kStatusMhaSoftmaxTimeout = 0x203,
   kStatusBadOffsets = 0x301,
+  kStatusSelfTestTimeout = 0x7F1,  // bt_selftest_bounded_wait(): the wait that nothing satisfies ran out, as intended
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -82,9 +83,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Wait for a phase with an upper bound.  Returns false when the bound ran out
 // or another role of this CTA already gave up (`*abort_flag` non-zero); the
 // caller must then leave its loop and fall through to the common teardown.
-// The bound is ~2^31 SM cycles (about a second), checked every 256 polls.
+// The bound is ~2^31 SM cycles (about a second) unless the caller gives another,
+// checked every 256 polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag, int* status, int code) {
+                                                  volatile int* abort_flag, int* status, int code,
+                                                  long long max_cycles = (1ll << 31)) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
@@ -92,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 255u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > (1ll << 31)) {
+      if (clock64() - t0 > max_cycles) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;

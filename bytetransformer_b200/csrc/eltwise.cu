@@ -378,4 +378,42 @@ cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int
   return launch_pdl(masked_softmax_kernel<false>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
 }
 
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded wait every pipeline of the library relies on: one CTA waits on an
+// mbarrier that nothing will ever arrive on.  The wait must give up after `max_cycles`, record
+// kStatusSelfTestTimeout in the status word and let the kernel return normally, leaving the
+// context usable.  Nothing faults, traps or spins without a limit.
+// ---------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(64) bounded_wait_selftest_kernel(int* status, long long max_cycles, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag_s = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_flag_s;
+  if (threadIdx.x == 0) {
+    // phase 0 never completes: no thread arrives on `bar`
+    const bool got = mbar_wait_bounded(&bar, 0u, abort_flag, status, kStatusSelfTestTimeout, max_cycles);
+    if (gave_up != nullptr) *gave_up = got ? 0 : 1;
+  } else if (threadIdx.x == 32) {
+    // a second role that sees the first one give up through the CTA's abort flag
+    long long spins = 0;
+    while (*abort_flag == 0 && spins < max_cycles) spins += 64, __nanosleep(64);
+  }
+  __syncthreads();
+}
+}  // namespace
+
+cudaError_t launch_bounded_wait_selftest(int* status, long long max_cycles, int* gave_up, cudaStream_t stream) {
+  if (max_cycles < 1024) max_cycles = 1024;
+  if (max_cycles > (1ll << 31)) max_cycles = (1ll << 31);
+  return launch_pdl(bounded_wait_selftest_kernel, dim3(1), dim3(64), 0, stream, status, max_cycles, gave_up);
+}
+
 }  // namespace bt

@@ -550,6 +550,13 @@ int bt_device_status(bt_handle h, void* stream, int* status) {
   return BT_OK;
 }
 
+int bt_selftest_bounded_wait(bt_handle h, long long max_cycles, int* gave_up_dev, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_bounded_wait_selftest(h->status, max_cycles, gave_up_dev, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(h, e, "self-test launch");
+  return BT_OK;
+}
+
 int bt_layer_forward_padded(bt_handle h, int layer, const void* input, const void* attr_mask, void* out,
                             void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream) {
   if (!h) return BT_ERR_INVALID_ARG;

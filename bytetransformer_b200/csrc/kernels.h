@@ -106,4 +106,9 @@ cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int
 // Address of the per-device status word (a __device__ variable of the library).
 int* device_status_word();
 
+// ---- self-test --------------------------------------------------------------
+// One CTA waits (bounded by max_cycles, clamped to [2^10, 2^31]) on a barrier nothing arrives on;
+// writes kStatusSelfTestTimeout to *status and 1 to *gave_up (device int, may be null).
+cudaError_t launch_bounded_wait_selftest(int* status, long long max_cycles, int* gave_up, cudaStream_t stream);
+
 }  // namespace bt

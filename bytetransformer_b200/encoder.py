@@ -113,6 +113,14 @@ class Encoder:
         self._call("bt_device_status", self._h, _stream_ptr(self.device), C.byref(st))
         return st.value
 
+    def selftest_bounded_wait(self, max_cycles: int, gave_up: torch.Tensor | None = None):
+        """Enqueue the library's failure-path self-test: a wait that nothing satisfies gives up after
+        about `max_cycles` SM cycles and leaves BT_STATUS_SELFTEST_TIMEOUT in the status word."""
+        if gave_up is not None:
+            _check(gave_up, "gave_up", torch.int32)
+        self._call("bt_selftest_bounded_wait", self._h, int(max_cycles),
+                   gave_up.data_ptr() if gave_up is not None else None, _stream_ptr(self.device))
+
     def profile_enable(self, on: bool = True):
         self._call("bt_profile_enable", self._h, int(bool(on)))
 

@@ -104,6 +104,16 @@ const char* bt_last_error(bt_handle h);
  * wait ran out.  Synchronises `stream`.  0 = no device-side error. */
 int bt_device_status(bt_handle h, void* stream, int* status);
 
+#define BT_STATUS_SELFTEST_TIMEOUT 0x7F1
+/* Self-test of the failure path (no counterpart in the reference, whose kernels have no
+ * device-side waits): enqueues a one-CTA kernel that waits, with the same bounded wait as
+ * every pipeline of the library, on a barrier that nothing arrives on.  After about
+ * `max_cycles` SM cycles (clamped to [2^10, 2^31]) the wait gives up, the kernel writes
+ * BT_STATUS_SELFTEST_TIMEOUT to the status word (read it with bt_device_status) and 1 to
+ * `*gave_up_dev` (device int, may be NULL) and returns normally; the CUDA context stays
+ * usable.  Nothing faults or traps. */
+int bt_selftest_bounded_wait(bt_handle h, long long max_cycles, int* gave_up_dev, void* stream);
+
 /* ---- forward passes ----------------------------------------------------- */
 
 /* `BertTransformer::infer(param)` (bert_transformer.h:215-222 ->

@@ -392,3 +392,22 @@ def test_gemm_with_fused_layernorm(enc, cuda_device, M, N, K, gb32, m_valid):
     if mv < M:
         assert got[mv:].abs().max().item() == 0.0
     assert enc.device_status() == 0
+
+
+# ---------------------------------------------------------------- failure path
+def test_expired_wait_is_reported_and_the_context_stays_usable(enc, cuda_device):
+    """A device-side wait that nothing satisfies (the library's own self-test kernel: an mbarrier
+    nobody arrives on) gives up after its bound, the kernel returns normally, the status word
+    carries the code, reading it clears it, and the next GEMM on the same handle is correct."""
+    import time
+    from bytetransformer_b200 import _abi
+    gave_up = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    t0 = time.time()
+    enc.selftest_bounded_wait(4_000_000, gave_up)      # ~2 ms of SM cycles
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert gave_up.item() == 1
+    assert enc.device_status() == 0x7F1
+    assert enc.device_status() == 0                     # read-and-clear
+    _gemm_case(enc, cuda_device, 300, 768, 768, _abi.BT_EPI_BIAS)
+    assert enc.device_status() == 0
