@@ -62,6 +62,9 @@ SIGNATURES = {
     "bt_layer_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
     "bt_layer_forward_padded_static": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "bt_stack_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
+    "bt_layer_forward_padded_general": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
+    "bt_stack_forward_padded_general": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
+    "bt_mask_is_right_padded": (_i, [_vp, _i, _i, _vp, C.POINTER(_i), _vp]),
     "bt_stack_forward_packed": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "bt_build_offsets": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "bt_pack_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),

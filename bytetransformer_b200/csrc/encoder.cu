@@ -282,8 +282,15 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
   return BT_OK;
 }
 
+// General-mask attention: [B,S,S] mask applied to every (query, key) pair and an optional
+// [heads,S,S] additive bias (bytetransformer/include/softmax.h:41-45); null mask = lengths only.
+struct GeneralMask {
+  const __half* mask = nullptr;
+  const __half* bias = nullptr;
+};
+
 static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch_idx, int B, int max_len, int rows,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const GeneralMask* gm = nullptr) {
   MhaLaunch a;
   if (!h->tmap(&a.tm_qkv, qkv, rows, 3 * static_cast<uint64_t>(h->hidden), 64, 128))
     return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed for qkv");
@@ -295,6 +302,11 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   a.hidden = h->hidden;
   a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(h->cfg.size_per_head)) / h->cfg.tao;
   a.status = h->status;
+  if (gm != nullptr && gm->mask != nullptr) {
+    a.gen_mask = gm->mask;
+    a.gen_bias = gm->bias;
+    a.gen_inv_scale = sqrtf(static_cast<float>(h->cfg.size_per_head)) * h->cfg.tao;
+  }
   cudaError_t e;
   {
     LaunchScope scope(h, BT_PROF_MHA, stream);
@@ -325,7 +337,7 @@ static int prepare_ln_sync(bt_handle h, const Workspace& ws, long long rows, cud
 // in which case the last LayerNorm scatters into the padded tensor.
 static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, __half* restore_to,
                      const Workspace& ws, const int* batch_idx, int B, int S_or_maxlen, int rows,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const GeneralMask* gm = nullptr) {
   if (layer < 0 || layer >= static_cast<int>(h->layers.size()) || !h->layers[layer].set)
     return fail(h, BT_ERR_INVALID_ARG, "layer weights not set");
   const bt_layer_weights& w = h->layers[layer].w;
@@ -336,7 +348,7 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
   if ((rc = run_gemm(h, BT_PROF_GEMM_QKV, x_in, w.qkv_kernel, ws.qkv, w.qkv_bias, nullptr, m_dev, rows, 3 * H, H, BT_EPI_BIAS, 0,
                      stream)) != BT_OK)
     return rc;
-  if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream)) != BT_OK) return rc;
+  if ((rc = run_mha(h, ws.qkv, ws.ctx, batch_idx, B, S_or_maxlen, rows, stream, gm)) != BT_OK) return rc;
   // LayerNorm rides in the GEMM kernel (clusters of H/256 CTAs per 128-row tile) once there are
   // enough row tiles to occupy the machine that way; below that the narrow-tile GEMM followed by
   // the row kernel spreads the few rows over more SMs.
@@ -426,6 +438,46 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
     __half* t = cur;
     cur = nxt;
     nxt = t;
+  }
+  return BT_OK;
+}
+
+// The general-mask path: nothing is packed (every sequence keeps its S rows, so the padded tensor IS
+// the packed tensor with offsets b*S) and the attention kernel applies the whole [B,S,S] mask and the
+// optional bias.  Every output row is computed, as on the reference's padded path.
+static int stack_general(bt_handle h, int first_layer, int n_layers, const void* input, const void* mask,
+                         const void* attention_bias, void* out, void* workspace, size_t workspace_bytes, int B, int S,
+                         void* stream_v) {
+  int rc = check_shape(h, B, S);
+  if (rc != BT_OK) return rc;
+  if (!input || !mask || !out || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
+  if (input == out) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
+  if (n_layers <= 0) return fail(h, BT_ERR_INVALID_ARG, "n_layers must be positive");
+  if ((reinterpret_cast<uintptr_t>(mask) & 15u) != 0 || (reinterpret_cast<uintptr_t>(attention_bias) & 15u) != 0)
+    return fail(h, BT_ERR_INVALID_ARG, "mask and attention_bias must be 16-byte aligned");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  const size_t rows = static_cast<size_t>(B) * S;
+  Workspace need = carve(nullptr, rows, h->hidden, h->ffn, B + 1, rows);
+  if (workspace_bytes < need.bytes) return fail(h, BT_ERR_WORKSPACE, "workspace smaller than bt_workspace_bytes()");
+  void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
+  Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
+  if ((rc = prepare_ln_sync(h, ws, static_cast<long long>(rows), stream)) != BT_OK) return rc;
+  cudaError_t e;
+  {
+    LaunchScope scope(h, BT_PROF_OFFSETS, stream);
+    e = launch_uniform_offsets(ws.batch_idx, B, S, stream);
+  }
+  if (e != cudaSuccess) return fail_cuda(h, e, "offsets launch");
+  GeneralMask gm;
+  gm.mask = reinterpret_cast<const __half*>(mask);
+  gm.bias = reinterpret_cast<const __half*>(attention_bias);
+  const __half* cur = reinterpret_cast<const __half*>(input);
+  for (int l = 0; l < n_layers; ++l) {
+    const bool last = (l == n_layers - 1);
+    __half* dst = last ? reinterpret_cast<__half*>(out) : ((l & 1) ? ws.xb : ws.xa);
+    rc = run_layer(h, first_layer + l, cur, dst, nullptr, ws, ws.batch_idx, B, S, static_cast<int>(rows), stream, &gm);
+    if (rc != BT_OK) return rc;
+    cur = dst;
   }
   return BT_OK;
 }
@@ -605,6 +657,33 @@ int bt_layer_forward_padded_static(bt_handle h, int layer, const void* input, co
   if (rc != BT_OK) return fail(h, rc, "cudaGetSymbolAddress failed for the built-in scratch array");
   return stack_padded(h, layer, 1, input, attr_mask, out, scratch, static_cast<size_t>(BT_STATIC_SCRATCH_BYTES),
                       batch_size, seq_len, stream);
+}
+
+int bt_layer_forward_padded_general(bt_handle h, int layer, const void* input, const void* attr_mask,
+                                    const void* attention_bias, void* out, void* workspace, size_t workspace_bytes,
+                                    int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  return stack_general(h, layer, 1, input, attr_mask, attention_bias, out, workspace, workspace_bytes, batch_size,
+                       seq_len, stream);
+}
+
+int bt_stack_forward_padded_general(bt_handle h, int n_layers, const void* input, const void* attr_mask,
+                                    const void* attention_bias, void* out, void* workspace, size_t workspace_bytes,
+                                    int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  return stack_general(h, 0, n_layers, input, attr_mask, attention_bias, out, workspace, workspace_bytes, batch_size,
+                       seq_len, stream);
+}
+
+int bt_mask_is_right_padded(const void* attr_mask, int batch_size, int seq_len, int* scratch_dev, int* result,
+                            void* stream) {
+  if (!attr_mask || !scratch_dev || !result || batch_size <= 0 || seq_len <= 0) return BT_ERR_INVALID_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_mask_is_right_padded(reinterpret_cast<const __half*>(attr_mask), batch_size, seq_len,
+                                              scratch_dev, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(result, scratch_dev, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
 }
 
 int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const void* attr_mask, void* out,

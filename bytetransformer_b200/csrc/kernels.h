@@ -44,6 +44,12 @@ cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_id
                                  cudaStream_t stream);
 cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S,
                              int hidden, cudaStream_t stream);
+// batch_idx[i] = i * S for i = 0..B (every sequence keeps all S rows: the general-mask path)
+cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream);
+// *flag_dev = 1 if every mask[b] is a right-padding mask (exactly the first len_b keys allowed in each of
+// the first len_b rows, no key from len_b on allowed in any later row; len_b = number of entries >= 0.5
+// in row 0), else 0.
+cudaError_t launch_mask_is_right_padded(const __half* mask, int B, int S, int* flag_dev, cudaStream_t stream);
 cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int* batch_idx, int B, int S,
                                 int hidden, cudaStream_t stream);
 
@@ -87,6 +93,10 @@ struct MhaLaunch {
   int hidden;          // H = head_num * 64
   float scale_log2e;   // log2(e) / sqrt(64) / tao
   int* status;
+  // general-mask variant: all sequences have max_len rows, scores get bias - 10000 * (1 - mask) added
+  const __half* gen_mask = nullptr;  // [batch, max_len, max_len], null = lengths from batch_idx only
+  const __half* gen_bias = nullptr;  // [head_num, max_len, max_len] or null
+  float gen_inv_scale = 8.0f;        // sqrt(64) * tao
 };
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
 

@@ -72,6 +72,13 @@ struct MhaArgs {
   float scale_log2e;
   int* status;
   long long* timing;  // diagnostics: per CTA and key-tile step, clock64 stamps (null = off)
+  // General-mask variant (GENERAL = true): every sequence has `gen_seq_len` rows; the score of
+  // (query q, key k) gets  attn_bias[head, q, k] + (1 - mask[b, q, k]) * -10000  added after scaling,
+  // the rule of the reference's unfused softmax (bytetransformer/include/softmax.h:41-45).
+  const __half* gen_mask;  // [batch, S, S]
+  const __half* gen_bias;  // [heads, S, S] or null
+  int gen_seq_len;
+  float gen_inv_scale;     // 1 / (softmax scale): the additive term is applied to the unscaled score
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -211,6 +218,54 @@ __device__ __forceinline__ float tile_probs(uint32_t t_s, int kv_valid, float c,
   return l;
 }
 
+// General-mask variant: S(q, k) += (attn_bias[h,q,k] - 10000 * (1 - mask[b,q,k])) / scale for the 128
+// keys of this tile, in tensor memory, before the two softmax passes read it.  `mrow` / `brow`
+// point at (q, first key of the tile); `n_keys` keys exist from there on (the others are
+// dropped later by the key-count mask); `vec` says that 16-byte loads are aligned.  The
+// tensor-memory loads and stores are warp-wide instructions: every lane of the warp must call
+// this function, lanes whose query row does not exist pass n_keys = 0 and add nothing.
+__device__ __forceinline__ void tile_add_mask_bias(uint32_t t_s, const __half* mrow, const __half* brow, int n_keys,
+                                                   bool vec, float inv_scale) {
+#pragma unroll 1
+  for (int cb = 0; cb < kKvRows; cb += 32) {
+    uint32_t v[32];
+    tmem_ld_32x32(t_s + cb, v);
+    float add[32];
+    if (vec && cb + 32 <= n_keys) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(mrow + cb) + q);
+        const __half2* mh = reinterpret_cast<const __half2*>(&m4);
+        uint4 b4 = make_uint4(0u, 0u, 0u, 0u);
+        if (brow != nullptr) b4 = __ldg(reinterpret_cast<const uint4*>(brow + cb) + q);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fm = __half22float2(mh[j]);
+          const float2 fb = __half22float2(bh[j]);
+          add[q * 8 + 2 * j] = fb.x - 10000.0f * (1.0f - fm.x);
+          add[q * 8 + 2 * j + 1] = fb.y - 10000.0f * (1.0f - fm.y);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float a = 0.f;
+        if (cb + i < n_keys) {
+          a = -10000.0f * (1.0f - __half2float(__ldg(mrow + cb + i)));
+          if (brow != nullptr) a += __half2float(__ldg(brow + cb + i));
+        }
+        add[i] = a;
+      }
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(add[i], inv_scale, __uint_as_float(v[i])));
+    tmem_st_32x32(t_s + cb, v);
+  }
+  tmem_st_wait();
+}
+
 __device__ __forceinline__ void stamp(long long* timing, int j, int slot) {
   if (timing != nullptr && j < 8) {
     const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
@@ -218,7 +273,7 @@ __device__ __forceinline__ void stamp(long long* timing, int j, int slot) {
   }
 }
 
-template <int TILES, bool EXP16>
+template <int TILES, bool EXP16, bool GENERAL = false>
 __global__ void __launch_bounds__(MhaCfg<TILES>::kThreads, MhaCfg<TILES>::kMinBlocks)
 mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   using Cfg = MhaCfg<TILES>;
@@ -403,6 +458,15 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         }
         tc_fence_after();
         if (warp == 2 && lane == 0) stamp(args.timing, j, 0);
+        if (GENERAL) {
+          const int S = args.gen_seq_len;
+          const int q_row = q0 + t * kQRows + r;
+          const bool q_ok = q_row < S;
+          const size_t off = static_cast<size_t>(q_ok ? q_row : 0) * S + static_cast<size_t>(j) * kKvRows;
+          tile_add_mask_bias(t_s, args.gen_mask + static_cast<size_t>(b) * S * S + off,
+                             args.gen_bias != nullptr ? args.gen_bias + static_cast<size_t>(head) * S * S + off : nullptr,
+                             q_ok ? kv_valid : 0, (S & 7) == 0, args.gen_inv_scale);
+        }
         // pass 1: row maximum (scaled to log2 units)
         const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
         if (j == 0) {
@@ -857,6 +921,25 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.scale_log2e = a.scale_log2e;
   args.status = a.status;
   args.timing = g_dbg_timing;
+  args.gen_mask = a.gen_mask;
+  args.gen_bias = a.gen_bias;
+  args.gen_seq_len = a.max_len;
+  args.gen_inv_scale = a.gen_inv_scale;
+  if (a.gen_mask != nullptr) {
+    // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
+    using Cfg = MhaCfg<1>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(mha_fwd_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::kSmemBytes);
+      if (e != cudaSuccess) return e;
+      attr_set[dev] = true;
+    }
+    dim3 grid((a.max_len + kQRows - 1) / kQRows, a.head_num, a.batch);
+    return launch_pdl(mha_fwd_kernel<1, false, true>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
+  }
   // Measured on B200 (18.9k packed tokens, 12 heads): the one-tile variant with two
   // co-resident CTAs per SM is faster at every length from 64 to 1024, so it is the
   // default; the two-tile variant stays selectable.

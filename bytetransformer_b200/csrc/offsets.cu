@@ -134,6 +134,55 @@ restore_rows_kernel(const uint4* __restrict__ packed, uint4* __restrict__ padded
     dst[v] = v < n ? __ldg(src + v) : make_uint4(0u, 0u, 0u, 0u);
 }
 
+__global__ void __launch_bounds__(256) uniform_offsets_kernel(int* __restrict__ batch_idx, int B, int S) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i <= B; i += gridDim.x * blockDim.x) batch_idx[i] = i * S;
+}
+
+// One CTA per sequence.  len = number of entries >= 0.5 in row 0 (the definition of the packed path);
+// the mask is a right-padding mask iff each of the first len rows allows exactly the first len keys
+// and no later row allows a key from len on (padding rows may allow the same prefix, as when the key
+// mask is broadcast over the rows, or nothing, as in an outer product of the length mask).  The second
+// condition is what tells a causal mask (row 0 = one key) from a sequence of length one.
+__global__ void __launch_bounds__(256)
+mask_is_right_padded_kernel(const __half* __restrict__ mask, int B, int S, int* __restrict__ flag) {
+  __shared__ int s_len;
+  __shared__ int s_bad;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const __half* m = mask + static_cast<size_t>(b) * S * S;
+  const __half half_thr = __float2half(0.5f);
+  if (threadIdx.x == 0) {
+    s_len = 0;
+    s_bad = 0;
+  }
+  __syncthreads();
+  int cnt = 0;
+  for (int j = threadIdx.x; j < S; j += blockDim.x) cnt += __hge(m[j], half_thr) ? 1 : 0;
+  if (cnt) atomicAdd(&s_len, cnt);
+  __syncthreads();
+  const int len = s_len;
+  bool bad = false;
+  const long long n = static_cast<long long>(S) * S;
+  for (long long e = threadIdx.x; e < n && !bad; e += blockDim.x) {
+    const int i = static_cast<int>(e / S);
+    const int j = static_cast<int>(e % S);
+    const bool allowed = __hge(m[e], half_thr);
+    bad = (i < len) ? (allowed != (j < len)) : (allowed && j >= len);
+  }
+  if (bad) s_bad = 1;
+  __syncthreads();
+  if (threadIdx.x == 0 && s_bad) atomicExch(flag, 0);
+}
+
+__global__ void set_flag_kernel(int* flag, int v) {
+  pdl_launch_dependents();
+  pdl_wait();
+  *flag = v;
+}
+
 inline int copy_grid_x(int S, int vec_per_row) {
   const long long total = static_cast<long long>(S) * vec_per_row;
   long long g = (total + 256 * 4 - 1) / (256 * 4);  // ~4 vectors (64 B) per thread
@@ -147,6 +196,17 @@ inline int copy_grid_x(int S, int vec_per_row) {
 cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_idx, int* word_idx,
                                  cudaStream_t stream) {
   return launch_pdl(build_offsets_kernel, dim3(1), dim3(kOffThreads), 0, stream, mask, B, S, batch_idx, word_idx);
+}
+
+cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream) {
+  const int grid = (B + 1 + 255) / 256;
+  return launch_pdl(uniform_offsets_kernel, dim3(grid), dim3(256), 0, stream, batch_idx, B, S);
+}
+
+cudaError_t launch_mask_is_right_padded(const __half* mask, int B, int S, int* flag_dev, cudaStream_t stream) {
+  cudaError_t e = launch_pdl(set_flag_kernel, dim3(1), dim3(1), 0, stream, flag_dev, 1);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(mask_is_right_padded_kernel, dim3(B), dim3(256), 0, stream, mask, B, S, flag_dev);
 }
 
 cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S, int hidden,

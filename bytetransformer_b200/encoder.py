@@ -170,6 +170,27 @@ class Encoder:
                        ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
         return out
 
+    def forward_general(self, x: torch.Tensor, attr_mask: torch.Tensor, attention_bias: Optional[torch.Tensor] = None,
+                        n_layers: Optional[int] = None) -> torch.Tensor:
+        """All layers with the reference's padded-path attention semantics: nothing is packed, the whole
+        [B,S,S] mask is applied element by element as (1 - mask) * -10000 and `attention_bias`
+        ([head_num,S,S] fp16, optional) is added to the scaled scores; every output row is computed."""
+        B, S = self._check_io(x, attr_mask)
+        if attention_bias is not None:
+            _check(attention_bias, "attention_bias", torch.float16)
+            if tuple(attention_bias.shape) != (self.head_num, S, S):
+                raise RuntimeError("attention_bias must be [head_num, seq_len, seq_len]")
+        nl = self.n_layers if n_layers is None else int(n_layers)
+        with torch.cuda.device(self.device):
+            out = torch.empty_like(x)
+            n = C.c_size_t()
+            self._call("bt_workspace_bytes", self._h, B, S, C.byref(n))
+            ws = self._workspace(n.value)
+            self._call("bt_stack_forward_padded_general", self._h, nl, x.data_ptr(), attr_mask.data_ptr(),
+                       attention_bias.data_ptr() if attention_bias is not None else None, out.data_ptr(),
+                       ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
+        return out
+
     def packed_workspace_bytes(self, batch: int, total_tokens: int) -> int:
         n = C.c_size_t()
         self._call("bt_workspace_bytes_packed", self._h, int(batch), int(total_tokens), C.byref(n))
@@ -234,6 +255,23 @@ class Encoder:
 
 # ---------------------------------------------------------------------------------------------
 # free functions over the stateless entry points
+def mask_is_right_padded(attr_mask: torch.Tensor) -> bool:
+    """True when the packed entry points would honour `attr_mask` [B,S,S] (they look at row 0 only, as the
+    reference's prefix-sum kernel does); otherwise use Encoder.forward_general.  Synchronises the stream."""
+    _check(attr_mask, "attr_mask", torch.float16)
+    if attr_mask.dim() != 3 or attr_mask.shape[1] != attr_mask.shape[2]:
+        raise RuntimeError("attr_mask must be [batch, seq_len, seq_len]")
+    lib = _abi.load()
+    with torch.cuda.device(attr_mask.device):
+        scratch = torch.empty(1, dtype=torch.int32, device=attr_mask.device)
+        res = C.c_int(0)
+        rc = lib.bt_mask_is_right_padded(attr_mask.data_ptr(), int(attr_mask.shape[0]), int(attr_mask.shape[1]),
+                                         scratch.data_ptr(), C.byref(res), _stream_ptr(attr_mask.device))
+    if rc != 0:
+        raise _abi.BtError(rc, "bt_mask_is_right_padded")
+    return bool(res.value)
+
+
 def build_offsets(attr_mask: torch.Tensor):
     """(batch_idx int32[B+1], word_idx int32[B*S]) on the device; only the first
     batch_idx[B] entries of word_idx are defined."""

@@ -84,7 +84,7 @@ struct BertTransformerInferParam {
   int seq_len;
   cublasHandle_t cublas_handle;  // unused
   cudaStream_t stream;
-  const T* attention_bias = NULL;          // must be NULL
+  const T* attention_bias = NULL;          // [head_num, seq_len, seq_len]: selects the general-mask path
   const uint32_t* position_ids = NULL;     // unused
   const uint32_t* token_type_ids = NULL;   // unused
 };
@@ -159,9 +159,15 @@ class BertTransformer {
 
   void infer(BertTransformerInferParam<DataType_> infer_param) {
     if (!handle_) throw std::runtime_error("bt_b200: initialize() must be called before infer()");
-    if (infer_param.attention_bias != NULL)
-      throw std::runtime_error("bt_b200: attention_bias is not supported on the fused path");
     if (buf_bytes_ == 0) cal_bufsize();
+    if (infer_param.attention_bias != NULL) {
+      // the reference's unfused attention: whole [B,S,S] mask, additive bias, no padding removal
+      check(bt_layer_forward_padded_general(handle_, 0, infer_param.input_tensor, infer_param.atten_mask,
+                                            infer_param.attention_bias, infer_param.transformer_output, infer_param.buf,
+                                            buf_bytes_, infer_param.batch_size, infer_param.seq_len, infer_param.stream),
+            "bt_layer_forward_padded_general");
+      return;
+    }
     check(bt_layer_forward_padded(handle_, 0, infer_param.input_tensor, infer_param.atten_mask,
                                   infer_param.transformer_output, infer_param.buf, buf_bytes_, infer_param.batch_size,
                                   infer_param.seq_len, infer_param.stream),

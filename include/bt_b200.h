@@ -153,6 +153,34 @@ int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const 
                             void* out, void* workspace, size_t workspace_bytes, int batch_size,
                             int seq_len, void* stream);
 
+/* The reference's padded / unfused attention semantics (`is_remove_padding = false`,
+ * `attention_bias`): nothing is packed, every one of the batch_size*seq_len output rows is
+ * computed, and the score of (query q, key k) of sequence b and head h is
+ *   q.k * scale + attention_bias[h,q,k] + (1 - attr_mask[b,q,k]) * -10000
+ * before the softmax (bytetransformer/include/softmax.h:41-45,
+ * bytetransformer/src/attention_nofused.cu:78-95, th_op/bert_transformer_ext.h:83-107).  Any
+ * [B,S,S] mask is honoured element by element (prefix-LM, block-diagonal, ...), not only row 0.
+ * `attention_bias` is fp16 [head_num, seq_len, seq_len] or NULL.  Workspace: bt_workspace_bytes().
+ * Rows that a right-padding mask would have dropped hold finite but meaningless values, as in
+ * the reference's padded path; use bt_mask_is_right_padded() to route such masks to the packed
+ * entry points instead. */
+int bt_layer_forward_padded_general(bt_handle h, int layer, const void* input, const void* attr_mask,
+                                    const void* attention_bias, void* out, void* workspace,
+                                    size_t workspace_bytes, int batch_size, int seq_len, void* stream);
+int bt_stack_forward_padded_general(bt_handle h, int n_layers, const void* input, const void* attr_mask,
+                                    const void* attention_bias, void* out, void* workspace,
+                                    size_t workspace_bytes, int batch_size, int seq_len, void* stream);
+
+/* Checks on the device whether every attr_mask[b] is a right-padding mask, i.e. whether the
+ * packed entry points (which, like the reference's `parallel_prefix`, look at row 0 only:
+ * remove_padding.h:51-54,81-85) would honour it: with len_b = number of entries >= 0.5 in row
+ * 0, each of the first len_b rows must allow exactly the first len_b keys and no later row may
+ * allow a key from len_b on (so a causal mask is not taken for length 1).  `scratch_dev` is
+ * one device int; `*result` (host) receives 1 or 0.  Synchronises `stream`.  The reference has
+ * no such check and silently mis-packs other masks. */
+int bt_mask_is_right_padded(const void* attr_mask, int batch_size, int seq_len, int* scratch_dev,
+                            int* result, void* stream);
+
 /* Same stack on an already packed batch: x_packed [T,H], cu_seqlens int32[B+1]
  * on the DEVICE (same meaning as batch_idx), `total_tokens` = T known to the
  * host (rows allocated in x_packed / out_packed), `max_len` >= every length.

@@ -32,7 +32,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import Optional, List, Sequence
 
 import numpy as np
 import torch
@@ -115,12 +115,16 @@ def gelu(x: torch.Tensor, kind: str = "erf") -> torch.Tensor:
 
 def encoder_layer(x: torch.Tensor, attr_mask: torch.Tensor, w: Sequence[torch.Tensor],
                   head_num: int, head_size: int, *, ln_eps: float = 1e-5,
-                  gelu_kind: str = "erf", tao: float = 1.0) -> torch.Tensor:
+                  gelu_kind: str = "erf", tao: float = 1.0,
+                  attention_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One post-LN BERT encoder layer, bert_transformer_test.py:120-158.
 
     x [B,S,H], attr_mask [B,S,S] (1 attend / 0 masked), w = the 12 tensors in
     WEIGHT_NAMES order with GEMM weights stored [in,out].  `tao` is the softmax
     temperature of bytetransformer/include/attention.h:33-39 (scores / tao).
+    `attention_bias` [head_num,S,S] is added to the scaled scores where the reference's
+    unfused softmax adds it (bytetransformer/include/softmax.h:41-45); its PyTorch
+    encoder has no such term.
     """
     (qkv_k, qkv_b, ao_k, ao_b, ln1_g, ln1_b, in_k, in_b, out_k, out_b, ln2_g, ln2_b) = w
     B, S, H = x.shape
@@ -133,6 +137,8 @@ def encoder_layer(x: torch.Tensor, attr_mask: torch.Tensor, w: Sequence[torch.Te
 
     q, k, v = split(q), split(k), split(v)
     scores = torch.matmul(q, k.transpose(-2, -1)) / (head_size ** 0.5) / tao
+    if attention_bias is not None:
+        scores = scores + attention_bias.unsqueeze(0)
     scores = scores - 10000.0 * (1.0 - attr_mask.unsqueeze(1))
     probs = F.softmax(scores, dim=-1)
     h = torch.matmul(probs, v).permute(0, 2, 1, 3).contiguous().view(B, S, H)
