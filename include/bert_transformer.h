@@ -12,7 +12,9 @@
 //   * `use_fused_attention` / `is_remove_padding` are accepted and ignored (execution
 //     is always padding-free with fused attention); `cublas_handle`, `cublas_Algo`,
 //     `position_ids`, `token_type_ids` are accepted and unused, as in the reference
-//     for the latter two; `attention_bias` must be NULL;
+//     for the latter two; a non-NULL `attention_bias` selects the general-mask path (whole
+//     [B,S,S] mask honoured, no padding removal, every output row computed), which is where
+//     the reference applies it too (its unfused softmax);
 //   * errors surface as std::runtime_error with the library's message, never exit().
 #pragma once
 
