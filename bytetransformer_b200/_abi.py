@@ -58,6 +58,8 @@ SIGNATURES = {
     "bt_workspace_bytes_packed": (_i, [_vp, _i, _i, C.POINTER(_sz)]),
     "bt_last_error": (C.c_char_p, [_vp]),
     "bt_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
+    "bt_embedding_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "bt_pooler": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bt_selftest_bounded_wait": (_i, [_vp, C.c_longlong, _vp, _vp]),
     "bt_layer_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
     "bt_layer_forward_padded_static": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp]),

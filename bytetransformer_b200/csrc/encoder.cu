@@ -602,6 +602,36 @@ int bt_device_status(bt_handle h, void* stream, int* status) {
   return BT_OK;
 }
 
+int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void* type_emb, const void* gamma,
+                           const void* beta, int gamma_beta_fp32, const int* token_ids, const int* type_ids,
+                           const int* position_ids, void* out, int batch_size, int seq_len, int hidden, int vocab_size,
+                           int max_positions, int type_vocab_size, float eps, void* stream) {
+  if (!word_emb || !pos_emb || !type_emb || !gamma || !beta || !token_ids || !out) return BT_ERR_INVALID_ARG;
+  if (batch_size <= 0 || seq_len <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 1024 || vocab_size <= 0 ||
+      max_positions <= 0 || type_vocab_size <= 0 || !(eps >= 0.f))
+    return BT_ERR_INVALID_ARG;
+  if (static_cast<long long>(batch_size) * seq_len > 0x7fffffffLL) return BT_ERR_INVALID_ARG;
+  const void* ptrs[6] = {word_emb, pos_emb, type_emb, gamma, beta, out};
+  for (const void* p : ptrs)
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_embedding_layernorm(
+      reinterpret_cast<const __half*>(word_emb), reinterpret_cast<const __half*>(pos_emb),
+      reinterpret_cast<const __half*>(type_emb), gamma, beta, gamma_beta_fp32 != 0, token_ids, type_ids, position_ids,
+      reinterpret_cast<__half*>(out), batch_size * seq_len, seq_len, hidden, vocab_size, max_positions, type_vocab_size,
+      eps, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* pooled, int batch_size, int seq_len,
+              int hidden, void* stream) {
+  if (!encoder_out || !W || !bias || !pooled || batch_size <= 0 || seq_len <= 0 || hidden <= 0) return BT_ERR_INVALID_ARG;
+  cudaError_t e = launch_pooler(reinterpret_cast<const __half*>(encoder_out), reinterpret_cast<const __half*>(W),
+                                reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(pooled), batch_size,
+                                seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaErrorInvalidValue) return BT_ERR_INVALID_ARG;
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
 int bt_selftest_bounded_wait(bt_handle h, long long max_cycles, int* gave_up_dev, void* stream) {
   if (!h) return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_bounded_wait_selftest(h->status, max_cycles, gave_up_dev, reinterpret_cast<cudaStream_t>(stream));

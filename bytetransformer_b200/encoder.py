@@ -255,6 +255,57 @@ class Encoder:
 
 # ---------------------------------------------------------------------------------------------
 # free functions over the stateless entry points
+def embedding_layernorm(word_emb: torch.Tensor, pos_emb: torch.Tensor, type_emb: torch.Tensor, gamma: torch.Tensor,
+                        beta: torch.Tensor, token_ids: torch.Tensor, type_ids: Optional[torch.Tensor] = None,
+                        position_ids: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    """Encoder input [B,S,H] = LayerNorm(word[token] + position + type) (the step before the stack)."""
+    for t, n in ((word_emb, "word_emb"), (pos_emb, "pos_emb"), (type_emb, "type_emb")):
+        _check(t, n, torch.float16)
+    _check(token_ids, "token_ids", torch.int32)
+    if token_ids.dim() != 2:
+        raise RuntimeError("token_ids must be [batch, seq_len]")
+    gb32 = gamma.dtype == torch.float32
+    _check(gamma, "gamma", torch.float32 if gb32 else torch.float16)
+    _check(beta, "beta", gamma.dtype)
+    B, S = int(token_ids.shape[0]), int(token_ids.shape[1])
+    H = int(word_emb.shape[1])
+    for t, n in ((type_ids, "type_ids"), (position_ids, "position_ids")):
+        if t is not None:
+            _check(t, n, torch.int32)
+            if tuple(t.shape) != (B, S):
+                raise RuntimeError(f"{n} must be [batch, seq_len]")
+    lib = _abi.load()
+    with torch.cuda.device(word_emb.device):
+        out = torch.empty(B, S, H, dtype=torch.float16, device=word_emb.device)
+        rc = lib.bt_embedding_layernorm(word_emb.data_ptr(), pos_emb.data_ptr(), type_emb.data_ptr(), gamma.data_ptr(),
+                                        beta.data_ptr(), int(gb32), token_ids.data_ptr(),
+                                        type_ids.data_ptr() if type_ids is not None else None,
+                                        position_ids.data_ptr() if position_ids is not None else None, out.data_ptr(),
+                                        B, S, H, int(word_emb.shape[0]), int(pos_emb.shape[0]), int(type_emb.shape[0]),
+                                        float(eps), _stream_ptr(word_emb.device))
+    if rc != 0:
+        raise _abi.BtError(rc, "bt_embedding_layernorm")
+    return out
+
+
+def pooler(encoder_out: torch.Tensor, W: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """pooled [B,H] = tanh(encoder_out[:,0,:] @ W + bias) (the step after the stack)."""
+    _check(encoder_out, "encoder_out", torch.float16)
+    _check(W, "W", torch.float16)
+    _check(bias, "bias", torch.float16)
+    B, S, H = (int(v) for v in encoder_out.shape)
+    if tuple(W.shape) != (H, H) or tuple(bias.shape) != (H,):
+        raise RuntimeError("W must be [hidden, hidden] and bias [hidden]")
+    lib = _abi.load()
+    with torch.cuda.device(encoder_out.device):
+        out = torch.empty(B, H, dtype=torch.float16, device=encoder_out.device)
+        rc = lib.bt_pooler(encoder_out.data_ptr(), W.data_ptr(), bias.data_ptr(), out.data_ptr(), B, S, H,
+                           _stream_ptr(encoder_out.device))
+    if rc != 0:
+        raise _abi.BtError(rc, "bt_pooler")
+    return out
+
+
 def mask_is_right_padded(attr_mask: torch.Tensor) -> bool:
     """True when the packed entry points would honour `attr_mask` [B,S,S] (they look at row 0 only, as the
     reference's prefix-sum kernel does); otherwise use Encoder.forward_general.  Synchronises the stream."""

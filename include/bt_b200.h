@@ -283,6 +283,26 @@ int bt_masked_softmax(void* logits, const void* attr_mask, int batch_size, int h
 #define BT_PROF_GEMM_FFN2 7
 #define BT_PROF_GEMM_OTHER 8
 #define BT_PROF_KINDS 9
+/* The steps either side of the encoder stack (no counterpart in the reference: its infer
+ * parameters only carry unused `position_ids` / `token_type_ids`,
+ * bytetransformer/include/bert_transformer.h:93-95, and an unused kernel hints at an embedding
+ * LayerNorm, bytetransformer/include/layernorm.h:219-240).
+ * bt_embedding_layernorm: out[b,s,:] = LayerNorm(word_emb[token_ids[b,s]] + pos_emb[p] +
+ *   type_emb[type_ids[b,s]]) * gamma + beta, p = position_ids[b,s] or s when position_ids is NULL,
+ *   type 0 when type_ids is NULL.  Tables fp16 row-major [vocab_size|max_positions|type_vocab_size,
+ *   hidden], ids int32 [batch_size, seq_len] (ids outside a table are clamped into it), gamma/beta
+ *   fp16 or fp32, out fp16 [batch_size, seq_len, hidden] = the encoder's input.  hidden % 8 == 0,
+ *   hidden <= 1024; all pointers but the ids 16-byte aligned.
+ * bt_pooler: pooled[b,:] = tanh(encoder_out[b,0,:] * W + bias), W fp16 [hidden, hidden] as [in,out],
+ *   pooled fp16 [batch_size, hidden]. */
+int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void* type_emb,
+                           const void* gamma, const void* beta, int gamma_beta_fp32,
+                           const int* token_ids, const int* type_ids, const int* position_ids, void* out,
+                           int batch_size, int seq_len, int hidden, int vocab_size, int max_positions,
+                           int type_vocab_size, float eps, void* stream);
+int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* pooled, int batch_size,
+              int seq_len, int hidden, void* stream);
+
 /* on != 0: reset the counters and bracket every kernel the handle launches with
  * CUDA events on the launching stream; on == 0: stop timing (counting goes on).
  * Replaces the reference's unused timing events (src/bert_transformer.cu:89-93). */
