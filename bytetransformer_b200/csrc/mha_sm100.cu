@@ -947,7 +947,11 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   // Default: the persistent kernel once sequences span more than two key tiles (measured at
   // 18.9k tokens: +4..7 % at lengths 384..1024, +12 % on lengths uniform in [16,1024]); for
   // short sequences one CTA per item is faster (lengths 64 / 128: 77 vs 89 us, 40 vs 47 us).
-  if (g_dbg_force_tiles == 0 && a.max_len > 256)
+  // With fewer than ~600 items (two per persistent CTA) the static item lists are too short to
+  // balance and the hardware's own block scheduling of one CTA per item is as good or better
+  // (12 layers, batch 1, 307 of 512 tokens: 0.756 vs 0.785 ms; batch 16 at max_seq 512: 1.544 vs 1.503 ms).
+  const long long items_max = static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);
+  if (g_dbg_force_tiles == 0 && a.max_len > 256 && items_max >= 600)
     return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
   if (g_dbg_force_tiles == 3) return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
   int tiles = 1;

@@ -53,6 +53,8 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B)")
     ap.add_argument("--fused-ln", type=int, default=-1,
                     help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
+    ap.add_argument("--mha-variant", type=int, default=-1,
+                    help="A/B aid: 0 default policy, 1 one CTA per (query tile, head, sequence), 3 persistent CTAs")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
@@ -65,6 +67,9 @@ def main():
     if args.fused_ln >= 0:
         from . import _abi
         _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
+    if args.mha_variant >= 0:
+        from . import _abi
+        _abi.load().bt_debug_set_mha_tiles(args.mha_variant)
     if args.no_pdl:
         from . import _abi
         _abi.load().bt_debug_set(6, 0)

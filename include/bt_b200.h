@@ -225,8 +225,11 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
  * followed by `add_bias_input_layernorm_kernel_launcher`
  * (bytetransformer/src/bert_transformer.cu:102-109 and :115-129):
  * out[M,N] = LayerNorm(A[M,K] * W[K,N] + bias + residual) * gamma + beta.
- * `scratch_f32` is float[m_rows, N] (the pre-normalisation sum in fp32, written and read
- * back by the same CTA).  N % 256 == 0, N <= 1024, K % 64 == 0. */
+ * The pre-normalisation sums stay in tensor memory; the N/256 CTAs that share a 128-row tile
+ * exchange row statistics through `scratch_f32`, a device buffer of m_rows*N*4 bytes whose
+ * contents are undefined afterwards (used: 8*N/128 bytes per row plus one counter per row
+ * tile, which this call zeroes itself).  N % 256 == 0, N <= 1024, K % 64 == 0.  The waits
+ * between CTAs are bounded like every other wait (bt_device_status). */
 int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bias, const void* residual,
                       const void* gamma, const void* beta, int gamma_beta_fp32, float eps,
                       void* scratch_f32, void* out, const int* m_dev, int m_rows, int N, int K,
