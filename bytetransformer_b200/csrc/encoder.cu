@@ -247,7 +247,8 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
   GemmLaunch g;
   bool ok = h->tmap(&g.tm_a, A, m_rows, K, 64, 128) && h->tmap(&g.tm_b, W, K, N, 64, 64);
   if (epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM)  // `out` is only the statistics scratch; the store map is the fp16 result's
-    ok = ok && ln != nullptr && h->tmap(&g.tm_out, ln->out_ln, m_rows, N, 64, 32, 2);
+    ok = ok && ln != nullptr && h->tmap(&g.tm_out, ln->out_ln, m_rows, N, 64, 32, 2) &&
+         h->tmap(&g.tm_res, residual, m_rows, N, 64, 32, 2);
   else if (epi == BT_EPI_BIAS_RESIDUAL_F32OUT)
     ok = ok && h->tmap(&g.tm_out, out, m_rows, N, 32, 32, 4);
   else

@@ -711,7 +711,8 @@ __device__ __forceinline__ bool wait_counter_bounded(const unsigned int* ctr, ui
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                   const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
+                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
+                   const GemmArgs args) {
   constexpr int kTileN = 256;
   using Cfg = GemmCfg<kTileN>;
   constexpr int kStages = Cfg::kStages;
@@ -726,7 +727,8 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   uint64_t* acc_empty = bars + 2 * kStages + 2; // [2]
   uint64_t* vec_full = bars + 2 * kStages + 4;   // bias / gamma / beta of the tile's columns are in shared memory
   uint64_t* vec_empty = bars + 2 * kStages + 5;  // all epilogue warps are done with them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
+  uint64_t* res_bar = bars + 2 * kStages + 6;    // [kEpiWarps] a warp's residual rows have landed in its staging buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6 + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // fp16 vectors of the current tile's 256 columns: bias | gamma | beta (gamma / beta only when they are fp16)
   uint4* vec_s = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bars) + 256);
@@ -747,6 +749,7 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
     mbar_init(vec_full, 1);
     mbar_init(vec_empty, kEpiWarps);
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_bar[w], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -758,6 +761,7 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
     tma_prefetch_desc(&tm_out);
+    tma_prefetch_desc(&tm_res);
   }
   tc_fence_before();
   __syncthreads();
@@ -887,11 +891,15 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive(vec_full);
       }
-      // residual of this thread's row, 32 columns at a time, one chunk ahead of its use
-      const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + gcol0);
-      uint4 rnext[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + q) : make_uint4(0u, 0u, 0u, 0u);
+      // Residual rows of this warp (32 rows x 128 columns) come through its staging buffer in two
+      // TMA boxes of 64 columns: row-strided 16-byte loads from the threads would cost one L1 tag
+      // look-up per lane and load (4096 per tile), which alone took longer than the main loop.
+      // The first box is requested now, the second when the first has been read.
+      if (lane == 0) {
+        tma_store_wait_read_n<0>();  // the bulk stores of the previous tile have read the buffer
+        mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
+        tma_load_2d(stg, &tm_res, &res_bar[e], gcol0, row0);
+      }
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
       if (!mbar_wait_bounded(vec_full, it & 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
@@ -906,40 +914,57 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       {
         uint32_t raw[2][32];
         tmem_ld_32x32(t_row, raw[0]);
+        bool res_ok = true;
 #pragma unroll
-        for (int ci = 0; ci < kColsPerThread / 32; ++ci) {
-          const int c = ci * 32;
-          uint4 rcur[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) rcur[q] = rnext[q];
-          tmem_ld_wait();
-          if (ci + 1 < kColsPerThread / 32) {
-            tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) rnext[q] = row_ok ? __ldg(rp + (c + 32) / 8 + q) : make_uint4(0u, 0u, 0u, 0u);
+        for (int hh = 0; hh < 2; ++hh) {
+          // this thread's 64 residual values of box hh: row `lane` of the swizzled buffer
+          if (!mbar_wait_bounded(&res_bar[e], (static_cast<uint32_t>(it) * 2u + hh) & 1u, abort_flag, args.status,
+                                 kStatusGemmEpilogueTimeout)) {
+            res_ok = false;
+            break;
           }
+          uint4 rres[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 b4 = sbias[c / 8 + q];
-            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-            const __half2* rh = reinterpret_cast<const __half2*>(&rcur[q]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 fb = __half22float2(bh[j]);
-              const float2 fr = __half22float2(rh[j]);
-              const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
-              const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
-              if (ci == 0 && q == 0 && j == 0) shift0 = v0;
-              const float d0 = v0 - shift0, d1 = v1 - shift0;
-              sd += d0 + d1;
-              sdd = fmaf(d0, d0, sdd);
-              sdd = fmaf(d1, d1, sdd);
-              raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
-              raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
+          for (int q = 0; q < 8; ++q)
+            rres[q] = *reinterpret_cast<const uint4*>(stg + lane * 128 + ((q ^ (lane & 7)) << 4));
+          if (hh == 0) {
+            fence_proxy_async_smem();  // the reads above precede the next bulk write into the buffer
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
+              tma_load_2d(stg, &tm_res, &res_bar[e], gcol0 + 64, row0);
             }
           }
-          tmem_st_32x32(t_row + c, raw[ci & 1]);
+#pragma unroll
+          for (int cj = 0; cj < 2; ++cj) {
+            const int ci = hh * 2 + cj;
+            const int c = ci * 32;
+            tmem_ld_wait();
+            if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 b4 = sbias[c / 8 + q];
+              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+              const __half2* rh = reinterpret_cast<const __half2*>(&rres[cj * 4 + q]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 fb = __half22float2(bh[j]);
+                const float2 fr = __half22float2(rh[j]);
+                const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
+                const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
+                if (ci == 0 && q == 0 && j == 0) shift0 = v0;
+                const float d0 = v0 - shift0, d1 = v1 - shift0;
+                sd += d0 + d1;
+                sdd = fmaf(d0, d0, sdd);
+                sdd = fmaf(d1, d1, sdd);
+                raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
+                raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
+              }
+            }
+            tmem_st_32x32(t_row + c, raw[ci & 1]);
+          }
         }
+        if (!res_ok) break;
       }
       const float lmean = shift0 + sd * (1.0f / kColsPerThread);
       const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
@@ -1172,7 +1197,7 @@ cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t 
   const long long tiles = static_cast<long long>(m_tiles) * (g.N / 256);
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
-  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
+  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, g.tm_res, a);
 }
 
 // The pair kernel needs N % 256 == 0 and pays off once every SM pair gets at least two

@@ -69,6 +69,7 @@ struct GemmLaunch {
   // the row-statistics partials, `ln_sync` two zeroed counters per 128-row tile (the kernel leaves them zero)
   __half* out_ln = nullptr;
   unsigned int* ln_sync = nullptr;
+  CUtensorMap tm_res;  // residual [m_rows, N] fp16, box {64, 32} (fused LayerNorm only)
   const void* gamma = nullptr;
   const void* beta = nullptr;
   bool gb_fp32 = false;
