@@ -125,6 +125,7 @@ struct bt_encoder_s {
   // 2.47 vs 2.37 ms), because the exchange of row statistics between CTAs lengthens the only wave.
   int fused_ln = 1;
   int fused_ln_min_tiles = 100;
+  uint32_t ln_epoch = 0;  // fused LayerNorm launches since the statistics scratch of the current call was zeroed
   bool fused_ln_ffn2_only = false;  // keep the attention-output LayerNorm as its own kernel
   std::vector<cudaEvent_t> ev_pool;
   size_t ev_used = 0;
@@ -201,8 +202,7 @@ struct Workspace {
   int* word_idx;
   __half *xa, *xb, *qkv, *ctx, *y, *mid;
   float* pre;  // pre-LayerNorm sum, kept in fp32 (LayerNorm as its own kernel), or the row-statistics partials
-  unsigned int* ln_sync;  // two counters per 128-row tile for LayerNorm inside the GEMM kernel (zero between launches)
-  size_t ln_sync_bytes;
+  size_t ln_stats_bytes;  // leading bytes of `pre` that hold the tagged row-statistics partials (fused LayerNorm)
   size_t bytes;
 };
 
@@ -226,14 +226,13 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   w.pre = reinterpret_cast<float*>(take(2 * rh));
   w.y = reinterpret_cast<__half*>(take(rh));
   w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
-  w.ln_sync_bytes = 8 * ((rows + 127) / 128);
-  w.ln_sync = reinterpret_cast<unsigned int*>(take(w.ln_sync_bytes));
+  w.ln_stats_bytes = rows * static_cast<size_t>(hidden / 128 > 0 ? hidden / 128 : 1) * 16;
   w.bytes = off + 1024;  // slack so that an unaligned base can be rounded up
   return w;
 }
 
 struct LnArgs {
-  unsigned int* sync = nullptr;
+  uint32_t epoch = 0;  // tag of this launch in the statistics scratch
   __half* out_ln = nullptr;
   const void* gamma = nullptr;
   const void* beta = nullptr;
@@ -267,7 +266,7 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
   g.status = h->status;
   g.num_sms = h->num_sms;
   if (ln != nullptr) {
-    g.ln_sync = ln->sync;
+    g.ln_epoch = ln->epoch;
     g.out_ln = ln->out_ln;
     g.gamma = ln->gamma;
     g.beta = ln->beta;
@@ -326,12 +325,14 @@ static bool want_fused_ln(bt_handle h, long long rows) {
   return (H % 256 == 0) && H <= 1024 && (h->fused_ln == 2 || (h->fused_ln == 1 && row_tiles >= h->fused_ln_min_tiles));
 }
 
-// The tile counters of the fused LayerNorm must be zero before the first layer; the kernels
-// leave them zero, but the caller's workspace starts out with arbitrary contents.
+// The statistics scratch of the fused LayerNorm (the head of `pre`) holds words tagged with the number
+// of the launch that wrote them; it is zeroed once per call (the caller's workspace starts out with
+// arbitrary contents) and the fused launches of the call are numbered from 1.
 static int prepare_ln_sync(bt_handle h, const Workspace& ws, long long rows, cudaStream_t stream) {
+  h->ln_epoch = 0;
   if (!want_fused_ln(h, rows)) return BT_OK;
-  cudaError_t e = cudaMemsetAsync(ws.ln_sync, 0, ws.ln_sync_bytes, stream);
-  return e == cudaSuccess ? BT_OK : fail_cuda(h, e, "memset of the LayerNorm tile counters");
+  cudaError_t e = cudaMemsetAsync(ws.pre, 0, ws.ln_stats_bytes, stream);
+  return e == cudaSuccess ? BT_OK : fail_cuda(h, e, "memset of the LayerNorm statistics scratch");
 }
 
 // One layer on packed rows.  `x_in` -> `x_out` (packed) unless restore_to != null,
@@ -357,7 +358,7 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
   const bool fuse_ln = fuse_any && !h->fused_ln_ffn2_only;
   cudaError_t e = cudaSuccess;
   if (fuse_ln) {
-    LnArgs ln{ws.ln_sync, ws.y, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta, gb32, h->cfg.ln_eps};
+    LnArgs ln{++h->ln_epoch, ws.y, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta, gb32, h->cfg.ln_eps};
     if ((rc = run_gemm(h, BT_PROF_GEMM_ATTN_OUT, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre),
                        w.attr_output_bias, x_in, m_dev, rows, H, H, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0, stream, &ln)) !=
         BT_OK)
@@ -377,7 +378,7 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
                      h->cfg.gelu_kind, stream)) != BT_OK)
     return rc;
   if (fuse_any && restore_to == nullptr) {
-    LnArgs ln{ws.ln_sync, x_out, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, h->cfg.ln_eps};
+    LnArgs ln{++h->ln_epoch, x_out, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, h->cfg.ln_eps};
     return run_gemm(h, BT_PROF_GEMM_FFN2, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias,
                     ws.y, m_dev, rows, H, F, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0, stream, &ln);
   }
@@ -801,13 +802,11 @@ int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bia
     return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (m_rows <= 0 || N <= 0 || K <= 0 || N % 256 != 0 || N > 1024 || K % 64 != 0)
     return fail(h, BT_ERR_INVALID_ARG, "bt_gemm_layernorm needs m_rows > 0, N % 256 == 0, N <= 1024, K % 64 == 0");
-  // scratch: [m_rows][N/128] partials of 8 bytes, then the tile counters
-  const size_t sync_off = align_up(static_cast<size_t>(m_rows) * (N / 128) * 8, 16);
-  unsigned int* sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(scratch_f32) + sync_off);
-  cudaError_t me = cudaMemsetAsync(sync, 0, 8 * ((static_cast<size_t>(m_rows) + 127) / 128),
+  // scratch: [m_rows][N/128] tagged partials of 16 bytes, zeroed here; this launch is number 1 on it
+  cudaError_t me = cudaMemsetAsync(scratch_f32, 0, static_cast<size_t>(m_rows) * (N / 128) * 16,
                                    reinterpret_cast<cudaStream_t>(stream));
-  if (me != cudaSuccess) return fail_cuda(h, me, "memset of the LayerNorm tile counters");
-  LnArgs ln{sync, reinterpret_cast<__half*>(out), gamma, beta, gamma_beta_fp32 != 0, eps};
+  if (me != cudaSuccess) return fail_cuda(h, me, "memset of the LayerNorm statistics scratch");
+  LnArgs ln{1u, reinterpret_cast<__half*>(out), gamma, beta, gamma_beta_fp32 != 0, eps};
   return run_gemm(h, BT_PROF_GEMM_OTHER, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(scratch_f32),
                   bias, reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0,
                   reinterpret_cast<cudaStream_t>(stream), &ln);

@@ -88,7 +88,7 @@ struct GemmArgs {
   const void* beta;
   int gb_fp32;
   float eps;
-  unsigned int* ln_sync;  // fused LayerNorm: one counter per 128-row tile (see gemm_f16_ln_kernel)
+  uint32_t ln_epoch;  // fused LayerNorm: tag of this launch in the statistics scratch (see gemm_f16_ln_kernel)
   long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
@@ -672,43 +672,28 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 // owns one row and 128 of its columns:
 //   1. v = accumulator + bias + residual, written back to tensor memory, with the sum and
 //      sum of squares of v - s (s = the thread's first value: shifted one-pass statistics);
-//   2. the partial (mean_i, M2_i) goes to a global scratch row (it stays in L2), then lane 0
-//      of the warp adds 1 to the row tile's counter (after a device-scope fence);
-//   3. lane 0 polls the counter (acquire, bounded) until the 8*C warps that cover these rows
-//      have published; the 2*C partials of the row are merged (equal counts):
+//   2. the partial (mean_i, M2_i) goes to a global scratch row (it stays in L2) as two 64-bit
+//      words, each (value bits << 32 | epoch of this launch): an aligned 64-bit store is
+//      single-copy atomic, so the tag validates the value and no fence or counter is needed;
+//   3. the thread polls (bounded) the 2 * 2*C words of its row until all carry the epoch and
+//      merges the 2*C partials (equal counts):
 //         mean = avg(mean_i),  M2 = sum(M2_i) + 128 * sum((mean_i - mean)^2);
-//      a counter grows by exactly 8*C per launch, so it is never reset: a launch waits for
-//      the next multiple of 8*C above the value it found;
 //   4. second read of tensor memory: normalise, gamma / beta, fp16, staging, TMA store.
 // Accumulators are double buffered, so 1-4 of a tile overlap the main loop of the CTA's next
 // tile.  A CTA only ever waits for CTAs working on the same row tile, which never wait for
 // anything but that row tile in turn, so there is no circular wait whatever subset of the
 // grid is resident; the wait is bounded like every other wait of the library.
-// `ln_sync` (one counter per row tile) must be a multiple of 8*C, e.g. zero, when the kernel starts.
+// The scratch (16 * N/128 bytes per row) must not hold this launch's epoch in the low half of any
+// word beforehand: the caller zeroes it once and numbers the launches that share it 1, 2, 3, ...
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ bool wait_counter_bounded(const unsigned int* ctr, uint32_t target, volatile int* abort_flag,
-                                                     int* status, int code) {
-  if (ld_acquire_gpu(ctr) >= target) return true;
-  const long long t0 = clock64();
-  uint32_t polls = 0;
-  while (true) {
-    if (ld_acquire_gpu(ctr) >= target) return true;
-    if ((++polls & 63u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > (1ll << 31)) {
-        *abort_flag = 1;
-        if (status != nullptr) atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
@@ -862,8 +847,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const int col_half = e >> 2;
     uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;
     const int parts = 2 * n_tiles;                        // partials per row
-    const uint32_t target = static_cast<uint32_t>(n_tiles * kEpiWarps);
-    float2* stats = reinterpret_cast<float2*>(args.out);  // scratch: [row][parts] (mean_i, M2_i)
     const float inv_n = 1.0f / static_cast<float>(args.N);
     int m0 = 0, n0 = 0;
     for (int it = 0; tile_at(it, m0, n0); ++it) {
@@ -874,7 +857,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       const bool row_ok = row < M;
       const int gcol0 = n0 + col_half * kColsPerThread;  // first of this thread's 128 columns
       const int part = 2 * (n0 / kTileN) + col_half;
-      unsigned int* ctr = args.ln_sync + (m0 / kBlockM);  // warps that have published partials of this row tile
       // The first epilogue warp brings the tile's bias / gamma / beta slices into shared memory (every
       // thread re-reads them, and the residual loads below keep evicting them from L1).
       if (e == 0) {
@@ -969,43 +951,86 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       const float lmean = shift0 + sd * (1.0f / kColsPerThread);
       const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 4);
-      // ---- 2. publish the partial
-      if (row_ok) __stcg(&stats[static_cast<size_t>(row) * parts + part], make_float2(lmean, m2));
-      __threadfence();
-      __syncwarp();
-      // The counter only ever grows by `target` per launch that touches this row tile, so the value
-      // this launch has to reach follows from the value found.
-      int okw = 1;
-      if (lane == 0) {
-        const uint32_t found = atomicAdd(ctr, 1u);
-        gstamp(warp == 2 ? args.timing : nullptr, it, 5);
-        // ---- 3. wait for the other owners of these rows
-        okw = wait_counter_bounded(ctr, (found / target + 1u) * target, abort_flag, args.status,
-                                   kStatusGemmEpilogueTimeout) ? 1 : 0;
-      }
-      okw = __shfl_sync(0xffffffffu, okw, 0);
-      if (!okw) break;
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
-      float mean = 0.f, rstd = 0.f;
+      // ---- 2. publish the partial: two 64-bit words, each (value bits << 32 | epoch).  A naturally
+      // aligned 64-bit store is single-copy atomic, so a reader that finds this launch's epoch in a word
+      // also has its value: no fence, no counter, no second round trip.
+      const uint32_t epoch = args.ln_epoch;
+      unsigned long long* words = reinterpret_cast<unsigned long long*>(args.out);
       if (row_ok) {
-        float2 pv[8];  // N <= 1024: at most 8 partials per row
-        const float2* sp = stats + static_cast<size_t>(row) * parts;
+        unsigned long long* wp = words + (static_cast<size_t>(row) * parts + part) * 2;
+        st_relaxed_gpu_u64(wp, (static_cast<unsigned long long>(__float_as_uint(lmean)) << 32) | epoch);
+        st_relaxed_gpu_u64(wp + 1, (static_cast<unsigned long long>(__float_as_uint(m2)) << 32) | epoch);
+      }
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
+      // ---- 3. wait until the row's 2 * parts words all carry this epoch (bounded), then merge.
+      // The partials of the 32 rows of this slab come from the same 2*C warps, so one lane probes its
+      // own row (with a pause between probes: 2 * parts loads, not 64 * parts, per probe) and only
+      // then does every lane read and validate its row; a lane whose words are not all there yet
+      // sends the warp round again.
+      float mean = 0.f, rstd = 0.f;
+      float pm[8], pq[8];  // N <= 1024: at most 8 partials per row
+      const unsigned long long* rp64 = words + static_cast<size_t>(row_ok ? row : 0) * parts * 2;
+      const long long t0 = clock64();
+      bool give_up = false;
+      while (true) {
+        if (lane == 0 && row_ok) {
+          uint32_t probes = 0;
+          while (true) {
+            // all loads are issued before any tag is looked at (no short-circuit: one round trip, not 2*parts)
+            uint32_t bad = 0;
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+              if (p < parts) {
+                const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
+                const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
+                bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
+              }
+            if (bad == 0) break;
+            if ((++probes & 15u) == 0u && (*abort_flag != 0 || clock64() - t0 > (1ll << 31))) break;
+          }
+        }
+        __syncwarp();
+        uint32_t bad = 0;
+        if (row_ok) {
+#pragma unroll
+          for (int p = 0; p < 8; ++p)
+            if (p < parts) {
+              const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
+              const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
+              bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
+              pm[p] = __uint_as_float(static_cast<uint32_t>(w0 >> 32));
+              pq[p] = __uint_as_float(static_cast<uint32_t>(w1 >> 32));
+            }
+        }
+        if (__all_sync(0xffffffffu, bad == 0)) break;
+        if (*abort_flag != 0 || clock64() - t0 > (1ll << 31)) {
+          give_up = true;
+          break;
+        }
+        __nanosleep(100);
+      }
+      if (__any_sync(0xffffffffu, give_up)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          if (args.status != nullptr) atomicCAS(args.status, 0, kStatusGemmEpilogueTimeout);
+        }
+        break;
+      }
+      if (row_ok) {
 #pragma unroll
         for (int p = 0; p < 8; ++p)
-          if (p < parts) {
-            pv[p] = __ldcg(sp + p);
-            mean += pv[p].x;
-          }
+          if (p < parts) mean += pm[p];
         mean *= 1.0f / static_cast<float>(parts);
         float M2 = 0.f;
 #pragma unroll
         for (int p = 0; p < 8; ++p)
           if (p < parts) {
-            const float d = pv[p].x - mean;
-            M2 += pv[p].y + static_cast<float>(kColsPerThread) * d * d;
+            const float d = pm[p] - mean;
+            M2 += pq[p] + static_cast<float>(kColsPerThread) * d * d;
           }
         rstd = rsqrtf(M2 * inv_n + args.eps);
       }
+      if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
       const float shift = -mean * rstd;
       tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
       // ---- 4. normalise, gamma / beta, fp16, store (64 columns = 128 B per row at a time)
@@ -1184,7 +1209,7 @@ cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t 
   using Cfg = LnGemmCfg;
   static bool attr_set[64] = {};
   auto kern = gemm_f16_ln_kernel;
-  if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || !g.ln_sync)
+  if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || g.ln_epoch == 0)
     return cudaErrorInvalidValue;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1249,7 +1274,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.beta = g.beta;
   a.gb_fp32 = g.gb_fp32 ? 1 : 0;
   a.eps = g.eps;
-  a.ln_sync = g.ln_sync;
+  a.ln_epoch = g.ln_epoch;
   a.timing = g_dbg_gemm_timing;
   // A: K-major, 128B swizzle, 8-row groups 1024 B apart; 16 K-elements = 32 B.
   a.a_desc_hi = make_smem_desc_hi(16, 1024);

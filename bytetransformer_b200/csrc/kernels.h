@@ -65,10 +65,11 @@ struct GemmLaunch {
   int m_rows;        // rows allocated in A / out / residual (upper bound of M)
   int N;
   int K;
-  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is a scratch of 8 * N/128 bytes per row for
-  // the row-statistics partials, `ln_sync` two zeroed counters per 128-row tile (the kernel leaves them zero)
+  // fused LayerNorm (BT_EPI_BIAS_RESIDUAL_LAYERNORM): `out` is a scratch of 16 * N/128 bytes per row for the
+  // tagged row-statistics partials (zeroed once by the caller), `ln_epoch` >= 1 the tag of this launch,
+  // different from that of every earlier launch on the same scratch since it was zeroed
   __half* out_ln = nullptr;
-  unsigned int* ln_sync = nullptr;
+  uint32_t ln_epoch = 0;
   CUtensorMap tm_res;  // residual [m_rows, N] fp16, box {64, 32} (fused LayerNorm only)
   const void* gamma = nullptr;
   const void* beta = nullptr;
