@@ -227,8 +227,8 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
  * out[M,N] = LayerNorm(A[M,K] * W[K,N] + bias + residual) * gamma + beta.
  * The pre-normalisation sums stay in tensor memory; the N/256 CTAs that share a 128-row tile
  * exchange row statistics through `scratch_f32`, a device buffer of m_rows*N*4 bytes whose
- * contents are undefined afterwards (used: 8*N/128 bytes per row plus one counter per row
- * tile, which this call zeroes itself).  N % 256 == 0, N <= 1024, K % 64 == 0.  The waits
+ * contents are undefined afterwards (used: 16*N/128 bytes per row, which this call zeroes
+ * itself with a memset on `stream`).  N % 256 == 0, N <= 1024, K % 64 == 0.  The waits
  * between CTAs are bounded like every other wait (bt_device_status). */
 int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bias, const void* residual,
                       const void* gamma, const void* beta, int gamma_beta_fp32, float eps,
