@@ -8,7 +8,7 @@ the tensors it produced: the drawn lengths, the 12 weights per layer, the input,
 the [B,S,S] mask and every layer's output.  The reference tree is only needed
 to (re)generate the fixtures, which are committed next to this script.
 
-Usage:  python tests/golden/make_golden.py [reference_root]
+Usage:  python tests/golden/make_golden.py <reference_root>
 """
 import os
 import runpy
@@ -60,7 +60,9 @@ def run_case(script, args):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+    ref = sys.argv[1]
     script = os.path.join(ref, "unit_test/python_scripts/bert_transformer_test.py")
     here = os.path.dirname(os.path.abspath(__file__))
     for name, args in CASES.items():
