@@ -266,6 +266,58 @@ __device__ __forceinline__ void tile_add_mask_bias(uint32_t t_s, const __half* m
   tmem_st_wait();
 }
 
+// One 32-column chunk with the exponent reference of the EARLIER key tiles: probabilities, their
+// sum, and the largest exponent seen (to tell afterwards whether the reference was good enough).
+template <bool MASKED>
+__device__ __forceinline__ float chunk_probs_track(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
+                                                   uint32_t (&out)[16], float& xmax) {
+  float l0 = 0.f, l1 = 0.f, x0m = xmax, x1m = xmax;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float x0 = fmaf(__uint_as_float(v[2 * i]), c, -m_ref);
+    float x1 = fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref);
+    if (MASKED) {
+      x0 = (cbase + 2 * i < kv_valid) ? x0 : -INFINITY;
+      x1 = (cbase + 2 * i + 1 < kv_valid) ? x1 : -INFINITY;
+    }
+    x0m = fmaxf(x0m, x0);
+    x1m = fmaxf(x1m, x1);
+    const float p0 = ex2_approx(x0);
+    const float p1 = ex2_approx(x1);
+    l0 += p0;
+    l1 += p1;
+    out[i] = pack_half2(p0, p1);
+  }
+  xmax = fmaxf(x0m, x1m);
+  return l0 + l1;
+}
+
+// Same pass with P in its own tensor-memory columns (`t_p`, 64 cells): the chunk order is free and
+// nothing of S is overwritten, so the next S = Q K^T may be issued as soon as this pass has read S.
+template <bool MASKED>
+__device__ __forceinline__ float tile_probs_sep(uint32_t t_s, uint32_t t_p, int kv_valid, float c, float m_ref) {
+  uint32_t va[32], vb[32], pk[16];
+  float l = 0.f;
+  tmem_ld_32x32(t_s, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 32, vb);
+  l += chunk_probs<MASKED, false>(va, 0, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p, pk);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, va);
+  l += chunk_probs<MASKED, false>(vb, 32, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p + 16, pk);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 96, vb);
+  l += chunk_probs<MASKED, false>(va, 64, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p + 32, pk);
+  tmem_ld_wait();
+  l += chunk_probs<MASKED, false>(vb, 96, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p + 48, pk);
+  tmem_st_wait();
+  return l;
+}
+
 __device__ __forceinline__ void stamp(long long* timing, int j, int slot) {
   if (timing != nullptr && j < 8) {
     const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
@@ -594,7 +646,16 @@ __device__ __forceinline__ bool decode_item(const int* __restrict__ batch_idx, i
   return false;
 }
 
-template <bool EXP16>
+// PSEP = true: P lives in its own 64 tensor-memory columns instead of over the upper half of S.  The
+// MMA warp can then issue S(j+1) = Q K(j+1)^T BEFORE O += P(j) V(j): the next softmax starts after
+// four MMAs instead of twelve, and P V runs in its shadow.  The softmax waits for `pv_done` of the
+// previous key tile before it rescales O or overwrites P.
+// ONEPASS (needs PSEP): key tiles after the first are read from tensor memory ONCE: probabilities are
+// formed with the reference of the earlier tiles while the largest exponent is tracked; only when that
+// exceeds the threshold (the row maximum jumped by more than 2^8) is the tile redone with a new
+// reference, which is possible because S is still intact.  The two reads of every score were the
+// largest single load on the tensor-memory read path.
+template <bool EXP16, bool PSEP = false, bool ONEPASS = false>
 __global__ void __launch_bounds__(192, 2)
 mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {
   constexpr int kStages = 3;
@@ -602,7 +663,7 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   constexpr int kSmemK = kSmemQ + kTileBytes;
   constexpr int kSmemV = kSmemK + kStages * kTileBytes;
   constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-  constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 128;
+  constexpr uint32_t kTmemS = 0, kTmemP = PSEP ? 192 : 64, kTmemO = 128;
   constexpr float kRescaleThreshold = EXP16 ? 1.0f : 8.0f;
   extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -616,7 +677,8 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   uint64_t* s_full = bars + 2 + 3 * kStages;
   uint64_t* p_full = bars + 3 + 3 * kStages;
   uint64_t* o_done = bars + 4 + 3 * kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + 3 * kStages);
+  uint64_t* pv_done = bars + 5 + 3 * kStages;   // PSEP: the P V MMAs of a key tile have retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 3 * kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -634,6 +696,7 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
     mbar_init(s_full, 1);
     mbar_init(p_full, 128);
     mbar_init(o_done, 1);
+    mbar_init(pv_done, 1);
     *abort_flag = smem_ok ? 0 : 1;
     fence_mbar_init();
     if (!smem_ok && args.status != nullptr) atomicCAS(args.status, 0, kStatusMhaLoadTimeout + 0x10);
@@ -720,8 +783,21 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
           // P of this step is ready; it also tells that the softmax warps have finished the
           // previous item's O read-out, so the first PV of an item may overwrite O.
-          if (!mbar_wait_bounded(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
-              !mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+          if (!mbar_wait_bounded(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          if (PSEP && j + 1 < n_kv) {
+            // the softmax has read S(j) completely and P(j) sits elsewhere: S(j+1) goes first
+            if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(st_n);
+            if (j + 2 == n_kv) umma_commit(q_empty);
+          }
+          if (!mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
             ok = false;
             break;
           }
@@ -731,7 +807,8 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           for (int kk = 0; kk < kKvRows / 16; ++kk)
             umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
                         (j > 0 || kk != 0) ? 1u : 0u);
-          if (j + 1 < n_kv) {
+          if (PSEP) umma_commit(pv_done);
+          if (!PSEP && j + 1 < n_kv) {
             if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
               ok = false;
               break;
@@ -772,7 +849,71 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           break;
         }
         tc_fence_after();
+        if (ONEPASS && j > 0) {
+          // ---- optimistic single pass with the reference of the earlier tiles
+          const uint32_t t_p = t_lane + kTmemP;
+          uint32_t va[32], vb[32], pk0[16], pk1[16];
+          float xmax = -INFINITY, l_tile = 0.f;
+          tmem_ld_32x32(t_s, va);
+          tmem_ld_wait();
+          tmem_ld_32x32(t_s + 32, vb);
+          l_tile += full_tile ? chunk_probs_track<false>(va, 0, kv_valid, c, m_ref, pk0, xmax)
+                              : chunk_probs_track<true>(va, 0, kv_valid, c, m_ref, pk0, xmax);
+          tmem_ld_wait();
+          tmem_ld_32x32(t_s + 64, va);
+          l_tile += full_tile ? chunk_probs_track<false>(vb, 32, kv_valid, c, m_ref, pk1, xmax)
+                              : chunk_probs_track<true>(vb, 32, kv_valid, c, m_ref, pk1, xmax);
+          // P (and O) belong to the P V MMAs of the previous key tile until those have retired; the first
+          // two chunks were computed in the meantime
+          if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          tmem_st_32x16(t_p, pk0);
+          tmem_st_32x16(t_p + 16, pk1);
+          tmem_ld_wait();
+          tmem_ld_32x32(t_s + 96, vb);
+          l_tile += full_tile ? chunk_probs_track<false>(va, 64, kv_valid, c, m_ref, pk0, xmax)
+                              : chunk_probs_track<true>(va, 64, kv_valid, c, m_ref, pk0, xmax);
+          tmem_st_32x16(t_p + 32, pk0);
+          tmem_ld_wait();
+          l_tile += full_tile ? chunk_probs_track<false>(vb, 96, kv_valid, c, m_ref, pk1, xmax)
+                              : chunk_probs_track<true>(vb, 96, kv_valid, c, m_ref, pk1, xmax);
+          tmem_st_32x16(t_p + 48, pk1);
+          if (__any_sync(0xffffffffu, xmax > kRescaleThreshold)) {
+            // the reference was too low for some row of this warp: move it, rescale O and the running
+            // sum, and form this tile's probabilities again from S (rows that did not need it get f = 1)
+            const float m_new = m_ref + fmaxf(xmax, 0.f);
+            const float f = ex2_approx(m_ref - m_new);
+#pragma unroll
+            for (int cb = 0; cb < kHeadDim; cb += 32) {
+              uint32_t v[32];
+              tmem_ld_32x32(t_o + cb, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+              tmem_st_32x32(t_o + cb, v);
+            }
+            l_run *= f;
+            m_ref = m_new;
+            tmem_st_wait();
+            l_tile = full_tile ? tile_probs_sep<false>(t_s, t_p, kv_valid, c, m_ref)
+                               : tile_probs_sep<true>(t_s, t_p, kv_valid, c, m_ref);
+          } else {
+            tmem_st_wait();
+          }
+          l_run += l_tile;
+        } else {
         const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
+        if (PSEP && j > 0) {
+          // O and P still belong to the P V MMAs of the previous key tile until those have retired
+          if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
         if (j == 0) {
           m_ref = mx;
         } else {
@@ -793,8 +934,13 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
             m_ref = m_new;
           }
         }
-        l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
-                           : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
+        if (PSEP)
+          l_run += full_tile ? tile_probs_sep<false>(t_s, t_lane + kTmemP, kv_valid, c, m_ref)
+                             : tile_probs_sep<true>(t_s, t_lane + kTmemP, kv_valid, c, m_ref);
+        else
+          l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
+                             : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
+        }
         if (!full_tile) {
           // tail tile: blank the V rows of keys that do not belong to this sequence
           if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
@@ -855,7 +1001,7 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   }
 }
 
-template <bool EXP16>
+template <bool EXP16, bool PSEP = false, bool ONEPASS = false>
 cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   constexpr int kSmemBytes = 7 * kTileBytes + 256;
   static bool attr_set[64] = {};
@@ -865,7 +1011,7 @@ cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!attr_set[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(mha_persistent_kernel<EXP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaFuncSetAttribute(mha_persistent_kernel<EXP16, PSEP, ONEPASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)
       sms[dev] = 148;
@@ -884,7 +1030,7 @@ cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   long long grid = 2LL * sms[dev];
   if (grid > items_max) grid = items_max;
   if (grid < 1) grid = 1;
-  return launch_pdl(mha_persistent_kernel<EXP16>, dim3(static_cast<unsigned>(grid)), dim3(192), kSmemBytes, stream,
+  return launch_pdl(mha_persistent_kernel<EXP16, PSEP, ONEPASS>, dim3(static_cast<unsigned>(grid)), dim3(192), kSmemBytes, stream,
                     a.tm_qkv, args);
 }
 
@@ -952,8 +1098,11 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   // (12 layers, batch 1, 307 of 512 tokens: 0.756 vs 0.785 ms; batch 16 at max_seq 512: 1.544 vs 1.503 ms).
   const long long items_max = static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);
   if (g_dbg_force_tiles == 0 && a.max_len > 256 && items_max >= 600)
-    return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
-  if (g_dbg_force_tiles == 3) return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false>(a, stream);
+    return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false, true, true>(a, stream);
+  if (g_dbg_force_tiles == 3) return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false, true, true>(a, stream);
+  if (g_dbg_force_tiles == 6) return launch_persistent<false>(a, stream);  // P over the upper half of S, two reads of S per key tile
+  if (g_dbg_force_tiles == 4) return launch_persistent<false, true>(a, stream);  // P in its own columns, S(j+1) before P V(j)
+  if (g_dbg_force_tiles == 5) return launch_persistent<false, true, true>(a, stream);  // + one read of S per key tile
   int tiles = 1;
   if (g_dbg_force_tiles == 1 || g_dbg_force_tiles == 2) tiles = static_cast<int>(g_dbg_force_tiles);
   if (tiles == 1) return exp16 ? launch_tiles<1, true>(a, args, stream) : launch_tiles<1, false>(a, args, stream);

@@ -338,7 +338,7 @@ def test_gemm_pair_twice_bit_identical_and_equal_to_single(enc, cuda_device):
     assert torch.equal(o1, o3)          # same accumulation order: K is walked identically
 
 
-@pytest.mark.parametrize("tiles,exp16", [(0, 0), (3, 0), (3, 1), (1, 0), (2, 0), (1, 1), (2, 1)])
+@pytest.mark.parametrize("tiles,exp16", [(0, 0), (3, 0), (3, 1), (4, 0), (5, 0), (1, 0), (2, 0), (1, 1), (2, 1)])
 def test_attention_variants(enc, cuda_device, tiles, exp16):
     """The persistent kernel (0) and the one-CTA-per-item kernels with one / two query tiles
     per CTA (1, 2), each with both exponential flavours (fp32, and
