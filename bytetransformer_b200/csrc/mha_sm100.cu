@@ -30,6 +30,13 @@
 //   O += P V       128x64x128 with the A operand (P) read from tensor memory and V
 //                  consumed MN-major from shared memory exactly as it lies in the QKV
 //                  buffer -> 64 fp32 columns per tile
+// The persistent kernel for long sequences (further down) uses the free 64 columns of its 256
+// for P instead (S 0..127, O 128..191, P 192..255): S stays intact, so the next S = Q K^T is
+// issued before O += P V, and every key tile is read from tensor memory only once (the
+// probabilities are formed with the reference of the earlier tiles and the tile is redone only
+// when the row maximum jumped past the threshold).  Reading the fp32 scores out of tensor
+// memory is the kernel's largest load: 64 KB per 128x128 tile against a measured ~48 B/clk per
+// SM for tcgen05.ld (the same rate bounds the GEMM epilogues: 128 KB in ~2.7k clocks).
 // P never touches shared memory.  O stays in tensor memory across key tiles.  The
 // exponent reference m only moves when the running maximum grows by more than a
 // threshold (then the O row is rescaled in tensor memory); otherwise P simply grows
@@ -612,8 +619,9 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
 // (sequence, 128-row query tile, head), item n going to CTA n mod gridDim.x.  Barriers,
 // tensor memory and the launch are paid once per CTA instead of once per item, and the
 // loader runs ahead: the next item's Q/K/V tiles are requested while the current item's last
-// key tiles are still being processed.  Per item the work is exactly that of
-// mha_fwd_kernel<1> (same tile_row_max / tile_probs, same MMAs).
+// key tiles are still being processed.  Per item the MMAs are those of mha_fwd_kernel<1>; the
+// softmax follows the PSEP / ONEPASS scheme described at the kernel (default) or, selectable, the
+// two-pass scheme of mha_fwd_kernel<1> (same tile_row_max / tile_probs).
 // ------------------------------------------------------------------------------------------
 struct MhaPersistentArgs {
   __half* ctx;
@@ -849,14 +857,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           break;
         }
         tc_fence_after();
-        if (ONEPASS && j > 0) {
-          // ---- optimistic single pass with the reference of the earlier tiles
+        if (ONEPASS) {
+          // ---- optimistic single pass with the reference of the earlier tiles (first tile of an item:
+          // with the maximum of its first 32 keys)
           const uint32_t t_p = t_lane + kTmemP;
           uint32_t va[32], vb[32], pk0[16], pk1[16];
           float xmax = -INFINITY, l_tile = 0.f;
           tmem_ld_32x32(t_s, va);
           tmem_ld_wait();
           tmem_ld_32x32(t_s + 32, vb);
+          if (j == 0) m_ref = c * (full_tile ? chunk_max<false>(va, 0, kv_valid) : chunk_max<true>(va, 0, kv_valid));
           l_tile += full_tile ? chunk_probs_track<false>(va, 0, kv_valid, c, m_ref, pk0, xmax)
                               : chunk_probs_track<true>(va, 0, kv_valid, c, m_ref, pk0, xmax);
           tmem_ld_wait();
@@ -864,12 +874,15 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           l_tile += full_tile ? chunk_probs_track<false>(vb, 32, kv_valid, c, m_ref, pk1, xmax)
                               : chunk_probs_track<true>(vb, 32, kv_valid, c, m_ref, pk1, xmax);
           // P (and O) belong to the P V MMAs of the previous key tile until those have retired; the first
-          // two chunks were computed in the meantime
-          if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-            ok = false;
-            break;
+          // two chunks were computed in the meantime.  (First tile of an item: the wait for the previous
+          // item's O at its end already covered that.)
+          if (j > 0) {
+            if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
           }
-          tc_fence_after();
           tmem_st_32x16(t_p, pk0);
           tmem_st_32x16(t_p + 16, pk1);
           tmem_ld_wait();
@@ -887,7 +900,7 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
             const float m_new = m_ref + fmaxf(xmax, 0.f);
             const float f = ex2_approx(m_ref - m_new);
 #pragma unroll
-            for (int cb = 0; cb < kHeadDim; cb += 32) {
+            for (int cb = 0; cb < (j > 0 ? kHeadDim : 0); cb += 32) {  // (no O yet on the first tile)
               uint32_t v[32];
               tmem_ld_32x32(t_o + cb, v);
               tmem_ld_wait();
