@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ bias,
                       const __half* __restrict__ residual, const void* __restrict__ gamma,
                       const void* __restrict__ beta, __half* __restrict__ out, const int* __restrict__ m_dev,
-                      int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps) {
+                      int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps, LnSplit split) {
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5;
@@ -123,6 +123,13 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
         const float4 a = __ldg(xf + 2 * v), b = __ldg(xf + 2 * v + 1);
         val[it][0] = a.x; val[it][1] = a.y; val[it][2] = a.z; val[it][3] = a.w;
         val[it][4] = b.x; val[it][5] = b.y; val[it][6] = b.z; val[it][7] = b.w;
+        // the sum arrives in `split.n` fp32 parts (K ranges of the GEMM before)
+        for (int sp = 1; sp < split.n; ++sp) {
+          const float4* xs = xf + sp * (split.stride / 4);
+          const float4 c = __ldg(xs + 2 * v), d = __ldg(xs + 2 * v + 1);
+          val[it][0] += c.x; val[it][1] += c.y; val[it][2] += c.z; val[it][3] += c.w;
+          val[it][4] += d.x; val[it][5] += d.y; val[it][6] += d.z; val[it][7] += d.w;
+        }
       } else {
         unpack8(__ldg(x4 + v), val[it]);
       }
@@ -178,11 +185,12 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
 template <bool RESTORE, bool GB_FP32, bool X_FP32>
 cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, const void* x, const __half* bias,
                            const __half* residual, const void* gamma, const void* beta, __half* out,
-                           const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps) {
+                           const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps,
+                           LnSplit split) {
 #define BT_LN_CASE(NV)                                                                                        \
   case NV:                                                                                                    \
     return launch_pdl(layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV>, grid, dim3(kLnWarps * 32), 0, stream,  \
-                      x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps);
+                      x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps, split);
   switch (nvec_needed) {
     BT_LN_CASE(1)
     BT_LN_CASE(2)
@@ -320,41 +328,43 @@ template <bool RESTORE>
 static cudaError_t launch_ln_dispatch(bool gb_fp32, bool x_fp32, int nv, dim3 grid, cudaStream_t stream, const void* x,
                                       const __half* bias, const __half* residual, const void* gamma, const void* beta,
                                       __half* out, const int* m_dev, int m_rows, const int* batch_idx, int S,
-                                      int hidden, float eps) {
+                                      int hidden, float eps, LnSplit split) {
   if (gb_fp32) {
     if (x_fp32)
       return launch_ln_nvec<RESTORE, true, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                 batch_idx, S, hidden, eps);
+                                                 batch_idx, S, hidden, eps, split);
     return launch_ln_nvec<RESTORE, true, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                batch_idx, S, hidden, eps);
+                                                batch_idx, S, hidden, eps, split);
   }
   if (x_fp32)
     return launch_ln_nvec<RESTORE, false, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                batch_idx, S, hidden, eps);
+                                                batch_idx, S, hidden, eps, split);
   return launch_ln_nvec<RESTORE, false, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                               batch_idx, S, hidden, eps);
+                                               batch_idx, S, hidden, eps, split);
 }
 
 cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                              const void* gamma, const void* beta, bool gb_fp32, __half* out, const int* m_dev,
-                             int m_rows, int hidden, float eps, cudaStream_t stream) {
+                             int m_rows, int hidden, float eps, cudaStream_t stream, LnSplit split) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || m_rows <= 0) return cudaErrorInvalidValue;
+  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0)) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   dim3 grid(ln_grid((m_rows + kLnWarps - 1) / kLnWarps));
   return launch_ln_dispatch<false>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev,
-                                   m_rows, nullptr, 0, hidden, eps);
+                                   m_rows, nullptr, 0, hidden, eps, split);
 }
 
 cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                                      const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
                                      const int* batch_idx, int B, int S, int hidden, float eps,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, LnSplit split) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || B <= 0 || S <= 0) return cudaErrorInvalidValue;
+  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0)) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   const long long rows = static_cast<long long>(B) * S;
   dim3 grid(ln_grid((rows + kLnWarps - 1) / kLnWarps));
   return launch_ln_dispatch<true>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out_padded,
-                                  nullptr, static_cast<int>(rows), batch_idx, S, hidden, eps);
+                                  nullptr, static_cast<int>(rows), batch_idx, S, hidden, eps, split);
 }
 
 cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev, int m_rows, int n, int gelu_kind,

@@ -197,6 +197,10 @@ static int fail_cuda(bt_handle h, cudaError_t e, const char* where) {
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Split-K of the fp32-sum GEMMs is considered up to this many allocated rows, in at most this many ranges.
+constexpr size_t kSplitKMaxRows = 1024;
+constexpr int kMaxSplitK = 8;
+
 struct Workspace {
   int* batch_idx;
   int* word_idx;
@@ -223,7 +227,8 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   w.xb = reinterpret_cast<__half*>(take(rh));
   w.qkv = reinterpret_cast<__half*>(take(3 * rh));
   w.ctx = reinterpret_cast<__half*>(take(rh));
-  w.pre = reinterpret_cast<float*>(take(2 * rh));
+  // fp32 sums; with few rows the GEMMs that produce them cut K into up to kMaxSplitK ranges, one sum each
+  w.pre = reinterpret_cast<float*>(take(2 * rh * (rows <= kSplitKMaxRows ? kMaxSplitK : 1)));
   w.y = reinterpret_cast<__half*>(take(rh));
   w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
   w.ln_stats_bytes = rows * static_cast<size_t>(hidden / 128 > 0 ? hidden / 128 : 1) * 16;
@@ -242,7 +247,7 @@ struct LnArgs {
 
 static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __half* out, const void* bias,
                     const __half* residual, const int* m_dev, int m_rows, int N, int K, int epi, int gelu_kind,
-                    cudaStream_t stream, const LnArgs* ln = nullptr) {
+                    cudaStream_t stream, const LnArgs* ln = nullptr, int split_k = 1) {
   GemmLaunch g;
   bool ok = h->tmap(&g.tm_a, A, m_rows, K, 64, 128) && h->tmap(&g.tm_b, W, K, N, 64, 64);
   if (epi == BT_EPI_BIAS_RESIDUAL_LAYERNORM)  // `out` is only the statistics scratch; the store map is the fp16 result's
@@ -263,6 +268,7 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
   g.epilogue = epi;
   g.gelu_kind = gelu_kind;
   g.block_n = 0;
+  g.split_k = split_k;
   g.status = h->status;
   g.num_sms = h->num_sms;
   if (ln != nullptr) {
@@ -356,6 +362,15 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
   // the row kernel spreads the few rows over more SMs.
   const bool fuse_any = want_fused_ln(h, rows);
   const bool fuse_ln = fuse_any && !h->fused_ln_ffn2_only;
+  // Few rows: the two GEMMs that feed a LayerNorm cut K into ranges (one fp32 sum each, `rows * H`
+  // floats apart in `pre`) and the LayerNorm kernel adds them up.
+  auto split_for = [&](int K) {
+    if (static_cast<size_t>(rows) > kSplitKMaxRows) return 1;
+    const int s = gemm_pick_split_k(rows, H, K, h->num_sms);
+    return s <= kMaxSplitK ? s : 1;
+  };
+  const int split_attn = split_for(H), split_ffn2 = split_for(F);
+  const long long split_stride = static_cast<long long>(rows) * H;
   cudaError_t e = cudaSuccess;
   if (fuse_ln) {
     LnArgs ln{++h->ln_epoch, ws.y, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta, gb32, h->cfg.ln_eps};
@@ -365,12 +380,13 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
       return rc;
   } else {
     if ((rc = run_gemm(h, BT_PROF_GEMM_ATTN_OUT, ws.ctx, w.attr_output_kernel, reinterpret_cast<__half*>(ws.pre),
-                       w.attr_output_bias, x_in, m_dev, rows, H, H, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
+                       w.attr_output_bias, x_in, m_dev, rows, H, H, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream, nullptr,
+                       split_attn)) != BT_OK)
       return rc;
     {
       LaunchScope scope(h, BT_PROF_LAYERNORM, stream);
       e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.attr_output_layernorm_gamma, w.attr_output_layernorm_beta,
-                           gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream);
+                           gb32, ws.y, m_dev, rows, H, h->cfg.ln_eps, stream, LnSplit{split_attn, split_stride});
     }
     if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
   }
@@ -383,15 +399,16 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
                     ws.y, m_dev, rows, H, F, BT_EPI_BIAS_RESIDUAL_LAYERNORM, 0, stream, &ln);
   }
   if ((rc = run_gemm(h, BT_PROF_GEMM_FFN2, ws.mid, w.output_kernel, reinterpret_cast<__half*>(ws.pre), w.output_bias,
-                     ws.y, m_dev, rows, H, F, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream)) != BT_OK)
+                     ws.y, m_dev, rows, H, F, BT_EPI_BIAS_RESIDUAL_F32OUT, 0, stream, nullptr, split_ffn2)) != BT_OK)
     return rc;
   LaunchScope scope(h, BT_PROF_LAYERNORM, stream);
   if (restore_to != nullptr)
     e = launch_layernorm_restore(ws.pre, true, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32,
-                                 restore_to, batch_idx, B, S_or_maxlen, H, h->cfg.ln_eps, stream);
+                                 restore_to, batch_idx, B, S_or_maxlen, H, h->cfg.ln_eps, stream,
+                                 LnSplit{split_ffn2, split_stride});
   else
     e = launch_layernorm(ws.pre, true, nullptr, nullptr, w.output_layernorm_gamma, w.output_layernorm_beta, gb32, x_out,
-                         m_dev, rows, H, h->cfg.ln_eps, stream);
+                         m_dev, rows, H, h->cfg.ln_eps, stream, LnSplit{split_ffn2, split_stride});
   if (e != cudaSuccess) return fail_cuda(h, e, "layernorm launch");
   return BT_OK;
 }

@@ -89,6 +89,10 @@ struct GemmArgs {
   int gb_fp32;
   float eps;
   uint32_t ln_epoch;  // fused LayerNorm: tag of this launch in the statistics scratch (see gemm_f16_ln_kernel)
+  // split-K (kEpiSplitKF32): K is cut into `split_k` ranges, range s writes its fp32 partial sum to
+  // out + s * split_stride floats; range 0 also adds bias and residual
+  int split_k;
+  long long split_stride;
   long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
@@ -103,6 +107,7 @@ __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
   if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 8 + slot] = clock64();
 }
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
+long long g_dbg_split_k = 0;  // 0 = policy, < 0 = never, > 0 = that many ranges whenever the shape allows
 
 // ------------------------------------------------------------------------------------------
 // Epilogue of one 128 x TILE_N accumulator tile, executed by the 8 epilogue warps of a CTA.
@@ -120,10 +125,12 @@ __device__ __forceinline__ void tma_store_wait_read_n() {
 template <int TILE_N, int EPI, bool TMA_STORE, int STG_BUFS>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtensorMap* tm_out, uint8_t* stg,
                                               uint32_t tmem_acc, int m0, int n0, int M, int quarter, int col_half,
-                                              int lane, const uint4* resv) {
+                                              int lane, const uint4* resv, int split = 0) {
   constexpr int kColsPerWarp = TILE_N / 2;
-  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kSplitK = (EPI == kEpiSplitKF32);
+  constexpr bool kF32Out = (EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kSplitK;
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kSplitK;
+  static_assert(!(kSplitK && TMA_STORE), "split-K partials are stored by the threads");
   // 128 bytes of output per row and chunk: 32 fp32 or 64 fp16 columns.
   constexpr int kChunk = kF32Out ? 32 : (kColsPerWarp >= 64 ? 64 : 32);
   constexpr int kNChunks = kColsPerWarp / kChunk;
@@ -151,7 +158,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
     for (int h = 0; h < kHalves; ++h)
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[h * 32 + i] = __uint_as_float(raw[ci & 1][h][i]);
-    if (EPI != BT_EPI_NONE) {
+    if (EPI != BT_EPI_NONE && (!kSplitK || split == 0)) {
       const uint4* bp = reinterpret_cast<const uint4*>(args.bias + gcol);
 #pragma unroll
       for (int q = 0; q < kChunk / 8; ++q) {
@@ -174,7 +181,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
         for (int i = 0; i < kChunk; ++i) v[i] = gelu_erf_fast(v[i]);
       }
     }
-    const size_t off = static_cast<size_t>(row) * args.N + gcol;
+    const size_t off = static_cast<size_t>(row) * args.N + gcol +
+                       (kSplitK ? static_cast<size_t>(split) * static_cast<size_t>(args.split_stride) : 0);
     if (kHasResidual) {
 #pragma unroll
       for (int q = 0; q < kChunk / 8; ++q) {
@@ -233,13 +241,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
 // its latency hides behind the main loop of the tile.
 template <int TILE_N, int EPI>
 __device__ __forceinline__ void prefetch_residual(const GemmArgs& args, int m0, int n0, int M, int quarter,
-                                                  int col_half, int lane, uint4* resv) {
+                                                  int col_half, int lane, uint4* resv, int split = 0) {
   constexpr int kColsPerWarp = TILE_N / 2;
   constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT ||
-                                 EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM);
+                                 EPI == BT_EPI_BIAS_RESIDUAL_LAYERNORM || EPI == kEpiSplitKF32);
   if (kHasResidual) {
     const int row = m0 + quarter * 32 + lane;
-    const bool row_ok = row < M;
+    const bool row_ok = row < M && split == 0;  // only the first K range carries the residual
     const uint4* rp = reinterpret_cast<const uint4*>(args.residual + static_cast<size_t>(row) * args.N + n0 +
                                                      col_half * kColsPerWarp);
 #pragma unroll
@@ -256,7 +264,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_out, const GemmArgs args) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
-  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT);
+  constexpr bool kSplitK = (EPI == kEpiSplitKF32);
+  constexpr bool kHasResidual = (EPI == BT_EPI_BIAS_RESIDUAL || EPI == BT_EPI_BIAS_RESIDUAL_F32OUT) || kSplitK;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -309,12 +318,20 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   }
   const int n_tiles = args.N / BLOCK_N;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = args.K / kBlockK;
-  // The li-th tile of this CTA: tiles go round-robin over the CTAs.
-  auto tile_at = [&](int li, int& m0, int& n0) -> bool {
-    const int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
+  const int splits = kSplitK ? args.split_k : 1;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * splits;
+  const int num_kb = args.K / kBlockK / splits;  // K blocks per tile (per K range with split-K)
+  // The li-th tile of this CTA: tiles go round-robin over the CTAs.  With split-K a tile is an
+  // (output tile, K range) pair; `sp` is the range.
+  auto tile_at = [&](int li, int& m0, int& n0, int& sp) -> bool {
+    int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
     if (tile >= total_tiles) return false;
+    sp = 0;
+    if (kSplitK) {
+      sp = tile / mn_tiles;
+      tile -= sp * mn_tiles;
+    }
     m0 = (tile / n_tiles) * kBlockM;
     n0 = (tile % n_tiles) * BLOCK_N;
     return true;
@@ -326,9 +343,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int m0 = 0, n0 = 0;
-      for (int li = 0; ok && tile_at(li, m0, n0); ++li) {
-        for (int kb = 0; kb < num_kb; ++kb) {
+      int m0 = 0, n0 = 0, sp = 0;
+      for (int li = 0; ok && tile_at(li, m0, n0, sp); ++li) {
+        const int kb_end = (sp + 1) * num_kb;
+        for (int kb = sp * num_kb; kb < kb_end; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
                                  kStatusGemmProducerTimeout)) {
             ok = false;
@@ -354,8 +372,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int m0 = 0, n0 = 0;
-      for (int it = 0; ok && tile_at(it, m0, n0); ++it) {
+      int m0 = 0, n0 = 0, sp = 0;
+      for (int it = 0; ok && tile_at(it, m0, n0, sp); ++it) {
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait_bounded(&acc_empty[as], aphase ^ 1u, abort_flag, args.status, kStatusGemmMmaTimeout)) {
@@ -395,17 +413,17 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int col_half = e >> 2;   // which half of the tile's columns
     uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;  // 32 rows x 128 B, swizzled
-    int m0 = 0, n0 = 0;
-    for (int it = 0; tile_at(it, m0, n0); ++it) {
+    int m0 = 0, n0 = 0, sp = 0;
+    for (int it = 0; tile_at(it, m0, n0, sp); ++it) {
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       uint4 resv[kHasResidual ? BLOCK_N / 16 : 1];
-      prefetch_residual<BLOCK_N, EPI>(args, m0, n0, M, quarter, col_half, lane, resv);
+      prefetch_residual<BLOCK_N, EPI>(args, m0, n0, M, quarter, col_half, lane, resv, sp);
       if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
       tc_fence_after();
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
       epilogue_tile<BLOCK_N, EPI, Cfg::kTmaStore, 1>(args, &tm_out, stg, tmem_base + as * BLOCK_N, m0, n0, M, quarter,
-                                                  col_half, lane, resv);
+                                                  col_half, lane, resv, sp);
       if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
       tc_fence_before();
       __syncwarp();
@@ -1135,7 +1153,7 @@ cudaError_t launch_one(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stre
   }
   const int n_tiles = g.N / BLOCK_N;
   const int m_tiles = (g.m_rows + kBlockM - 1) / kBlockM;
-  long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+  long long tiles = static_cast<long long>(n_tiles) * m_tiles * (EPI == kEpiSplitKF32 ? a.split_k : 1);
   int grid = static_cast<int>(tiles < g.num_sms ? tiles : g.num_sms);
   if (grid < 1) grid = 1;
   return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out, a);
@@ -1242,6 +1260,25 @@ bool use_pair_kernel(const GemmLaunch& g) {
 
 }  // namespace
 
+// Few rows and a long K leave most SMs idle while a handful stream the weights one K block
+// after the other; cutting K spreads that stream.  The widest cut whose (tile, range) pairs number at
+// most one and a half times the SMs (the row count is an upper bound: padded rows make no tiles), with
+// at least three K blocks per range.
+int gemm_pick_split_k(int m_rows, int N, int K, int num_sms) {
+  if (N % 64 != 0 || K % kBlockK != 0) return 1;
+  if (g_dbg_split_k != 0)
+    return (g_dbg_split_k > 0 && (K / kBlockK) % g_dbg_split_k == 0) ? static_cast<int>(g_dbg_split_k) : 1;
+  const long long tiles = static_cast<long long>((m_rows + kBlockM - 1) / kBlockM) * (N / 64);
+  const int num_kb = K / kBlockK;
+  const int cands[3] = {8, 4, 2};
+  for (int i = 0; i < 3; ++i) {
+    const int s = cands[i];
+    if (num_kb % s != 0 || num_kb / s < 3) continue;
+    if (tiles * s <= num_sms + num_sms / 2) return s;
+  }
+  return 1;
+}
+
 int gemm_pick_block_n(int m_rows, int N, int num_sms) {
   if (g_dbg_force_block_n != 0) return static_cast<int>(g_dbg_force_block_n);
   const int m_tiles = (m_rows + kBlockM - 1) / kBlockM;
@@ -1285,6 +1322,16 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   const uint32_t sbo = g_dbg_b_sbo ? static_cast<uint32_t>(g_dbg_b_sbo) : 1024u;
   a.b_desc_hi = make_smem_desc_hi(lbo, sbo);
   a.b_kstep_bytes = g_dbg_b_kstep ? static_cast<uint32_t>(g_dbg_b_kstep) : 2048u;
+  a.split_k = 1;
+  a.split_stride = 0;
+  if (g.split_k > 1) {
+    if (g.epilogue != BT_EPI_BIAS_RESIDUAL_F32OUT || g.N % 64 != 0 || (g.K / kBlockK) % g.split_k != 0)
+      return cudaErrorInvalidValue;
+    a.split_k = g.split_k;
+    a.split_stride = static_cast<long long>(g.m_rows) * g.N;
+    a.idesc = make_idesc_f16(kBlockM, 64, 0, 1);
+    return launch_one<64, kEpiSplitKF32>(g, a, stream);
+  }
   if (use_pair_kernel(g)) {
     a.idesc = make_idesc_f16(256, 256, 0, 1);  // M = 256 across the pair
     return launch_pair_epi(g, a, stream);
@@ -1310,8 +1357,9 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // the W operand / the tile width so that encodings can be compared on a device
 // without rebuilding.  key: 1 = LBO bytes, 2 = SBO bytes, 3 = K-step bytes,
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
-// N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0).
-// value 0 restores the default for keys 1-5.
+// N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0),
+// 7 = split-K of the fp32-sum GEMMs (0 policy, < 0 never, > 0 that many K ranges).
+// value 0 restores the default for keys 1-5 and 7.
 // Device buffer of 148 x 16 x 8 long long for clock64 stamps of the GEMM kernels (null = off):
 // slots 0/1 MMA warp (accumulator free, last commit), 2/3 epilogue warp 2 (accumulator ready, tile
 // done), 4..6 LayerNorm kernel only (sums written back, partial published, partials of all peers seen).
@@ -1325,6 +1373,7 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 2: bt::g_dbg_b_sbo = value; return 0;
     case 3: bt::g_dbg_b_kstep = value; return 0;
     case 4: bt::g_dbg_force_block_n = value; return 0;
+    case 7: bt::g_dbg_split_k = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
     case 6: bt::set_pdl_enabled(value != 0); return 0;
     default: return 1;

@@ -54,6 +54,10 @@ cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int*
                                 int hidden, cudaStream_t stream);
 
 // ---- GEMM ---------------------------------------------------------------------
+// Epilogue of the split-K form of BT_EPI_BIAS_RESIDUAL_F32OUT (internal: chosen through GemmLaunch::split_k).
+constexpr int kEpiSplitKF32 = 64;
+// Ranges to cut K into for an fp32-sum GEMM of `m_rows` x N over K; 1 = no split.
+int gemm_pick_split_k(int m_rows, int N, int K, int num_sms);
 struct GemmLaunch {
   CUtensorMap tm_a;  // A [m_rows, K], box {64, 128}
   CUtensorMap tm_b;  // W [K, N],     box {64, 64}
@@ -78,6 +82,10 @@ struct GemmLaunch {
   int epilogue;      // BT_EPI_*
   int gelu_kind;     // BT_GELU_*
   int block_n;       // 64, 128 or 256; 0 = choose from the shape
+  // BT_EPI_BIAS_RESIDUAL_F32OUT only: > 1 cuts K into that many ranges, each handled by its own CTA
+  // (few rows, long K: more SMs stream the weights).  Range s writes an fp32 partial sum to
+  // out + s * m_rows * N floats, range 0 with bias and residual; the consumer adds the ranges up.
+  int split_k = 1;
   int* status;       // device status word
   int num_sms;
 };
@@ -103,13 +111,18 @@ struct MhaLaunch {
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
 
 // ---- element-wise / normalisation -------------------------------------------
+// An fp32 input may arrive as `n` partial sums `stride` floats apart (the K ranges of a split-K GEMM).
+struct LnSplit {
+  int n = 1;
+  long long stride = 0;
+};
 cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, const __half* residual, const void* gamma,
                              const void* beta, bool gb_fp32, __half* out, const int* m_dev, int m_rows,
-                             int hidden, float eps, cudaStream_t stream);
+                             int hidden, float eps, cudaStream_t stream, LnSplit split = LnSplit());
 cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                                      const void* gamma, const void* beta, bool gb_fp32, __half* out_padded,
                                      const int* batch_idx, int B, int S, int hidden, float eps,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, LnSplit split = LnSplit());
 cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev, int m_rows, int n,
                                  int gelu_kind, cudaStream_t stream);
 cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int nh, int S, float scale,

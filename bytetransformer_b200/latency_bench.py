@@ -55,6 +55,8 @@ def main():
                     help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
     ap.add_argument("--mha-variant", type=int, default=-1,
                     help="A/B aid: 0 default policy, 1 one CTA per (query tile, head, sequence), 3 persistent CTAs")
+    ap.add_argument("--split-k", type=int, default=0,
+                    help="A/B aid: K ranges of the GEMMs that feed a LayerNorm: 0 policy, -1 never, n > 0 forced")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
@@ -73,6 +75,9 @@ def main():
     if args.no_pdl:
         from . import _abi
         _abi.load().bt_debug_set(6, 0)
+    if args.split_k != 0:
+        from . import _abi
+        _abi.load().bt_debug_set(7, args.split_k)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
     H = BERT_BASE.hidden
     for S in [int(s) for s in args.seqs.split(",")]:

@@ -27,7 +27,7 @@ def _valid(lens, S):
 
 
 def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf", eps=1e-6, per_layer_op=False,
-              fused_ln=None):
+              fused_ln=None, split_k=None):
     from bytetransformer_b200.encoder import Encoder, bert_transformer
     from oracle.bert_oracle import build_attr_mask
     H = nh * 64
@@ -49,7 +49,14 @@ def _run_case(dev, B, S, nh, n_layers, lens, recipe, seed, gb32=False, gelu="erf
         if fused_ln is not None:  # 0 = LayerNorm as its own kernel, 2 = always inside the GEMM kernel
             from bytetransformer_b200 import _abi
             assert _abi.load().bt_debug_set_fused_layernorm(enc._h, fused_ln) == 0
-        got = enc.forward(xd, md)
+        if split_k is not None:  # K ranges of the two GEMMs that feed a LayerNorm: -1 never, n > 0 forced
+            from bytetransformer_b200 import _abi
+            assert _abi.load().bt_debug_set(7, split_k) == 0
+        try:
+            got = enc.forward(xd, md)
+        finally:
+            if split_k is not None:
+                _abi.load().bt_debug_set(7, 0)
         assert enc.device_status() == 0
         enc.close()
     v = _valid(lens, S)
@@ -146,6 +153,18 @@ def test_layernorm_inside_gemm_or_separate(cuda_device, nh, gb32, fused_ln):
     _run_case(cuda_device, 6, 300, nh, 3, lens, "normal", seed=21, gb32=gb32, fused_ln=fused_ln)
 
 
+@pytest.mark.parametrize("split_k", [-1, 2, 4, 6])
+@pytest.mark.parametrize("B,S,nh", [(1, 64, 12), (5, 130, 16)])
+def test_split_k_sums(cuda_device, B, S, nh, split_k):
+    """The attention-output and FFN2 GEMMs with K cut into ranges (one CTA and one fp32 partial sum per
+    range, added up by the LayerNorm kernel) against the oracle; -1 = one range.  Hidden 768 has 12 and
+    48 K blocks, hidden 1024 has 16 and 64, so 6 ranges only divide the former and the latter falls back
+    to one range."""
+    g = torch.Generator().manual_seed(5 + S)
+    lens = [round(0.6 * S)] if B == 1 else torch.randint(1, S + 1, (B,), generator=g).tolist()
+    _run_case(cuda_device, B, S, nh, 3, lens, "normal", seed=33, split_k=split_k, fused_ln=0)
+
+
 @pytest.mark.parametrize("S", [64, 320, 1024])
 def test_config2_batch1(cuda_device, S):
     """Batch 1, valid length round(0.6*S), 12 layers."""
@@ -177,10 +196,12 @@ def test_packed_entry_matches_padded(cuda_device):
     xp = pack_rows(x, bi)[:T].contiguous()
     outp = enc.forward_packed(xp, bi, max(lens))
     v = _valid(lens, S)
-    # same kernels except the last LayerNorm (padded: separate kernel with scatter, two-pass variance;
-    # packed: may be fused into the GEMM, one-pass variance): equal up to an fp16 ulp or two
+    # same kernels except where the row count decides: the last LayerNorm (padded: separate kernel with
+    # scatter, two-pass variance; packed: may be fused into the GEMM, one-pass variance) and the number of
+    # K ranges the fp32 sums before a LayerNorm are accumulated in (B*S rows against T): equal up to an
+    # fp16 ulp or two on a few elements
     d = (outp.cpu().float() - padded.cpu()[v].float()).abs()
-    assert d.max().item() <= 4e-3 and d.mean().item() <= 2e-5, (d.max().item(), d.mean().item())
+    assert d.max().item() <= 4e-3 and d.mean().item() <= 1e-4, (d.max().item(), d.mean().item())
     assert enc.device_status() == 0
     enc.close()
 
