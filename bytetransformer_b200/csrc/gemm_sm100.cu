@@ -93,6 +93,7 @@ struct GemmArgs {
   // out + s * split_stride floats; range 0 also adds bias and residual
   int split_k;
   long long split_stride;
+  int early_w;  // one-CTA kernel: request the first tile's W blocks before the wait for the kernel before
   long long* timing;  // diagnostics: clock64 stamps per CTA and tile (null = off)
   uint64_t a_desc_hi;
   uint64_t b_desc_hi;
@@ -107,6 +108,7 @@ __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
   if (timing != nullptr && it < 16 && blockIdx.x < 148) timing[(blockIdx.x * 16 + it) * 8 + slot] = clock64();
 }
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
+long long g_dbg_early_w = 1;  // 1 = W blocks of the first tile requested before the dependency wait
 long long g_dbg_split_k = 0;  // 0 = policy, < 0 = never, > 0 = that many ranges whenever the shape allows
 
 // ------------------------------------------------------------------------------------------
@@ -308,32 +310,54 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Everything above touched only this CTA's own resources; from here on global memory
-  // written by earlier kernels is read (the row count first of all).
+  const int n_tiles = args.N / BLOCK_N;
+  const int splits = kSplitK ? args.split_k : 1;
+  const int num_kb = args.K / kBlockK / splits;  // K blocks per tile (per K range with split-K)
+  // Tile number -> (K range, column block, row block).  The K range and the column block come from
+  // the low part of the number, so those of a CTA's first tile (number blockIdx.x) are known before
+  // the row count is.
+  auto tile_cols = [&](int tile, int& n0, int& sp) -> int {
+    sp = 0;
+    if (kSplitK) {
+      sp = tile % splits;
+      tile /= splits;
+    }
+    n0 = (tile % n_tiles) * BLOCK_N;
+    return tile / n_tiles;
+  };
+  // The weights are written by no kernel of the chain, so the W blocks of the first tile are
+  // requested before the wait for the kernel before (whose tail they then overlap): the first
+  // `pre_kb` stages get their full byte count armed and their W part requested here, their A
+  // part after the wait.
+  const int pre_kb = args.early_w ? (num_kb < kStages ? num_kb : kStages) : 0;
+  if (warp == 0 && lane == 0) {
+    int n0 = 0, sp = 0;
+    tile_cols(static_cast<int>(blockIdx.x), n0, sp);
+    for (int kb = 0; kb < pre_kb; ++kb) {
+      uint8_t* sb = smem + kb * Cfg::kStageBytes + kABytes;
+      mbar_arrive_expect_tx(&full_bar[kb], Cfg::kStageBytes);
+#pragma unroll
+      for (int c = 0; c < BLOCK_N / 64; ++c)
+        tma_load_2d(sb + c * (64 * kBlockK * 2), &tm_b, &full_bar[kb], n0 + c * 64, (sp * num_kb + kb) * kBlockK);
+    }
+  }
+
+  // Everything above touched only this CTA's own resources and the weights; from here on global
+  // memory written by earlier kernels is read (the row count first of all).
   pdl_wait();
   int M = args.m_rows;
   if (args.m_dev != nullptr) {
     const int md = __ldg(args.m_dev);
     M = md < M ? md : M;
   }
-  const int n_tiles = args.N / BLOCK_N;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  const int splits = kSplitK ? args.split_k : 1;
-  const int mn_tiles = m_tiles * n_tiles;
-  const int total_tiles = mn_tiles * splits;
-  const int num_kb = args.K / kBlockK / splits;  // K blocks per tile (per K range with split-K)
+  const int total_tiles = m_tiles * n_tiles * splits;
   // The li-th tile of this CTA: tiles go round-robin over the CTAs.  With split-K a tile is an
   // (output tile, K range) pair; `sp` is the range.
   auto tile_at = [&](int li, int& m0, int& n0, int& sp) -> bool {
-    int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
+    const int tile = static_cast<int>(blockIdx.x) + li * static_cast<int>(gridDim.x);
     if (tile >= total_tiles) return false;
-    sp = 0;
-    if (kSplitK) {
-      sp = tile / mn_tiles;
-      tile -= sp * mn_tiles;
-    }
-    m0 = (tile / n_tiles) * kBlockM;
-    n0 = (tile % n_tiles) * BLOCK_N;
+    m0 = tile_cols(tile, n0, sp) * kBlockM;
     return true;
   };
 
@@ -344,21 +368,33 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int m0 = 0, n0 = 0, sp = 0;
+      if (!tile_at(0, m0, n0, sp)) {
+        // No tile for this CTA after all (fewer valid rows than allocated): complete the armed
+        // stages with some A block and wait for them, so that no copy is in flight at exit.
+        for (int kb = 0; kb < pre_kb; ++kb) tma_load_2d(smem + kb * Cfg::kStageBytes, &tm_a, &full_bar[kb], 0, 0);
+        for (int kb = 0; kb < pre_kb; ++kb)
+          if (!mbar_wait_bounded(&full_bar[kb], 0u, abort_flag, args.status, kStatusGemmProducerTimeout)) break;
+      }
       for (int li = 0; ok && tile_at(li, m0, n0, sp); ++li) {
-        const int kb_end = (sp + 1) * num_kb;
-        for (int kb = sp * num_kb; kb < kb_end; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
-                                 kStatusGemmProducerTimeout)) {
-            ok = false;
-            break;
-          }
+        for (int i = 0; i < num_kb; ++i) {
+          const int kb = sp * num_kb + i;
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + kABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, &tm_a, &full_bar[stage], kb * kBlockK, m0);
+          if (li == 0 && i < pre_kb) {
+            // armed before the wait, W already requested (stage == i here)
+            tma_load_2d(sa, &tm_a, &full_bar[stage], kb * kBlockK, m0);
+          } else {
+            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
+                                   kStatusGemmProducerTimeout)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_2d(sa, &tm_a, &full_bar[stage], kb * kBlockK, m0);
 #pragma unroll
-          for (int c = 0; c < BLOCK_N / 64; ++c)
-            tma_load_2d(sb + c * (64 * kBlockK * 2), &tm_b, &full_bar[stage], n0 + c * 64, kb * kBlockK);
+            for (int c = 0; c < BLOCK_N / 64; ++c)
+              tma_load_2d(sb + c * (64 * kBlockK * 2), &tm_b, &full_bar[stage], n0 + c * 64, kb * kBlockK);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -1324,6 +1360,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   a.b_kstep_bytes = g_dbg_b_kstep ? static_cast<uint32_t>(g_dbg_b_kstep) : 2048u;
   a.split_k = 1;
   a.split_stride = 0;
+  a.early_w = g_dbg_early_w != 0 ? 1 : 0;
   if (g.split_k > 1) {
     if (g.epilogue != BT_EPI_BIAS_RESIDUAL_F32OUT || g.N % 64 != 0 || (g.K / kBlockK) % g.split_k != 0)
       return cudaErrorInvalidValue;
@@ -1358,7 +1395,8 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // without rebuilding.  key: 1 = LBO bytes, 2 = SBO bytes, 3 = K-step bytes,
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
 // N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0),
-// 7 = split-K of the fp32-sum GEMMs (0 policy, < 0 never, > 0 that many K ranges).
+// 7 = split-K of the fp32-sum GEMMs (0 policy, < 0 never, > 0 that many K ranges),
+// 8 = W blocks of a CTA's first tile requested before the dependency wait (1, default) or after (0).
 // value 0 restores the default for keys 1-5 and 7.
 // Device buffer of 148 x 16 x 8 long long for clock64 stamps of the GEMM kernels (null = off):
 // slots 0/1 MMA warp (accumulator free, last commit), 2/3 epilogue warp 2 (accumulator ready, tile
@@ -1374,6 +1412,7 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 3: bt::g_dbg_b_kstep = value; return 0;
     case 4: bt::g_dbg_force_block_n = value; return 0;
     case 7: bt::g_dbg_split_k = value; return 0;
+    case 8: bt::g_dbg_early_w = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
     case 6: bt::set_pdl_enabled(value != 0); return 0;
     default: return 1;

@@ -57,6 +57,8 @@ def main():
                     help="A/B aid: 0 default policy, 1 one CTA per (query tile, head, sequence), 3 persistent CTAs")
     ap.add_argument("--split-k", type=int, default=0,
                     help="A/B aid: K ranges of the GEMMs that feed a LayerNorm: 0 policy, -1 never, n > 0 forced")
+    ap.add_argument("--late-weights", action="store_true",
+                    help="A/B aid: request the first weight blocks of a GEMM only after the wait for the kernel before")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
@@ -75,6 +77,9 @@ def main():
     if args.no_pdl:
         from . import _abi
         _abi.load().bt_debug_set(6, 0)
+    if args.late_weights:
+        from . import _abi
+        _abi.load().bt_debug_set(8, 0)
     if args.split_k != 0:
         from . import _abi
         _abi.load().bt_debug_set(7, args.split_k)
