@@ -51,6 +51,11 @@ __device__ __forceinline__ bool elect_one() {
 // and its writes are visible.  Without the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Hint: bring the 128-byte line at `p` into L1 (constants such as bias, gamma and beta, asked for
+// while the kernel still waits for its predecessor).
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
 
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

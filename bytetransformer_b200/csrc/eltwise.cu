@@ -81,10 +81,19 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
                       const void* __restrict__ beta, __half* __restrict__ out, const int* __restrict__ m_dev,
                       int m_rows, const int* __restrict__ batch_idx, int S, int hidden, float eps, LnSplit split) {
   pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = hidden / 8;
+  {
+    // gamma and beta are written by no kernel of the chain: ask for their lines while waiting
+    const int gb_bytes = hidden * (GB_FP32 ? 4 : 2);
+    const int off = static_cast<int>(threadIdx.x) * 128;
+    if (off < gb_bytes) {
+      prefetch_l1(reinterpret_cast<const uint8_t*>(gamma) + off);
+      prefetch_l1(reinterpret_cast<const uint8_t*>(beta) + off);
+    }
+  }
+  pdl_wait();
   // Rows are walked with a grid stride (the grid is capped at a few waves of the machine), so
   // a warp keeps streaming instead of paying a block launch per row.
   long long row_limit = m_rows;

@@ -340,11 +340,25 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       for (int c = 0; c < BLOCK_N / 64; ++c)
         tma_load_2d(sb + c * (64 * kBlockK * 2), &tm_b, &full_bar[kb], n0 + c * 64, (sp * num_kb + kb) * kBlockK);
     }
+  } else if (warp >= 2 && EPI != BT_EPI_NONE && args.early_w && args.bias != nullptr) {
+    // the bias slice of the first tile, for the same reason
+    int n0 = 0, sp = 0;
+    tile_cols(static_cast<int>(blockIdx.x), n0, sp);
+    const __half* bp = args.bias + n0 + ((warp - 2) >> 2) * (BLOCK_N / 2);
+    if (lane * 64 < BLOCK_N / 2) prefetch_l1(bp + lane * 64);
   }
 
   // Everything above touched only this CTA's own resources and the weights; from here on global
-  // memory written by earlier kernels is read (the row count first of all).
+  // memory written by earlier kernels is read.  The A blocks of the armed stages go first, before
+  // the row count is known: the first tile's rows lie inside the allocation whether or not they
+  // are valid, and a CTA that turns out to have no tile only has to wait for them.
   pdl_wait();
+  if (warp == 0 && lane == 0 && pre_kb > 0) {
+    int n0 = 0, sp = 0;
+    const int m0 = tile_cols(static_cast<int>(blockIdx.x), n0, sp) * kBlockM;
+    for (int kb = 0; kb < pre_kb; ++kb)
+      tma_load_2d(smem + kb * Cfg::kStageBytes, &tm_a, &full_bar[kb], (sp * num_kb + kb) * kBlockK, m0);
+  }
   int M = args.m_rows;
   if (args.m_dev != nullptr) {
     const int md = __ldg(args.m_dev);
@@ -369,9 +383,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       bool ok = true;
       int m0 = 0, n0 = 0, sp = 0;
       if (!tile_at(0, m0, n0, sp)) {
-        // No tile for this CTA after all (fewer valid rows than allocated): complete the armed
-        // stages with some A block and wait for them, so that no copy is in flight at exit.
-        for (int kb = 0; kb < pre_kb; ++kb) tma_load_2d(smem + kb * Cfg::kStageBytes, &tm_a, &full_bar[kb], 0, 0);
+        // No tile for this CTA after all (fewer valid rows than allocated): wait for the armed
+        // stages, so that no copy is in flight at exit.
         for (int kb = 0; kb < pre_kb; ++kb)
           if (!mbar_wait_bounded(&full_bar[kb], 0u, abort_flag, args.status, kStatusGemmProducerTimeout)) break;
       }
@@ -381,8 +394,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + kABytes;
           if (li == 0 && i < pre_kb) {
-            // armed before the wait, W already requested (stage == i here)
-            tma_load_2d(sa, &tm_a, &full_bar[stage], kb * kBlockK, m0);
+            // armed and requested above (stage == i here)
           } else {
             if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
                                    kStatusGemmProducerTimeout)) {
