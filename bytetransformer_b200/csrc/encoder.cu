@@ -32,6 +32,13 @@ __device__ int g_status_word = 0;
 static bool g_pdl_on = true;
 bool pdl_enabled() { return g_pdl_on; }
 void set_pdl_enabled(bool on) { g_pdl_on = on; }
+static thread_local bool t_next_launch_plain = false;
+void pdl_next_launch_plain() { t_next_launch_plain = true; }
+bool pdl_take_attr() {
+  const bool plain = t_next_launch_plain;
+  t_next_launch_plain = false;
+  return g_pdl_on && !plain;
+}
 
 int* device_status_word() {
   int* p = nullptr;
@@ -436,6 +443,7 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
   Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
 
   if ((rc = prepare_ln_sync(h, ws, static_cast<long long>(rows), stream)) != BT_OK) return rc;
+  pdl_next_launch_plain();  // first kernel of the call: see kernels.h
   cudaError_t e;
   {
     LaunchScope scope(h, BT_PROF_OFFSETS, stream);
@@ -481,6 +489,7 @@ static int stack_general(bt_handle h, int first_layer, int n_layers, const void*
   void* base = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 1024));
   Workspace ws = carve(base, rows, h->hidden, h->ffn, B + 1, rows);
   if ((rc = prepare_ln_sync(h, ws, static_cast<long long>(rows), stream)) != BT_OK) return rc;
+  pdl_next_launch_plain();  // first kernel of the call: see kernels.h
   cudaError_t e;
   {
     LaunchScope scope(h, BT_PROF_OFFSETS, stream);
@@ -758,6 +767,7 @@ int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, con
     const int rc = prepare_ln_sync(h, ws, total_tokens, stream);
     if (rc != BT_OK) return rc;
   }
+  pdl_next_launch_plain();  // first kernel of the call: see kernels.h
   const __half* cur = reinterpret_cast<const __half*>(x_packed);
   for (int l = 0; l < n_layers; ++l) {
     const bool last = (l == n_layers - 1);
@@ -806,6 +816,7 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
   if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL_F32OUT) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
   if (epilogue != BT_EPI_NONE && !bias) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs bias");
   if ((epilogue == BT_EPI_BIAS_RESIDUAL || epilogue == BT_EPI_BIAS_RESIDUAL_F32OUT) && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
+  pdl_next_launch_plain();  // W may come straight from the caller's kernel before: see kernels.h
   return run_gemm(h, BT_PROF_GEMM_OTHER, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
                   reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, epilogue, gelu_kind,
                   reinterpret_cast<cudaStream_t>(stream));

@@ -16,6 +16,13 @@ namespace bt {
 // common.cuh); `pdl_enabled()` can be switched off for A/B measurements.
 bool pdl_enabled();
 void set_pdl_enabled(bool on);
+// The calling thread's next launch is serialised the ordinary way (it starts when everything before it
+// on the stream has completed and is visible).  The entry points whose GEMMs read their weights ahead
+// of `griddepcontrol.wait` ask for this for their first kernel: a later kernel of the call can only start
+// once that one has, so nothing a caller's own kernel wrote before the call (the weights, say) can still
+// be in flight when a weight block is requested early.
+void pdl_next_launch_plain();
+bool pdl_take_attr();  // whether the launch being made gets the attribute (consumes a pending request)
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                        Args&&... args) {
@@ -28,7 +35,7 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = pdl_take_attr() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
 }
 
