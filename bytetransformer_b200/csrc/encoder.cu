@@ -204,9 +204,11 @@ static int fail_cuda(bt_handle h, cudaError_t e, const char* where) {
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Split-K of the fp32-sum GEMMs is considered up to this many allocated rows, in at most this many ranges.
+// Split-K of the fp32-sum GEMMs is considered up to kSplitKMaxRows allocated rows; the partial sums of
+// all ranges together take at most kSplitKRowBudget rows of `pre` (8 ranges up to 256 rows, 4 up to
+// 512, 2 up to 1024).
 constexpr size_t kSplitKMaxRows = 1024;
-constexpr int kMaxSplitK = 8;
+constexpr size_t kSplitKRowBudget = 2048;
 
 struct Workspace {
   int* batch_idx;
@@ -234,8 +236,9 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   w.xb = reinterpret_cast<__half*>(take(rh));
   w.qkv = reinterpret_cast<__half*>(take(3 * rh));
   w.ctx = reinterpret_cast<__half*>(take(rh));
-  // fp32 sums; with few rows the GEMMs that produce them cut K into up to kMaxSplitK ranges, one sum each
-  w.pre = reinterpret_cast<float*>(take(2 * rh * (rows <= kSplitKMaxRows ? kMaxSplitK : 1)));
+  // fp32 sums; with few rows the GEMMs that produce them cut K into ranges, one sum each
+  const size_t pre_rows = rows <= kSplitKMaxRows ? kSplitKRowBudget : rows;
+  w.pre = reinterpret_cast<float*>(take(pre_rows * static_cast<size_t>(hidden) * 4));
   w.y = reinterpret_cast<__half*>(take(rh));
   w.mid = reinterpret_cast<__half*>(take(rows * static_cast<size_t>(ffn) * 2));
   w.ln_stats_bytes = rows * static_cast<size_t>(hidden / 128 > 0 ? hidden / 128 : 1) * 16;
@@ -373,8 +376,9 @@ static int run_layer(bt_handle h, int layer, const __half* x_in, __half* x_out, 
   // floats apart in `pre`) and the LayerNorm kernel adds them up.
   auto split_for = [&](int K) {
     if (static_cast<size_t>(rows) > kSplitKMaxRows) return 1;
-    const int s = gemm_pick_split_k(rows, H, K, h->num_sms);
-    return s <= kMaxSplitK ? s : 1;
+    int s = gemm_pick_split_k(rows, H, K, h->num_sms);
+    while (s > 1 && static_cast<size_t>(s) * static_cast<size_t>(rows) > kSplitKRowBudget) s >>= 1;
+    return (s >= 1 && (K / 64) % s == 0) ? s : 1;
   };
   const int split_attn = split_for(H), split_ffn2 = split_for(F);
   const long long split_stride = static_cast<long long>(rows) * H;
