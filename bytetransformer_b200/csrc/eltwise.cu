@@ -28,6 +28,7 @@ namespace {
 
 constexpr int kLnWarps = 4;
 constexpr int kLnMaxVec = 4;  // register-resident rows up to 4*32*8 = 1024 halves
+constexpr int kLnMaxSplit = 8;  // most fp32 partial sums a row may arrive in
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -74,7 +75,7 @@ __device__ __forceinline__ void load_gb8(const void* p, int vec, float (&f)[8]) 
 // RESTORE = false: rows [0, M) of x -> rows [0, M) of out.
 // RESTORE = true : grid covers the B*S padded rows; row (b,i) reads packed row
 //                  batch_idx[b]+i when i < len_b, else writes zeros.
-template <bool RESTORE, bool GB_FP32, bool X_FP32, int NVEC>
+template <bool RESTORE, bool GB_FP32, bool X_FP32, int NVEC, bool SPLIT>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ bias,
                       const __half* __restrict__ residual, const void* __restrict__ gamma,
@@ -132,12 +133,21 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
         const float4 a = __ldg(xf + 2 * v), b = __ldg(xf + 2 * v + 1);
         val[it][0] = a.x; val[it][1] = a.y; val[it][2] = a.z; val[it][3] = a.w;
         val[it][4] = b.x; val[it][5] = b.y; val[it][6] = b.z; val[it][7] = b.w;
-        // the sum arrives in `split.n` fp32 parts (K ranges of the GEMM before)
-        for (int sp = 1; sp < split.n; ++sp) {
-          const float4* xs = xf + sp * (split.stride / 4);
-          const float4 c = __ldg(xs + 2 * v), d = __ldg(xs + 2 * v + 1);
-          val[it][0] += c.x; val[it][1] += c.y; val[it][2] += c.z; val[it][3] += c.w;
-          val[it][4] += d.x; val[it][5] += d.y; val[it][6] += d.z; val[it][7] += d.w;
+        // the sum arrives in `split.n` <= kLnMaxSplit fp32 parts (K ranges of the GEMM before); the loads of
+        // all parts are independent and issued together
+        if (SPLIT) {
+          float4 c[kLnMaxSplit - 1], d[kLnMaxSplit - 1];
+#pragma unroll
+          for (int sp = 1; sp < kLnMaxSplit; ++sp) {
+            const float4* xs = xf + sp * (split.stride / 4);
+            c[sp - 1] = sp < split.n ? __ldg(xs + 2 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            d[sp - 1] = sp < split.n ? __ldg(xs + 2 * v + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int sp = 0; sp < kLnMaxSplit - 1; ++sp) {
+            val[it][0] += c[sp].x; val[it][1] += c[sp].y; val[it][2] += c[sp].z; val[it][3] += c[sp].w;
+            val[it][4] += d[sp].x; val[it][5] += d[sp].y; val[it][6] += d[sp].z; val[it][7] += d[sp].w;
+          }
         }
       } else {
         unpack8(__ldg(x4 + v), val[it]);
@@ -191,14 +201,14 @@ layernorm_rows_kernel(const void* __restrict__ x_v, const __half* __restrict__ b
   }  // row loop
 }
 
-template <bool RESTORE, bool GB_FP32, bool X_FP32>
+template <bool RESTORE, bool GB_FP32, bool X_FP32, bool SPLIT>
 cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, const void* x, const __half* bias,
                            const __half* residual, const void* gamma, const void* beta, __half* out,
                            const int* m_dev, int m_rows, const int* batch_idx, int S, int hidden, float eps,
                            LnSplit split) {
 #define BT_LN_CASE(NV)                                                                                        \
   case NV:                                                                                                    \
-    return launch_pdl(layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV>, grid, dim3(kLnWarps * 32), 0, stream,  \
+    return launch_pdl(layernorm_rows_kernel<RESTORE, GB_FP32, X_FP32, NV, SPLIT>, grid, dim3(kLnWarps * 32), 0, stream,  \
                       x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps, split);
   switch (nvec_needed) {
     BT_LN_CASE(1)
@@ -338,25 +348,25 @@ static cudaError_t launch_ln_dispatch(bool gb_fp32, bool x_fp32, int nv, dim3 gr
                                       const __half* bias, const __half* residual, const void* gamma, const void* beta,
                                       __half* out, const int* m_dev, int m_rows, const int* batch_idx, int S,
                                       int hidden, float eps, LnSplit split) {
-  if (gb_fp32) {
-    if (x_fp32)
-      return launch_ln_nvec<RESTORE, true, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                 batch_idx, S, hidden, eps, split);
-    return launch_ln_nvec<RESTORE, true, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                batch_idx, S, hidden, eps, split);
+#define BT_LN_ARGS nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows, batch_idx, S, hidden, eps, split
+  if (split.n > 1) {  // fp32 partial sums (checked by the callers)
+    if (gb_fp32) return launch_ln_nvec<RESTORE, true, true, true>(BT_LN_ARGS);
+    return launch_ln_nvec<RESTORE, false, true, true>(BT_LN_ARGS);
   }
-  if (x_fp32)
-    return launch_ln_nvec<RESTORE, false, true>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                                batch_idx, S, hidden, eps, split);
-  return launch_ln_nvec<RESTORE, false, false>(nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev, m_rows,
-                                               batch_idx, S, hidden, eps, split);
+  if (gb_fp32) {
+    if (x_fp32) return launch_ln_nvec<RESTORE, true, true, false>(BT_LN_ARGS);
+    return launch_ln_nvec<RESTORE, true, false, false>(BT_LN_ARGS);
+  }
+  if (x_fp32) return launch_ln_nvec<RESTORE, false, true, false>(BT_LN_ARGS);
+  return launch_ln_nvec<RESTORE, false, false, false>(BT_LN_ARGS);
+#undef BT_LN_ARGS
 }
 
 cudaError_t launch_layernorm(const void* x, bool x_fp32, const __half* bias, const __half* residual,
                              const void* gamma, const void* beta, bool gb_fp32, __half* out, const int* m_dev,
                              int m_rows, int hidden, float eps, cudaStream_t stream, LnSplit split) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || m_rows <= 0) return cudaErrorInvalidValue;
-  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0)) return cudaErrorInvalidValue;
+  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0 || split.n > kLnMaxSplit)) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   dim3 grid(ln_grid((m_rows + kLnWarps - 1) / kLnWarps));
   return launch_ln_dispatch<false>(gb_fp32, x_fp32, nv, grid, stream, x, bias, residual, gamma, beta, out, m_dev,
@@ -368,7 +378,7 @@ cudaError_t launch_layernorm_restore(const void* x, bool x_fp32, const __half* b
                                      const int* batch_idx, int B, int S, int hidden, float eps,
                                      cudaStream_t stream, LnSplit split) {
   if (hidden % 8 != 0 || hidden > kLnMaxVec * 256 || B <= 0 || S <= 0) return cudaErrorInvalidValue;
-  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0)) return cudaErrorInvalidValue;
+  if (split.n > 1 && (!x_fp32 || split.stride % 4 != 0 || split.n > kLnMaxSplit)) return cudaErrorInvalidValue;
   const int nv = (hidden / 8 + 31) / 32;
   const long long rows = static_cast<long long>(B) * S;
   dim3 grid(ln_grid((rows + kLnWarps - 1) / kLnWarps));
