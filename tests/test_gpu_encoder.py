@@ -226,3 +226,63 @@ def test_error_behaviour(cuda_device):
     with pytest.raises(RuntimeError):
         Encoder(2, 32, [w])                             # head size must be 64
     enc.close()
+
+
+def test_whole_box_workload_full_size_properties(cuda_device):
+    """The benchmark workload at full size (1024 sequences of U[16,1024] tokens, BERT-base, 12 layers,
+    cut into micro-batches of at most 148 x 128 packed tokens exactly as the benchmark does), through
+    the packed entry point.  The CPU oracle cannot run 556k tokens in test time, so at this size:
+      (a) every micro-batch is run a second time with its sequences in reverse order: a sequence's rows
+          must come out bit-identical wherever the sequence sits in the batch;
+      (b) all outputs are finite and every row is normalised (the last op is a LayerNorm with gamma 1,
+          beta 0: row mean ~ 0, row variance ~ 1);
+      (c) the longest, a middle and the shortest sequence are checked against the oracle run on that
+          sequence alone (tolerance of the fp16 path: max-abs 2e-2, mean-abs 1e-3)."""
+    from bytetransformer_b200.encoder import Encoder
+    from bytetransformer_b200.runner import DEFAULT_TOKEN_BUDGET
+    from bytetransformer_b200.sharding import micro_batches
+    from bytetransformer_b200.workloads import BERT_BASE, lengths_for, make_weights
+    dev = cuda_device
+    H, nh = BERT_BASE.hidden, BERT_BASE.head_num
+    lens = lengths_for("whole_box_1024x1024")
+    assert len(lens) == 1024 and lens.min() >= 16 and lens.max() <= 1024
+    weights = make_weights(BERT_BASE, seed=7, device="cpu")
+    enc = Encoder(nh, 64, [[t.to(dev) for t in layer] for layer in weights])
+    mbs = micro_batches(lens, np.arange(len(lens)), DEFAULT_TOKEN_BUDGET)
+    assert sum(mb.tokens for mb in mbs) == int(lens.sum())
+    order = np.argsort(lens, kind="stable")
+    sampled = {int(order[-1]), int(order[len(order) // 2]), int(order[0])}
+    kept = {}
+    for k, mb in enumerate(mbs):
+        g = torch.Generator(device=dev).manual_seed(1000 + k)
+        x = torch.randn(mb.tokens, H, generator=g, device=dev, dtype=torch.float32).half()
+        cu = torch.from_numpy(mb.cu_seqlens).to(dev)
+        out = enc.forward_packed(x, cu, mb.max_len)
+        # (a) reversed order of the sequences
+        n = len(mb.seq_ids)
+        ls = np.diff(mb.cu_seqlens)
+        rev = np.arange(n)[::-1]
+        cu_rev = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum(ls[rev], out=cu_rev[1:])
+        x_rev = torch.cat([x[mb.cu_seqlens[i]:mb.cu_seqlens[i + 1]] for i in rev])
+        out_rev = enc.forward_packed(x_rev, torch.from_numpy(cu_rev).to(dev), mb.max_len)
+        back = torch.cat([out_rev[cu_rev[n - 1 - i]:cu_rev[n - i]] for i in range(n)])
+        assert torch.equal(out, back), f"micro-batch {k}: rows depend on the position of their sequence"
+        # (b)
+        of = out.float()
+        assert torch.isfinite(of).all()
+        assert of.mean(dim=1).abs().max().item() < 5e-3
+        assert (of.var(dim=1, unbiased=False) - 1.0).abs().max().item() < 2e-2
+        for i, sid in enumerate(mb.seq_ids):
+            if int(sid) in sampled:
+                a, b = mb.cu_seqlens[i], mb.cu_seqlens[i + 1]
+                kept[int(sid)] = (x[a:b].cpu(), out[a:b].cpu())
+    assert enc.device_status() == 0
+    enc.close()
+    # (c)
+    assert set(kept) == sampled
+    layers32 = [[t.float() for t in layer] for layer in weights]
+    for sid, (xs, got) in kept.items():
+        L = xs.shape[0]
+        want = _oracle(xs.float()[None], torch.ones(1, L, L), layers32, nh, 64)[-1][0]
+        assert_close_fp16(got, want, f"sequence {sid} of {L} tokens")
