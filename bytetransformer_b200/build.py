@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 
-CU_SOURCES = ["offsets.cu", "eltwise.cu", "embed_pool.cu", "gemm_sm100.cu", "mha_sm100.cu", "encoder.cu"]
+CU_SOURCES = ["offsets.cu", "eltwise.cu", "embed_pool.cu", "tmem_probe.cu", "gemm_sm100.cu", "mha_sm100.cu", "encoder.cu"]
 CORE_LIB = os.path.join(LIB_DIR, "libbt_b200.so")
 THS_LIB = os.path.join(LIB_DIR, "libths_bytetransformer.so")
 

@@ -34,9 +34,11 @@
 // for P instead (S 0..127, O 128..191, P 192..255): S stays intact, so the next S = Q K^T is
 // issued before O += P V, and every key tile is read from tensor memory only once (the
 // probabilities are formed with the reference of the earlier tiles and the tile is redone only
-// when the row maximum jumped past the threshold).  Reading the fp32 scores out of tensor
-// memory is the kernel's largest load: 64 KB per 128x128 tile against a measured ~48 B/clk per
-// SM for tcgen05.ld (the same rate bounds the GEMM epilogues: 128 KB in ~2.7k clocks).
+// when the row maximum jumped past the threshold).  The softmax is a chain of dependent
+// latencies (tcgen05.ld, wait, arithmetic, tcgen05.st, barrier) run by two warps per scheduler
+// (S, O and P take 256 of the 512 tensor-memory columns, so two CTAs fit on an SM), not a
+// bandwidth problem: a read-only loop (tmem_probe.cu) gets 120-370 B/clk per SM out of tensor memory,
+// the softmax consumes ~48.  Touching every score once instead of twice shortened that chain.
 // P never touches shared memory.  O stays in tensor memory across key tiles.  The
 // exponent reference m only moves when the running maximum grows by more than a
 // threshold (then the O row is rescaled in tensor memory); otherwise P simply grows
@@ -661,8 +663,8 @@ __device__ __forceinline__ bool decode_item(const int* __restrict__ batch_idx, i
 // ONEPASS (needs PSEP): key tiles after the first are read from tensor memory ONCE: probabilities are
 // formed with the reference of the earlier tiles while the largest exponent is tracked; only when that
 // exceeds the threshold (the row maximum jumped by more than 2^8) is the tile redone with a new
-// reference, which is possible because S is still intact.  The two reads of every score were the
-// largest single load on the tensor-memory read path.
+// reference, which is possible because S is still intact.  The second read of every score (load, wait,
+// arithmetic) was the longest avoidable piece of the softmax's latency chain.
 template <bool EXP16, bool PSEP = false, bool ONEPASS = false>
 __global__ void __launch_bounds__(192, 2)
 mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {

@@ -411,3 +411,12 @@ def test_expired_wait_is_reported_and_the_context_stays_usable(enc, cuda_device)
     assert enc.device_status() == 0                     # read-and-clear
     _gemm_case(enc, cuda_device, 300, 768, 768, _abi.BT_EPI_BIAS)
     assert enc.device_status() == 0
+
+
+def test_tensor_memory_read_rate_is_far_above_what_the_kernels_consume(cuda_device):
+    """The GEMM epilogues and the attention softmax consume their tiles at roughly 48 B/clk per SM; a loop
+    that only reads tensor memory gets several times that, so they are not bounded by tensor-memory
+    bandwidth (the figure this test guards is quoted where the kernels are described)."""
+    from bytetransformer_b200.tmem_probe import read_rate
+    assert read_rate(0, 4, device=cuda_device) > 100.0
+    assert read_rate(2, 8, device=cuda_device) > 200.0
