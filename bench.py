@@ -310,7 +310,7 @@ def main():
     if not args.no_kernel_events and gemm_ms > 0:
         achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
         traffic = GEMM_DRAM_BYTES_PER_LAUNCH if not (args.max_seqs or args.layers) else None
-        roofline = {"bound": "tensor", "kernel": "the four GEMMs of a layer: gemm_f16_pair_kernel (QKV), gemm_f16_ln_kernel (attention output and FFN2, with LayerNorm), gemm_f16_kernel (FFN1 + GELU)", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": "the four GEMMs of a layer: gemm_f16_pair_kernel (QKV, FFN1 + GELU), gemm_f16_ln_kernel (attention output and FFN2, with LayerNorm)", "achieved": achieved,
                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                     "peak_source": peaks["source"] + " sustained bf16 dense", "traffic": traffic,
                     "launches": int(gemm_launches), "avg_launch_ms": gemm_ms / max(1, gemm_launches)}
