@@ -109,6 +109,7 @@ __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
 }
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 long long g_dbg_early_w = 1;  // 1 = W blocks of the first tile requested before the dependency wait
+long long g_dbg_ln_pair = 0;  // GEMM + LayerNorm on SM pairs: 1 = always, anything else = never (default)
 long long g_dbg_split_k = 0;  // 0 = policy, < 0 = never, > 0 = that many ranges whenever the shape allows
 
 // ------------------------------------------------------------------------------------------
@@ -760,6 +761,286 @@ __device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned 
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+// The epilogue warps' loop of the GEMM + LayerNorm kernels (one-CTA and pair form share it): steps 1-4
+// of the description above for every tile that `tile_at(it, m0, n0)` yields (m0 = first of this CTA's 128
+// rows, n0 = first of the tile's 256 columns); `release_acc(as)` hands accumulator buffer `as` back to the
+// MMA issuer.  `stg_base`: 8 staging buffers of 4 KB; `res_bar`: 8 barriers, one per epilogue warp.
+template <class TileAt, class ReleaseAcc>
+__device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUtensorMap* tm_out,
+                                                 const CUtensorMap* tm_res, uint8_t* stg_base, uint64_t* acc_full,
+                                                 uint64_t* vec_full, uint64_t* vec_empty, uint64_t* res_bar,
+                                                 uint4* vec_s, volatile int* abort_flag, uint32_t tmem_base, int M,
+                                                 int n_tiles, int warp, int lane, TileAt tile_at,
+                                                 ReleaseAcc release_acc) {
+  constexpr int kTileN = 256;
+  constexpr int kColsPerThread = kTileN / 2;  // 128
+  const int e = warp - 2;
+  const int quarter = warp & 3;
+  const int col_half = e >> 2;
+  uint8_t* stg = stg_base + e * kStagingBytesPerWarp;
+  const int parts = 2 * n_tiles;                        // partials per row
+  const float inv_n = 1.0f / static_cast<float>(args.N);
+  int m0 = 0, n0 = 0;
+  for (int it = 0; tile_at(it, m0, n0); ++it) {
+    const int as = it & 1;
+    const uint32_t aphase = (it >> 1) & 1;
+    const int row0 = m0 + quarter * 32;
+    const int row = row0 + lane;
+    const bool row_ok = row < M;
+    const int gcol0 = n0 + col_half * kColsPerThread;  // first of this thread's 128 columns
+    const int part = 2 * (n0 / kTileN) + col_half;
+    // The first epilogue warp brings the tile's bias / gamma / beta slices into shared memory (every
+    // thread re-reads them, and the residual loads below keep evicting them from L1).
+    if (e == 0) {
+      uint4 vb = __ldg(reinterpret_cast<const uint4*>(args.bias + n0) + lane);
+      uint4 vg = make_uint4(0u, 0u, 0u, 0u), vt = vg;
+      if (!args.gb_fp32) {
+        vg = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.gamma) + n0) + lane);
+        vt = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.beta) + n0) + lane);
+      }
+      if (!mbar_wait_bounded(vec_empty, (it & 1u) ^ 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+      vec_s[lane] = vb;
+      vec_s[32 + lane] = vg;
+      vec_s[64 + lane] = vt;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(vec_full);
+    }
+    // Residual rows of this warp (32 rows x 128 columns) come through its staging buffer in two
+    // TMA boxes of 64 columns: row-strided 16-byte loads from the threads would cost one L1 tag
+    // look-up per lane and load (4096 per tile), which alone took longer than the main loop.
+    // The first box is requested now, the second when the first has been read.
+    if (lane == 0) {
+      tma_store_wait_read_n<0>();  // the bulk stores of the previous tile have read the buffer
+      mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
+      tma_load_2d(stg, tm_res, &res_bar[e], gcol0, row0);
+    }
+    if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+    tc_fence_after();
+    if (!mbar_wait_bounded(vec_full, it & 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
+    if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
+    const uint4* sbias = vec_s + col_half * (kColsPerThread / 8);
+    const uint4* sgamma = vec_s + 32 + col_half * (kColsPerThread / 8);
+    const uint4* sbeta = vec_s + 64 + col_half * (kColsPerThread / 8);
+    const uint32_t t_row = tmem_base + as * kTileN + (static_cast<uint32_t>(quarter * 32) << 16) +
+                           col_half * kColsPerThread;
+    // ---- 1. v = acc + bias + residual -> tensor memory; shifted sums
+    float sd = 0.f, sdd = 0.f, shift0 = 0.f;
+    {
+      uint32_t raw[2][32];
+      tmem_ld_32x32(t_row, raw[0]);
+      bool res_ok = true;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        // this thread's 64 residual values of box hh: row `lane` of the swizzled buffer
+        if (!mbar_wait_bounded(&res_bar[e], (static_cast<uint32_t>(it) * 2u + hh) & 1u, abort_flag, args.status,
+                               kStatusGemmEpilogueTimeout)) {
+          res_ok = false;
+          break;
+        }
+        uint4 rres[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          rres[q] = *reinterpret_cast<const uint4*>(stg + lane * 128 + ((q ^ (lane & 7)) << 4));
+        if (hh == 0) {
+          fence_proxy_async_smem();  // the reads above precede the next bulk write into the buffer
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
+            tma_load_2d(stg, tm_res, &res_bar[e], gcol0 + 64, row0);
+          }
+        }
+#pragma unroll
+        for (int cj = 0; cj < 2; ++cj) {
+          const int ci = hh * 2 + cj;
+          const int c = ci * 32;
+          tmem_ld_wait();
+          if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 b4 = sbias[c / 8 + q];
+            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+            const __half2* rh = reinterpret_cast<const __half2*>(&rres[cj * 4 + q]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 fb = __half22float2(bh[j]);
+              const float2 fr = __half22float2(rh[j]);
+              const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
+              const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
+              if (ci == 0 && q == 0 && j == 0) shift0 = v0;
+              const float d0 = v0 - shift0, d1 = v1 - shift0;
+              sd += d0 + d1;
+              sdd = fmaf(d0, d0, sdd);
+              sdd = fmaf(d1, d1, sdd);
+              raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
+              raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
+            }
+          }
+          tmem_st_32x32(t_row + c, raw[ci & 1]);
+        }
+      }
+      if (!res_ok) break;
+    }
+    const float lmean = shift0 + sd * (1.0f / kColsPerThread);
+    const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
+    if (warp == 2 && lane == 0) gstamp(args.timing, it, 4);
+    // ---- 2. publish the partial: two 64-bit words, each (value bits << 32 | epoch).  A naturally
+    // aligned 64-bit store is single-copy atomic, so a reader that finds this launch's epoch in a word
+    // also has its value: no fence, no counter, no second round trip.
+    const uint32_t epoch = args.ln_epoch;
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(args.out);
+    if (row_ok) {
+      unsigned long long* wp = words + (static_cast<size_t>(row) * parts + part) * 2;
+      st_relaxed_gpu_u64(wp, (static_cast<unsigned long long>(__float_as_uint(lmean)) << 32) | epoch);
+      st_relaxed_gpu_u64(wp + 1, (static_cast<unsigned long long>(__float_as_uint(m2)) << 32) | epoch);
+    }
+    if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
+    // ---- 3. wait until the row's 2 * parts words all carry this epoch (bounded), then merge.
+    // The partials of the 32 rows of this slab come from the same 2*C warps, so one lane probes its
+    // own row (with a pause between probes: 2 * parts loads, not 64 * parts, per probe) and only
+    // then does every lane read and validate its row; a lane whose words are not all there yet
+    // sends the warp round again.
+    float mean = 0.f, rstd = 0.f;
+    float pm[8], pq[8];  // N <= 1024: at most 8 partials per row
+    const unsigned long long* rp64 = words + static_cast<size_t>(row_ok ? row : 0) * parts * 2;
+    const long long t0 = clock64();
+    bool give_up = false;
+    while (true) {
+      if (lane == 0 && row_ok) {
+        uint32_t probes = 0;
+        while (true) {
+          // all loads are issued before any tag is looked at (no short-circuit: one round trip, not 2*parts)
+          uint32_t bad = 0;
+#pragma unroll
+          for (int p = 0; p < 8; ++p)
+            if (p < parts) {
+              const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
+              const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
+              bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
+            }
+          if (bad == 0) break;
+          if ((++probes & 15u) == 0u && (*abort_flag != 0 || clock64() - t0 > (1ll << 31))) break;
+        }
+      }
+      __syncwarp();
+      uint32_t bad = 0;
+      if (row_ok) {
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < parts) {
+            const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
+            const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
+            bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
+            pm[p] = __uint_as_float(static_cast<uint32_t>(w0 >> 32));
+            pq[p] = __uint_as_float(static_cast<uint32_t>(w1 >> 32));
+          }
+      }
+      if (__all_sync(0xffffffffu, bad == 0)) break;
+      if (*abort_flag != 0 || clock64() - t0 > (1ll << 31)) {
+        give_up = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (__any_sync(0xffffffffu, give_up)) {
+      if (lane == 0) {
+        *abort_flag = 1;
+        if (args.status != nullptr) atomicCAS(args.status, 0, kStatusGemmEpilogueTimeout);
+      }
+      break;
+    }
+    if (row_ok) {
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+        if (p < parts) mean += pm[p];
+      mean *= 1.0f / static_cast<float>(parts);
+      float M2 = 0.f;
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+        if (p < parts) {
+          const float d = pm[p] - mean;
+          M2 += pq[p] + static_cast<float>(kColsPerThread) * d * d;
+        }
+      rstd = rsqrtf(M2 * inv_n + args.eps);
+    }
+    if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
+    const float shift = -mean * rstd;
+    tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
+    // ---- 4. normalise, gamma / beta, fp16, store (64 columns = 128 B per row at a time)
+    const bool slab_full = row0 + 32 <= M;
+    {
+      uint32_t raw[2][32];
+      tmem_ld_32x32(t_row, raw[0]);
+#pragma unroll
+      for (int ci = 0; ci < kColsPerThread / 32; ++ci) {
+        const int c = ci * 32;
+        const int hh = ci & 1;  // which half of the current 64-column store chunk
+        uint8_t* srow = stg + lane * 128;
+        if (hh == 0 && slab_full) {
+          if (lane == 0) tma_store_wait_read_n<0>();  // the previous bulk store has read the staging rows
+          __syncwarp();
+        }
+        tmem_ld_wait();
+        if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int col8 = gcol0 + c + q * 8;  // first of these 8 columns
+          float g[8], b[8];
+          if (args.gb_fp32) {
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2) + 1);
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2) + 1);
+            g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+            b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+          } else {
+            const uint4 g4 = sgamma[c / 8 + q];
+            const uint4 b4 = sbeta[c / 8 + q];
+            const __half2* gh = reinterpret_cast<const __half2*>(&g4);
+            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 fg = __half22float2(gh[j]);
+              const float2 fb = __half22float2(bh[j]);
+              g[2 * j] = fg.x; g[2 * j + 1] = fg.y;
+              b[2 * j] = fb.x; b[2 * j + 1] = fb.y;
+            }
+          }
+          float y[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            y[i] = fmaf(fmaf(__uint_as_float(raw[ci & 1][q * 8 + i]), rstd, shift), g[i], b[i]);
+          uint4 u;
+          u.x = pack_half2(y[0], y[1]);
+          u.y = pack_half2(y[2], y[3]);
+          u.z = pack_half2(y[4], y[5]);
+          u.w = pack_half2(y[6], y[7]);
+          const int unit = hh * 4 + q;  // 16-byte unit inside the 128-byte row
+          if (slab_full)
+            *reinterpret_cast<uint4*>(srow + ((unit ^ (lane & 7)) << 4)) = u;
+          else if (row_ok)
+            *reinterpret_cast<uint4*>(args.out_ln + static_cast<size_t>(row) * args.N + col8) = u;
+        }
+        if (hh == 1 && slab_full) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(tm_out, stg, gcol0 + c - 32, row0);
+            tma_store_commit();
+          }
+        }
+      }
+    }
+    if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      release_acc(as);
+      mbar_arrive(vec_empty);
+    }
+  }
+  if (lane == 0) tma_store_wait_all();
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
@@ -767,7 +1048,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   constexpr int kTileN = 256;
   using Cfg = GemmCfg<kTileN>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kColsPerThread = kTileN / 2;  // 128
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -908,271 +1188,9 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int e = warp - 2;
-    const int quarter = warp & 3;
-    const int col_half = e >> 2;
-    uint8_t* stg = smem + kStages * Cfg::kStageBytes + e * kStagingBytesPerWarp;
-    const int parts = 2 * n_tiles;                        // partials per row
-    const float inv_n = 1.0f / static_cast<float>(args.N);
-    int m0 = 0, n0 = 0;
-    for (int it = 0; tile_at(it, m0, n0); ++it) {
-      const int as = it & 1;
-      const uint32_t aphase = (it >> 1) & 1;
-      const int row0 = m0 + quarter * 32;
-      const int row = row0 + lane;
-      const bool row_ok = row < M;
-      const int gcol0 = n0 + col_half * kColsPerThread;  // first of this thread's 128 columns
-      const int part = 2 * (n0 / kTileN) + col_half;
-      // The first epilogue warp brings the tile's bias / gamma / beta slices into shared memory (every
-      // thread re-reads them, and the residual loads below keep evicting them from L1).
-      if (e == 0) {
-        uint4 vb = __ldg(reinterpret_cast<const uint4*>(args.bias + n0) + lane);
-        uint4 vg = make_uint4(0u, 0u, 0u, 0u), vt = vg;
-        if (!args.gb_fp32) {
-          vg = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.gamma) + n0) + lane);
-          vt = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(args.beta) + n0) + lane);
-        }
-        if (!mbar_wait_bounded(vec_empty, (it & 1u) ^ 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
-        vec_s[lane] = vb;
-        vec_s[32 + lane] = vg;
-        vec_s[64 + lane] = vt;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(vec_full);
-      }
-      // Residual rows of this warp (32 rows x 128 columns) come through its staging buffer in two
-      // TMA boxes of 64 columns: row-strided 16-byte loads from the threads would cost one L1 tag
-      // look-up per lane and load (4096 per tile), which alone took longer than the main loop.
-      // The first box is requested now, the second when the first has been read.
-      if (lane == 0) {
-        tma_store_wait_read_n<0>();  // the bulk stores of the previous tile have read the buffer
-        mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
-        tma_load_2d(stg, &tm_res, &res_bar[e], gcol0, row0);
-      }
-      if (!mbar_wait_bounded(&acc_full[as], aphase, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
-      tc_fence_after();
-      if (!mbar_wait_bounded(vec_full, it & 1u, abort_flag, args.status, kStatusGemmEpilogueTimeout)) break;
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 2);
-      const uint4* sbias = vec_s + col_half * (kColsPerThread / 8);
-      const uint4* sgamma = vec_s + 32 + col_half * (kColsPerThread / 8);
-      const uint4* sbeta = vec_s + 64 + col_half * (kColsPerThread / 8);
-      const uint32_t t_row = tmem_base + as * kTileN + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             col_half * kColsPerThread;
-      // ---- 1. v = acc + bias + residual -> tensor memory; shifted sums
-      float sd = 0.f, sdd = 0.f, shift0 = 0.f;
-      {
-        uint32_t raw[2][32];
-        tmem_ld_32x32(t_row, raw[0]);
-        bool res_ok = true;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          // this thread's 64 residual values of box hh: row `lane` of the swizzled buffer
-          if (!mbar_wait_bounded(&res_bar[e], (static_cast<uint32_t>(it) * 2u + hh) & 1u, abort_flag, args.status,
-                                 kStatusGemmEpilogueTimeout)) {
-            res_ok = false;
-            break;
-          }
-          uint4 rres[8];
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            rres[q] = *reinterpret_cast<const uint4*>(stg + lane * 128 + ((q ^ (lane & 7)) << 4));
-          if (hh == 0) {
-            fence_proxy_async_smem();  // the reads above precede the next bulk write into the buffer
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive_expect_tx(&res_bar[e], kStagingBytesPerWarp);
-              tma_load_2d(stg, &tm_res, &res_bar[e], gcol0 + 64, row0);
-            }
-          }
-#pragma unroll
-          for (int cj = 0; cj < 2; ++cj) {
-            const int ci = hh * 2 + cj;
-            const int c = ci * 32;
-            tmem_ld_wait();
-            if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 b4 = sbias[c / 8 + q];
-              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-              const __half2* rh = reinterpret_cast<const __half2*>(&rres[cj * 4 + q]);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 fb = __half22float2(bh[j]);
-                const float2 fr = __half22float2(rh[j]);
-                const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
-                const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
-                if (ci == 0 && q == 0 && j == 0) shift0 = v0;
-                const float d0 = v0 - shift0, d1 = v1 - shift0;
-                sd += d0 + d1;
-                sdd = fmaf(d0, d0, sdd);
-                sdd = fmaf(d1, d1, sdd);
-                raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
-                raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
-              }
-            }
-            tmem_st_32x32(t_row + c, raw[ci & 1]);
-          }
-        }
-        if (!res_ok) break;
-      }
-      const float lmean = shift0 + sd * (1.0f / kColsPerThread);
-      const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 4);
-      // ---- 2. publish the partial: two 64-bit words, each (value bits << 32 | epoch).  A naturally
-      // aligned 64-bit store is single-copy atomic, so a reader that finds this launch's epoch in a word
-      // also has its value: no fence, no counter, no second round trip.
-      const uint32_t epoch = args.ln_epoch;
-      unsigned long long* words = reinterpret_cast<unsigned long long*>(args.out);
-      if (row_ok) {
-        unsigned long long* wp = words + (static_cast<size_t>(row) * parts + part) * 2;
-        st_relaxed_gpu_u64(wp, (static_cast<unsigned long long>(__float_as_uint(lmean)) << 32) | epoch);
-        st_relaxed_gpu_u64(wp + 1, (static_cast<unsigned long long>(__float_as_uint(m2)) << 32) | epoch);
-      }
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
-      // ---- 3. wait until the row's 2 * parts words all carry this epoch (bounded), then merge.
-      // The partials of the 32 rows of this slab come from the same 2*C warps, so one lane probes its
-      // own row (with a pause between probes: 2 * parts loads, not 64 * parts, per probe) and only
-      // then does every lane read and validate its row; a lane whose words are not all there yet
-      // sends the warp round again.
-      float mean = 0.f, rstd = 0.f;
-      float pm[8], pq[8];  // N <= 1024: at most 8 partials per row
-      const unsigned long long* rp64 = words + static_cast<size_t>(row_ok ? row : 0) * parts * 2;
-      const long long t0 = clock64();
-      bool give_up = false;
-      while (true) {
-        if (lane == 0 && row_ok) {
-          uint32_t probes = 0;
-          while (true) {
-            // all loads are issued before any tag is looked at (no short-circuit: one round trip, not 2*parts)
-            uint32_t bad = 0;
-#pragma unroll
-            for (int p = 0; p < 8; ++p)
-              if (p < parts) {
-                const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
-                const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
-                bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
-              }
-            if (bad == 0) break;
-            if ((++probes & 15u) == 0u && (*abort_flag != 0 || clock64() - t0 > (1ll << 31))) break;
-          }
-        }
-        __syncwarp();
-        uint32_t bad = 0;
-        if (row_ok) {
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p < parts) {
-              const unsigned long long w0 = ld_relaxed_gpu_u64(rp64 + 2 * p);
-              const unsigned long long w1 = ld_relaxed_gpu_u64(rp64 + 2 * p + 1);
-              bad |= (static_cast<uint32_t>(w0) ^ epoch) | (static_cast<uint32_t>(w1) ^ epoch);
-              pm[p] = __uint_as_float(static_cast<uint32_t>(w0 >> 32));
-              pq[p] = __uint_as_float(static_cast<uint32_t>(w1 >> 32));
-            }
-        }
-        if (__all_sync(0xffffffffu, bad == 0)) break;
-        if (*abort_flag != 0 || clock64() - t0 > (1ll << 31)) {
-          give_up = true;
-          break;
-        }
-        __nanosleep(100);
-      }
-      if (__any_sync(0xffffffffu, give_up)) {
-        if (lane == 0) {
-          *abort_flag = 1;
-          if (args.status != nullptr) atomicCAS(args.status, 0, kStatusGemmEpilogueTimeout);
-        }
-        break;
-      }
-      if (row_ok) {
-#pragma unroll
-        for (int p = 0; p < 8; ++p)
-          if (p < parts) mean += pm[p];
-        mean *= 1.0f / static_cast<float>(parts);
-        float M2 = 0.f;
-#pragma unroll
-        for (int p = 0; p < 8; ++p)
-          if (p < parts) {
-            const float d = pm[p] - mean;
-            M2 += pq[p] + static_cast<float>(kColsPerThread) * d * d;
-          }
-        rstd = rsqrtf(M2 * inv_n + args.eps);
-      }
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
-      const float shift = -mean * rstd;
-      tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
-      // ---- 4. normalise, gamma / beta, fp16, store (64 columns = 128 B per row at a time)
-      const bool slab_full = row0 + 32 <= M;
-      {
-        uint32_t raw[2][32];
-        tmem_ld_32x32(t_row, raw[0]);
-#pragma unroll
-        for (int ci = 0; ci < kColsPerThread / 32; ++ci) {
-          const int c = ci * 32;
-          const int hh = ci & 1;  // which half of the current 64-column store chunk
-          uint8_t* srow = stg + lane * 128;
-          if (hh == 0 && slab_full) {
-            if (lane == 0) tma_store_wait_read_n<0>();  // the previous bulk store has read the staging rows
-            __syncwarp();
-          }
-          tmem_ld_wait();
-          if (ci + 1 < kColsPerThread / 32) tmem_ld_32x32(t_row + c + 32, raw[(ci + 1) & 1]);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int col8 = gcol0 + c + q * 8;  // first of these 8 columns
-            float g[8], b[8];
-            if (args.gb_fp32) {
-              const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2));
-              const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gamma) + (col8 >> 2) + 1);
-              const float4 b0 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2));
-              const float4 b1 = __ldg(reinterpret_cast<const float4*>(args.beta) + (col8 >> 2) + 1);
-              g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
-              b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
-            } else {
-              const uint4 g4 = sgamma[c / 8 + q];
-              const uint4 b4 = sbeta[c / 8 + q];
-              const __half2* gh = reinterpret_cast<const __half2*>(&g4);
-              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 fg = __half22float2(gh[j]);
-                const float2 fb = __half22float2(bh[j]);
-                g[2 * j] = fg.x; g[2 * j + 1] = fg.y;
-                b[2 * j] = fb.x; b[2 * j + 1] = fb.y;
-              }
-            }
-            float y[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              y[i] = fmaf(fmaf(__uint_as_float(raw[ci & 1][q * 8 + i]), rstd, shift), g[i], b[i]);
-            uint4 u;
-            u.x = pack_half2(y[0], y[1]);
-            u.y = pack_half2(y[2], y[3]);
-            u.z = pack_half2(y[4], y[5]);
-            u.w = pack_half2(y[6], y[7]);
-            const int unit = hh * 4 + q;  // 16-byte unit inside the 128-byte row
-            if (slab_full)
-              *reinterpret_cast<uint4*>(srow + ((unit ^ (lane & 7)) << 4)) = u;
-            else if (row_ok)
-              *reinterpret_cast<uint4*>(args.out_ln + static_cast<size_t>(row) * args.N + col8) = u;
-          }
-          if (hh == 1 && slab_full) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tm_out, stg, gcol0 + c - 32, row0);
-              tma_store_commit();
-            }
-          }
-        }
-      }
-      if (warp == 2 && lane == 0) gstamp(args.timing, it, 3);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&acc_empty[as]);
-        mbar_arrive(vec_empty);
-      }
-    }
-    if (lane == 0) tma_store_wait_all();
+    ln_epilogue_loop(args, &tm_out, &tm_res, smem + kStages * Cfg::kStageBytes, acc_full, vec_full, vec_empty, res_bar,
+                     vec_s, abort_flag, tmem_base, M, n_tiles, warp, lane, tile_at,
+                     [&](int as) { mbar_arrive(&acc_empty[as]); });
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1185,6 +1203,190 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
+// ------------------------------------------------------------------------------------------
+// GEMM + bias + residual + LayerNorm on SM pairs: the main loop of gemm_f16_pair_kernel (256 x 256
+// tiles, cta_group::2, half of the W tile per SM) with the epilogue of gemm_f16_ln_kernel.  Each CTA
+// of a pair holds the accumulator of its own 128 rows, so its epilogue warps do exactly what those of
+// the one-CTA kernel do; the partials of a row come from the N/256 clusters working on that row tile.
+// Tiles go round-robin over the clusters (all resident: the launch asks for no more clusters than fit),
+// and a cluster only waits for clusters working on earlier or the same row tiles: no circular wait.
+// ------------------------------------------------------------------------------------------
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_f16_pair_ln_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                        const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
+                        const GemmArgs args) {
+  using Cfg = PairCfg;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kTileN = Cfg::kTileN;
+
+  extern __shared__ uint8_t smem_raw[];
+  // Both CTAs of the pair must use identical shared-memory offsets (the MMA and the multicast
+  // commit address the peer by offset); dynamic shared memory starts at the same offset in
+  // every CTA of a launch, so the same round-up applies to both.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+  uint64_t* full_bar = bars;                    // [kStages]  (leader's copy is the live one)
+  uint64_t* empty_bar = bars + kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;      // [2]
+  uint64_t* acc_empty = bars + 2 * kStages + 2; // [2]        (leader's copy is the live one)
+  uint64_t* vec_full = bars + 2 * kStages + 4;   // as in gemm_f16_ln_kernel
+  uint64_t* vec_empty = bars + 2 * kStages + 5;
+  uint64_t* res_bar = bars + 2 * kStages + 6;    // [kEpiWarps]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6 + kEpiWarps);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint4* vec_s = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bars) + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+  const bool leader = cta_rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  pdl_launch_dependents();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 2 * kEpiWarps);
+    }
+    mbar_init(vec_full, 1);
+    mbar_init(vec_empty, kEpiWarps);
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_bar[w], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // see gemm_f16_kernel
+  int M = args.m_rows;
+  if (args.m_dev != nullptr) {
+    const int md = __ldg(args.m_dev);
+    M = md < M ? md : M;
+  }
+  const int n_tiles = args.N / kTileN;
+  const int m_tiles = (M + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = args.K / kBlockK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_a);
+      tma_prefetch_desc(&tm_b);
+      tma_prefetch_desc(&tm_out);
+      tma_prefetch_desc(&tm_res);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile / n_tiles) * (2 * kBlockM) + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = (tile % n_tiles) * kTileN + static_cast<int>(cta_rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, args.status,
+                                 kStatusGemmProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          // the leader announces the bytes of both CTAs; all copies complete on its barrier
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sa, &tm_a, bar, kb * kBlockK, m0);
+          tma_load_2d_pair(sb, &tm_b, bar, n0, kb * kBlockK);
+          tma_load_2d_pair(sb + 64 * kBlockK * 2, &tm_b, bar, n0 + 64, kb * kBlockK);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++it) {
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[as], aphase ^ 1u, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        gstamp(args.timing, it, 0);
+        const uint32_t d_tmem = tmem_base + as * kTileN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, args.status, kStatusGemmMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint64_t adesc = smem_desc(args.a_desc_hi, sa + k * args.a_kstep_bytes);
+            const uint64_t bdesc = smem_desc(args.b_desc_hi, sb + k * args.b_kstep_bytes);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, args.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);  // frees the stage in both CTAs
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(&acc_full[as]);
+        gstamp(args.timing, it, 1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    auto tile_at = [&](int it, int& m0, int& n0) -> bool {
+      const int tile = cluster_id + it * num_clusters;
+      if (tile >= total_tiles) return false;
+      m0 = (tile / n_tiles) * (2 * kBlockM) + static_cast<int>(cta_rank) * kBlockM;
+      n0 = (tile % n_tiles) * kTileN;
+      return true;
+    };
+    ln_epilogue_loop(args, &tm_out, &tm_res, smem + kStages * Cfg::kStageBytes, acc_full, vec_full, vec_empty, res_bar,
+                     vec_s, abort_flag, tmem_base, M, n_tiles, warp, lane, tile_at,
+                     [&](int as) { mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[as]), 0)); });
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
 
 // ------------------------------------------------------------------------------------------ launch
 template <int BLOCK_N, int EPI>
@@ -1271,12 +1473,70 @@ struct LnGemmCfg {
 };
 static_assert(LnGemmCfg::kSmemBytes <= 227 * 1024, "shared memory of the GEMM + LayerNorm kernel");
 
-cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
+struct PairLnGemmCfg {
+  static constexpr int kSmemBytes = PairCfg::kSmemBytes + 1536;
+};
+static_assert(PairLnGemmCfg::kSmemBytes <= 227 * 1024, "shared memory of the pair GEMM + LayerNorm kernel");
+int g_pair_ln_clusters[64] = {};
+
+// The pair form of the GEMM + LayerNorm kernel.  `a.idesc` must describe M = 256.
+cudaError_t launch_pair_ln_gemm(const GemmLaunch& g, const GemmArgs& a, cudaStream_t stream) {
+  using Cfg = PairLnGemmCfg;
+  static bool attr_set[64] = {};
+  auto kern = gemm_f16_pair_ln_kernel;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  if (g_pair_ln_clusters[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (g.num_sms / 2));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    int n = 0;
+    // every cluster must be resident (clusters wait for one another's row statistics): without an
+    // answer from the occupancy query the pair form is not used
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = -1;
+    }
+    g_pair_ln_clusters[dev] = n;
+  }
+  if (g_pair_ln_clusters[dev] <= 0) return cudaErrorNotSupported;
+  const int n_tiles = g.N / 256;
+  const int m_tiles = (g.m_rows + 2 * kBlockM - 1) / (2 * kBlockM);
+  long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+  int clusters = static_cast<int>(tiles < g_pair_ln_clusters[dev] ? tiles : g_pair_ln_clusters[dev]);
+  if (clusters < 1) clusters = 1;
+  return launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), Cfg::kSmemBytes, stream, g.tm_a, g.tm_b, g.tm_out,
+                    g.tm_res, a);
+}
+
+cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a_in, cudaStream_t stream) {
   using Cfg = LnGemmCfg;
   static bool attr_set[64] = {};
   auto kern = gemm_f16_ln_kernel;
   if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || g.ln_epoch == 0)
     return cudaErrorInvalidValue;
+  // The pair form is selectable (debug key 9 = 1) but not the default.  Measured on 18.9k-row calls, 1800
+  // launches each: FFN2 (K = 3072, main loop the longer leg) 155 against 164 ms of kernel time, attention
+  // output (K = 768, epilogue the longer leg) 97 against 87 ms: a buffer of the shared accumulator is only
+  // released when the epilogue warps of BOTH CTAs are done with it.  With the pair form for FFN2 alone the
+  // kernels of a forward sum to 1 % less, but the forward as a whole does not change (150.6 against
+  // 150.4 ms per step over 20 steps, three A/B pairs on one box): the step runs at the power cap, and a
+  // kernel that finishes sooner by working the tensor cores harder gives the time back in clock.
+  const bool want_pair = g_dbg_ln_pair == 1;
+  if (want_pair) {
+    GemmArgs ap = a_in;
+    ap.idesc = make_idesc_f16(256, 256, 0, 1);
+    const cudaError_t e = launch_pair_ln_gemm(g, ap, stream);
+    if (e != cudaErrorNotSupported) return e;
+  }
+  const GemmArgs& a = a_in;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -1408,7 +1668,8 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // 4 = forced BLOCK_N of the one-CTA kernel, 5 = pair kernel (0 auto, 1 always when
 // N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0),
 // 7 = split-K of the fp32-sum GEMMs (0 policy, < 0 never, > 0 that many K ranges),
-// 8 = W blocks of a CTA's first tile requested before the dependency wait (1, default) or after (0).
+// 8 = W blocks of a CTA's first tile requested before the dependency wait (1, default) or after (0),
+// 9 = GEMM + LayerNorm on SM pairs (1 always; 0, the default, and 2 never).
 // value 0 restores the default for keys 1-5 and 7.
 // Device buffer of 148 x 16 x 8 long long for clock64 stamps of the GEMM kernels (null = off):
 // slots 0/1 MMA warp (accumulator free, last commit), 2/3 epilogue warp 2 (accumulator ready, tile
@@ -1425,6 +1686,7 @@ extern "C" int bt_debug_set(int key, long long value) {
     case 4: bt::g_dbg_force_block_n = value; return 0;
     case 7: bt::g_dbg_split_k = value; return 0;
     case 8: bt::g_dbg_early_w = value; return 0;
+    case 9: bt::g_dbg_ln_pair = value; return 0;
     case 5: bt::g_dbg_pair_mode = value; return 0;
     case 6: bt::set_pdl_enabled(value != 0); return 0;
     default: return 1;

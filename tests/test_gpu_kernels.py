@@ -369,8 +369,19 @@ def test_attention_variants(enc, cuda_device, tiles, exp16):
     (128, 256, 64, False, None), (333, 768, 768, False, None), (1000, 768, 3072, True, None),
     (18944, 768, 768, False, None), (700, 1024, 1024, True, 555), (40000, 768, 768, False, 39999), (130, 512, 128, False, 0),
 ])
-def test_gemm_with_fused_layernorm(enc, cuda_device, M, N, K, gb32, m_valid):
-    """bt_gemm_layernorm: GEMM + bias + residual + LayerNorm in one kernel (a CTA owns whole rows)."""
+@pytest.mark.parametrize("pair", [2, 1], ids=["one_cta", "sm_pairs"])
+def test_gemm_with_fused_layernorm(enc, cuda_device, M, N, K, gb32, m_valid, pair):
+    """bt_gemm_layernorm: GEMM + bias + residual + LayerNorm in one kernel, in its one-CTA form and in the
+    form that runs the main loop on SM pairs (256-row tiles), each forced for every shape."""
+    from bytetransformer_b200 import _abi
+    _abi.load().bt_debug_set(9, pair)
+    try:
+        _fused_layernorm_case(enc, cuda_device, M, N, K, gb32, m_valid)
+    finally:
+        _abi.load().bt_debug_set(9, 0)
+
+
+def _fused_layernorm_case(enc, cuda_device, M, N, K, gb32, m_valid):
     g = torch.Generator().manual_seed(M + N + K)
     a = torch.randn(M, K, generator=g).half()
     w = (torch.randn(K, N, generator=g) * 0.05).half()
