@@ -813,10 +813,14 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           }
           tc_fence_after();
           const uint32_t sv = s_v + st * kTileBytes;
+          // only the 16-key steps that hold keys of this sequence (in the last tile the softmax leaves
+          // the P columns of 32-key chunks without any key unwritten)
+          const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
 #pragma unroll
           for (int kk = 0; kk < kKvRows / 16; ++kk)
-            umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
-                        (j > 0 || kk != 0) ? 1u : 0u);
+            if (kk < kk_n)
+              umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
+                          (j > 0 || kk != 0) ? 1u : 0u);
           if (PSEP) umma_commit(pv_done);
           if (!PSEP && j + 1 < n_kv) {
             if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
@@ -865,37 +869,54 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           const uint32_t t_p = t_lane + kTmemP;
           uint32_t va[32], vb[32], pk0[16], pk1[16];
           float xmax = -INFINITY, l_tile = 0.f;
-          tmem_ld_32x32(t_s, va);
-          tmem_ld_wait();
-          tmem_ld_32x32(t_s + 32, vb);
-          if (j == 0) m_ref = c * (full_tile ? chunk_max<false>(va, 0, kv_valid) : chunk_max<true>(va, 0, kv_valid));
-          l_tile += full_tile ? chunk_probs_track<false>(va, 0, kv_valid, c, m_ref, pk0, xmax)
-                              : chunk_probs_track<true>(va, 0, kv_valid, c, m_ref, pk0, xmax);
-          tmem_ld_wait();
-          tmem_ld_32x32(t_s + 64, va);
-          l_tile += full_tile ? chunk_probs_track<false>(vb, 32, kv_valid, c, m_ref, pk1, xmax)
-                              : chunk_probs_track<true>(vb, 32, kv_valid, c, m_ref, pk1, xmax);
-          // P (and O) belong to the P V MMAs of the previous key tile until those have retired; the first
-          // two chunks were computed in the meantime.  (First tile of an item: the wait for the previous
-          // item's O at its end already covered that.)
-          if (j > 0) {
-            if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-              ok = false;
-              break;
+          if (full_tile) {
+            tmem_ld_32x32(t_s, va);
+            tmem_ld_wait();
+            tmem_ld_32x32(t_s + 32, vb);
+            if (j == 0) m_ref = c * (chunk_max<false>(va, 0, kv_valid));
+            l_tile += chunk_probs_track<false>(va, 0, kv_valid, c, m_ref, pk0, xmax);
+            tmem_ld_wait();
+            tmem_ld_32x32(t_s + 64, va);
+            l_tile += chunk_probs_track<false>(vb, 32, kv_valid, c, m_ref, pk1, xmax);
+            // P (and O) belong to the P V MMAs of the previous key tile until those have retired; the first
+            // two chunks were computed in the meantime.  (First tile of an item: the wait for the previous
+            // item's O at its end already covered that.)
+            if (j > 0) {
+              if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
             }
-            tc_fence_after();
+            tmem_st_32x16(t_p, pk0);
+            tmem_st_32x16(t_p + 16, pk1);
+            tmem_ld_wait();
+            tmem_ld_32x32(t_s + 96, vb);
+            l_tile += chunk_probs_track<false>(va, 64, kv_valid, c, m_ref, pk0, xmax);
+            tmem_st_32x16(t_p + 32, pk0);
+            tmem_ld_wait();
+            l_tile += chunk_probs_track<false>(vb, 96, kv_valid, c, m_ref, pk1, xmax);
+            tmem_st_32x16(t_p + 48, pk1);
+          } else {
+            // last tile of the sequence: only the 32-key chunks that hold at least one key are read and
+            // exponentiated; the P columns of the others stay unwritten (the P V steps stop before them)
+            const int n_chunks = (kv_valid + 31) >> 5;
+            for (int ch = 0; ch < n_chunks; ++ch) {
+              tmem_ld_32x32(t_s + ch * 32, va);
+              tmem_ld_wait();
+              if (j == 0 && ch == 0) m_ref = c * chunk_max<true>(va, 0, kv_valid);
+              l_tile += chunk_probs_track<true>(va, ch * 32, kv_valid, c, m_ref, pk0, xmax);
+              if (ch == 0 && j > 0) {
+                if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+              }
+              tmem_st_32x16(t_p + ch * 16, pk0);
+            }
+            if (!ok) break;
           }
-          tmem_st_32x16(t_p, pk0);
-          tmem_st_32x16(t_p + 16, pk1);
-          tmem_ld_wait();
-          tmem_ld_32x32(t_s + 96, vb);
-          l_tile += full_tile ? chunk_probs_track<false>(va, 64, kv_valid, c, m_ref, pk0, xmax)
-                              : chunk_probs_track<true>(va, 64, kv_valid, c, m_ref, pk0, xmax);
-          tmem_st_32x16(t_p + 32, pk0);
-          tmem_ld_wait();
-          l_tile += full_tile ? chunk_probs_track<false>(vb, 96, kv_valid, c, m_ref, pk1, xmax)
-                              : chunk_probs_track<true>(vb, 96, kv_valid, c, m_ref, pk1, xmax);
-          tmem_st_32x16(t_p + 48, pk1);
           if (__any_sync(0xffffffffu, xmax > kRescaleThreshold)) {
             // the reference was too low for some row of this warp: move it, rescale O and the running
             // sum, and form this tile's probabilities again from S (rows that did not need it get f = 1)
