@@ -7,6 +7,13 @@
  * `cudaStream_t` passed as `void*`.  The library allocates no device memory:
  * scratch is the caller's `workspace` (size from bt_workspace_bytes()).
  *
+ * Concurrency: a handle may be used by one host thread at a time (it caches tensor maps and
+ * counts launches); different handles may be used from different threads and streams at once.
+ * Calls on one handle are ordered by the stream they are given; a handle's kernels on two
+ * streams at once must not share a workspace.  The first kernel of every forward call is
+ * serialised behind all earlier work of its stream the ordinary way; the others use programmatic
+ * dependent launch among themselves.
+ *
  * Each declaration names the reference interface it stands in for
  * (paths relative to the ByteTransformer project root).
  *
