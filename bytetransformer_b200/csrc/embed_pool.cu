@@ -123,11 +123,13 @@ embedding_layernorm_kernel(const __half* __restrict__ word_emb, const __half* __
 }
 
 // pooled[b, n] = tanh(sum_k y[b, 0, k] * W[k, n] + bias[n]).  CTA = (64 output columns, one sequence),
-// 256 threads: thread (kq, c) sums the k = kq mod 4 quarter for column c; the quarters meet in shared memory.
+// 256 threads: thread (kg, cp) sums every 8th k (k = kg mod 8) for the column pair cp, so a warp reads
+// one 128-byte line of W per k and up to 32 loads are in flight per thread; the eight groups meet in shared
+// memory.  The work is tiny (B x H x H): what matters is that no thread walks a long chain of loads.
 __global__ void __launch_bounds__(256)
 pooler_kernel(const __half* __restrict__ y, const __half* __restrict__ W, const __half* __restrict__ bias,
               __half* __restrict__ pooled, int seq_len, int hidden) {
-  extern __shared__ float xs[];  // hidden floats: the first token's row, then 4 x 64 partial sums
+  extern __shared__ float xs[];  // hidden floats: the first token's row, then 8 x 64 partial sums
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.y;
@@ -135,19 +137,30 @@ pooler_kernel(const __half* __restrict__ y, const __half* __restrict__ W, const 
   const __half* row = y + static_cast<size_t>(b) * seq_len * hidden;
   for (int k = threadIdx.x; k < hidden; k += blockDim.x) xs[k] = __half2float(__ldg(row + k));
   __syncthreads();
-  const int c = threadIdx.x & 63;
-  const int kq = threadIdx.x >> 6;
-  const int n = n0 + c;
-  float acc = 0.f;
-  if (n < hidden) {
-    for (int k = kq; k < hidden; k += 4) acc = fmaf(xs[k], __half2float(__ldg(W + static_cast<size_t>(k) * hidden + n)), acc);
+  const int cp = threadIdx.x & 31;   // column pair
+  const int kg = threadIdx.x >> 5;   // k group (the warp)
+  const int n = n0 + 2 * cp;
+  float acc0 = 0.f, acc1 = 0.f;
+  if (n + 1 < hidden) {  // hidden is even (checked by the launcher)
+    const __half2* wp = reinterpret_cast<const __half2*>(W + n);
+    const size_t ld2 = static_cast<size_t>(hidden) / 2;  // row stride in half2
+#pragma unroll 32
+    for (int k = kg; k < hidden; k += 8) {
+      const float2 w = __half22float2(__ldg(wp + static_cast<size_t>(k) * ld2));
+      acc0 = fmaf(xs[k], w.x, acc0);
+      acc1 = fmaf(xs[k], w.y, acc1);
+    }
   }
   float* part = xs + hidden;
-  part[kq * 64 + c] = acc;
+  part[kg * 64 + 2 * cp] = acc0;
+  part[kg * 64 + 2 * cp + 1] = acc1;
   __syncthreads();
-  if (kq == 0 && n < hidden) {
-    const float s = part[c] + part[64 + c] + part[128 + c] + part[192 + c] + __half2float(__ldg(bias + n));
-    pooled[static_cast<size_t>(b) * hidden + n] = __float2half(tanhf(s));
+  const int c = threadIdx.x;
+  if (c < 64 && n0 + c < hidden) {
+    float sum = __half2float(__ldg(bias + n0 + c));
+#pragma unroll
+    for (int g = 0; g < 8; ++g) sum += part[g * 64 + c];
+    pooled[static_cast<size_t>(b) * hidden + n0 + c] = __float2half(tanhf(sum));
   }
 }
 
@@ -183,9 +196,9 @@ cudaError_t launch_embedding_layernorm(const __half* word_emb, const __half* pos
 
 cudaError_t launch_pooler(const __half* y, const __half* W, const __half* bias, __half* pooled, int B, int seq_len,
                           int hidden, cudaStream_t stream) {
-  if (B <= 0 || B > 65535 || seq_len <= 0 || hidden <= 0 || hidden > 8192) return cudaErrorInvalidValue;
+  if (B <= 0 || B > 65535 || seq_len <= 0 || hidden <= 0 || hidden > 8192 || hidden % 2 != 0) return cudaErrorInvalidValue;
   dim3 grid((hidden + 63) / 64, B);
-  const size_t smem = (static_cast<size_t>(hidden) + 256) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(hidden) + 512) * sizeof(float);
   return launch_pdl(pooler_kernel, grid, dim3(256), smem, stream, y, W, bias, pooled, seq_len, hidden);
 }
 

@@ -59,6 +59,11 @@ def main():
                     help="A/B aid: K ranges of the GEMMs that feed a LayerNorm: 0 policy, -1 never, n > 0 forced")
     ap.add_argument("--late-weights", action="store_true",
                     help="A/B aid: request the first weight blocks of a GEMM only after the wait for the kernel before")
+    ap.add_argument("--general", choices=["padded", "causal"], default=None,
+                    help="time the general-mask entry point instead (nothing packed, the whole [B,S,S] mask applied): "
+                         "with the same right-padded mask, or with a causal mask over the valid keys")
+    ap.add_argument("--front-back", action="store_true",
+                    help="also time the embedding + LayerNorm front end (30522-word table) and the pooler for each shape")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
@@ -93,7 +98,12 @@ def main():
         x = torch.randn(B, S, H, generator=g).half().to(dev)
         mask = (torch.arange(S)[None, :] < lens[:, None]).unsqueeze(1).expand(B, S, S).contiguous().half().to(dev)
 
+        if args.general == "causal":
+            mask = (mask.bool() & torch.tril(torch.ones(S, S, dtype=torch.bool, device=dev))[None]).half().contiguous()
+
         def fwd():
+            if args.general is not None:
+                return enc.forward_general(x, mask)
             if args.per_layer_op:
                 h = x
                 for l in range(BERT_BASE.layers):
@@ -138,13 +148,45 @@ def main():
             breakdown = {k: {"us_per_forward": round(v[0] * 1e3 / reps, 2), "launches_per_forward": v[1] // reps}
                          for k, v in enc.profile_read().items() if v[1]}
             enc.profile_enable(False)
+        extra = {}
+        if args.front_back:
+            from .encoder import embedding_layernorm, pooler
+            gg = torch.Generator().manual_seed(3)
+            vocab = 30522
+            word = (torch.randn(vocab, H, generator=gg) * 0.02).half().to(dev)
+            pos = (torch.randn(1024, H, generator=gg) * 0.02).half().to(dev)
+            typ = (torch.randn(2, H, generator=gg) * 0.02).half().to(dev)
+            gam, bet = torch.ones(H).half().to(dev), torch.zeros(H).half().to(dev)
+            ids = torch.randint(0, vocab, (B, S), generator=gg, dtype=torch.int32).to(dev)
+            pw, pb = (torch.randn(H, H, generator=gg) * 0.02).half().to(dev), torch.zeros(H).half().to(dev)
+
+            def timed(fn):
+                ts = []
+                for i in range(args.warmup + args.iters):
+                    flush.zero_()
+                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a0.record()
+                    fn()
+                    a1.record()
+                    torch.cuda.synchronize()
+                    if i >= args.warmup:
+                        ts.append(a0.elapsed_time(a1))
+                return statistics.median(ts)
+
+            t_emb = timed(lambda: embedding_layernorm(word, pos, typ, gam, bet, ids))
+            t_pool = timed(lambda: pooler(x, pw, pb))
+            emb_bytes = B * S * H * 2 * 4  # word row + position row + type row in, one row out
+            extra = {"embedding_layernorm_us": round(t_emb * 1e3, 2),
+                     "embedding_layernorm_gbs": round(emb_bytes / t_emb / 1e6, 1),
+                     "pooler_us": round(t_pool * 1e3, 2)}
+        api = ("general-mask stack (" + args.general + " mask)") if args.general else None
         print(json.dumps({
             "metric": "ms_per_12_layer_forward", "batch": B, "max_seq": S, "valid_tokens": T, "value": ms,
             "unit": "ms", "min_ms": min(times), "tokens_per_s": T / ms * 1e3, "algorithmic_tflops": fl / ms / 1e9,
             "higher_is_better": False, "reference_a100_ms": ref, "speedup_vs_reference_a100": (ref / ms) if ref else None,
-            "api": ("per-layer operator x12" if args.per_layer_op else "one-call padded stack") + (", CUDA graph" if graph else "") + (", no PDL" if args.no_pdl else ""),
+            "api": (api or ("per-layer operator x12" if args.per_layer_op else "one-call padded stack")) + (", CUDA graph" if graph else "") + (", no PDL" if args.no_pdl else ""),
             "l2": "flushed before every timed iteration", "data": "synthetic", "dtype": "f16",
-            **({"breakdown": breakdown} if breakdown else {})}), flush=True)
+            **extra, **({"breakdown": breakdown} if breakdown else {})}), flush=True)
     if enc.device_status() != 0:
         print("device status non-zero", file=sys.stderr)
         return 1

@@ -304,7 +304,7 @@ int bt_masked_softmax(void* logits, const void* attr_mask, int batch_size, int h
  *   fp16 or fp32, out fp16 [batch_size, seq_len, hidden] = the encoder's input.  hidden % 8 == 0,
  *   hidden <= 1024; all pointers but the ids 16-byte aligned.
  * bt_pooler: pooled[b,:] = tanh(encoder_out[b,0,:] * W + bias), W fp16 [hidden, hidden] as [in,out],
- *   pooled fp16 [batch_size, hidden]. */
+ *   pooled fp16 [batch_size, hidden]; hidden even, W 4-byte aligned. */
 int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void* type_emb,
                            const void* gamma, const void* beta, int gamma_beta_fp32,
                            const int* token_ids, const int* type_ids, const int* position_ids, void* out,
