@@ -429,5 +429,5 @@ def test_tensor_memory_read_rate_is_far_above_what_the_kernels_consume(cuda_devi
     that only reads tensor memory gets several times that, so they are not bounded by tensor-memory
     bandwidth (the figure this test guards is quoted where the kernels are described)."""
     from bytetransformer_b200.tmem_probe import read_rate
-    assert read_rate(0, 4, device=cuda_device) > 100.0
-    assert read_rate(2, 8, device=cuda_device) > 200.0
+    assert read_rate(0, 4, device=cuda_device) > 80.0    # measured 123
+    assert read_rate(2, 8, device=cuda_device) > 150.0   # measured 370
