@@ -41,7 +41,7 @@ WORKLOAD = "whole_box_1024x1024"
 # 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_kernels_microbatch18k.txt
 # (algorithmic bytes of the same four launches: 132.4 MB mean; DRAM sees less because outputs of one
 # kernel are still in the 126 MB L2 when the next kernel reads them).
-GEMM_DRAM_BYTES_PER_LAUNCH = 94.5e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 94.6e6
 WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
 
 
