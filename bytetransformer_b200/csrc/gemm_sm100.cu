@@ -896,9 +896,10 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
     if (warp == 2 && lane == 0) gstamp(args.timing, it, 5);
     // ---- 3. wait until the row's 2 * parts words all carry this epoch (bounded), then merge.
     // The partials of the 32 rows of this slab come from the same 2*C warps, so one lane probes its
-    // own row (with a pause between probes: 2 * parts loads, not 64 * parts, per probe) and only
-    // then does every lane read and validate its row; a lane whose words are not all there yet
-    // sends the warp round again.
+    // own row (2 * parts loads per probe, not 64 * parts: letting every lane poll its row was measured
+    // and cost 15 % of the kernel, a pause between probes changed nothing) and only then does every
+    // lane read and validate its row; a lane whose words are not all there yet sends the warp round
+    // again.
     float mean = 0.f, rstd = 0.f;
     float pm[8], pq[8];  // N <= 1024: at most 8 partials per row
     const unsigned long long* rp64 = words + static_cast<size_t>(row_ok ? row : 0) * parts * 2;
