@@ -1679,6 +1679,25 @@ extern "C" int bt_debug_set_gemm_timing(long long* device_buffer) {
   bt::g_dbg_gemm_timing = device_buffer;
   return 0;
 }
+// Host-side shape policies, callable without a device (tests): what 0 = tile width of the one-CTA
+// kernel, 1 = K ranges of an fp32-sum GEMM, 2 = 1 if the pair kernel would take a bias-only GEMM.
+extern "C" int bt_debug_policy(int what, int m_rows, int N, int K, int num_sms) {
+  switch (what) {
+    case 0: return bt::gemm_pick_block_n(m_rows, N, num_sms);
+    case 1: return bt::gemm_pick_split_k(m_rows, N, K, num_sms);
+    case 2: {
+      bt::GemmLaunch g = {};
+      g.m_rows = m_rows;
+      g.N = N;
+      g.K = K;
+      g.epilogue = BT_EPI_BIAS;
+      g.block_n = 0;
+      g.num_sms = num_sms;
+      return bt::use_pair_kernel(g) ? 1 : 0;
+    }
+    default: return -1;
+  }
+}
 extern "C" int bt_debug_set(int key, long long value) {
   switch (key) {
     case 1: bt::g_dbg_b_lbo = value; return 0;
