@@ -5,13 +5,13 @@ import ctypes as C
 
 import pytest
 
-from bytetransformer_b200 import _abi
-
 SMS = 148
 
 
 @pytest.fixture(scope="module")
 def policy():
+    from bytetransformer_b200 import _abi, build
+    build.build_core()  # no-op when the library is up to date
     lib = _abi.load()
     fn = lib.bt_debug_policy
     fn.restype = C.c_int
