@@ -303,6 +303,7 @@ static int run_gemm(bt_handle h, int kind, const __half* A, const void* W, __hal
 struct GeneralMask {
   const __half* mask = nullptr;
   const __half* bias = nullptr;
+  const int* kv_bound = nullptr;  // per (sequence, query tile): leading keys that matter (launch_mask_key_bound)
 };
 
 static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch_idx, int B, int max_len, int rows,
@@ -321,6 +322,7 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   if (gm != nullptr && gm->mask != nullptr) {
     a.gen_mask = gm->mask;
     a.gen_bias = gm->bias;
+    a.gen_kv_bound = gm->kv_bound;
     a.gen_inv_scale = sqrtf(static_cast<float>(h->cfg.size_per_head)) * h->cfg.tao;
   }
   cudaError_t e;
@@ -503,6 +505,14 @@ static int stack_general(bt_handle h, int first_layer, int n_layers, const void*
   GeneralMask gm;
   gm.mask = reinterpret_cast<const __half*>(mask);
   gm.bias = reinterpret_cast<const __half*>(attention_bias);
+  // Key tiles that no row of a query tile may see are left out of the attention (once per call; the
+  // packed-index region of the workspace is free on this path: B * ceil(S/128) <= B * S ints).
+  {
+    LaunchScope scope(h, BT_PROF_OFFSETS, stream);
+    e = launch_mask_key_bound(gm.mask, B, S, ws.word_idx, stream);
+  }
+  if (e != cudaSuccess) return fail_cuda(h, e, "mask key-bound launch");
+  gm.kv_bound = ws.word_idx;
   const __half* cur = reinterpret_cast<const __half*>(input);
   for (int l = 0; l < n_layers; ++l) {
     const bool last = (l == n_layers - 1);

@@ -57,6 +57,8 @@ cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t st
 // the first len_b rows, no key from len_b on allowed in any later row; len_b = number of entries >= 0.5
 // in row 0), else 0.
 cudaError_t launch_mask_is_right_padded(const __half* mask, int B, int S, int* flag_dev, cudaStream_t stream);
+// bound_dev[b * ceil(S/128) + t] = number of leading keys that query tile t of sequence b needs (see offsets.cu)
+cudaError_t launch_mask_key_bound(const __half* mask, int B, int S, int* bound_dev, cudaStream_t stream);
 cudaError_t launch_restore_rows(const __half* packed, __half* padded, const int* batch_idx, int B, int S,
                                 int hidden, cudaStream_t stream);
 
@@ -114,6 +116,7 @@ struct MhaLaunch {
   const __half* gen_mask = nullptr;  // [batch, max_len, max_len], null = lengths from batch_idx only
   const __half* gen_bias = nullptr;  // [head_num, max_len, max_len] or null
   float gen_inv_scale = 8.0f;        // sqrt(64) * tao
+  const int* gen_kv_bound = nullptr; // [batch, ceil(max_len/128)] keys that matter per query tile (launch_mask_key_bound) or null
 };
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
 

@@ -88,6 +88,7 @@ struct MhaArgs {
   const __half* gen_bias;  // [heads, S, S] or null
   int gen_seq_len;
   float gen_inv_scale;     // 1 / (softmax scale): the additive term is applied to the unscaled score
+  const int* gen_kv_bound; // [batch, query tiles]: leading keys that matter for the query tile, or null
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -371,7 +372,13 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_kv = (L + kKvRows - 1) / kKvRows;
+  // General masks: the key tiles behind the last key that any row of this query tile may see are left out
+  int kv_rows = L;
+  if (GENERAL && args.gen_kv_bound != nullptr) {
+    const int bound = __ldg(args.gen_kv_bound + b * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x));
+    kv_rows = bound < L ? (bound > 0 ? bound : 1) : L;
+  }
+  const int n_kv = (kv_rows + kKvRows - 1) / kKvRows;
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < TILES; ++t) {
@@ -1107,6 +1114,7 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.gen_bias = a.gen_bias;
   args.gen_seq_len = a.max_len;
   args.gen_inv_scale = a.gen_inv_scale;
+  args.gen_kv_bound = a.gen_kv_bound;
   if (a.gen_mask != nullptr) {
     // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
     using Cfg = MhaCfg<1>;

@@ -177,6 +177,48 @@ mask_is_right_padded_kernel(const __half* __restrict__ mask, int B, int S, int* 
   if (threadIdx.x == 0 && s_bad) atomicExch(flag, 0);
 }
 
+// General-mask attention: for every (sequence, tile of 128 query rows) the number of leading keys that
+// matter.  A key whose mask value is exactly 0 gets -10000 added to its score and an exponential of 0,
+// so the key tiles behind the last non-zero mask entry of every row of the query tile can be left out -
+// unless a row has no non-zero entry at all: then all its scores are shifted alike, its softmax runs
+// over ALL keys, and the bound of its tile is the full length.  Thread = one query row, scanned from
+// the end; CTA = one query tile.
+__global__ void __launch_bounds__(128)
+mask_key_bound_kernel(const __half* __restrict__ mask, int S, int* __restrict__ bound) {
+  __shared__ int s_bound;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) s_bound = 0;
+  __syncthreads();
+  const int b = blockIdx.y;
+  const int row = blockIdx.x * 128 + threadIdx.x;
+  if (row < S) {
+    const __half* m = mask + (static_cast<size_t>(b) * S + row) * S;
+    const __half zero = __float2half(0.f);
+    int last = -1;
+    int j = S - 1;
+    if ((S & 7) == 0) {
+      // 16-byte steps while the vector is all zero
+      for (; j >= 7 && last < 0; j -= 8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(m + j - 7));
+        if ((v.x | v.y | v.z | v.w) & 0x7FFF7FFFu) {  // some half is not +-0
+          for (int k = j; k > j - 8; --k)
+            if (__hne(m[k], zero)) {
+              last = k;
+              break;
+            }
+        }
+      }
+    } else {
+      for (; j >= 0 && last < 0; --j)
+        if (__hne(m[j], zero)) last = j;
+    }
+    atomicMax(&s_bound, last < 0 ? S : last + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) bound[b * gridDim.x + blockIdx.x] = s_bound;
+}
+
 __global__ void set_flag_kernel(int* flag, int v) {
   pdl_launch_dependents();
   pdl_wait();
@@ -207,6 +249,11 @@ cudaError_t launch_mask_is_right_padded(const __half* mask, int B, int S, int* f
   cudaError_t e = launch_pdl(set_flag_kernel, dim3(1), dim3(1), 0, stream, flag_dev, 1);
   if (e != cudaSuccess) return e;
   return launch_pdl(mask_is_right_padded_kernel, dim3(B), dim3(256), 0, stream, mask, B, S, flag_dev);
+}
+
+cudaError_t launch_mask_key_bound(const __half* mask, int B, int S, int* bound_dev, cudaStream_t stream) {
+  if (B <= 0 || B > 65535 || S <= 0) return cudaErrorInvalidValue;
+  return launch_pdl(mask_key_bound_kernel, dim3((S + 127) / 128, B), dim3(128), 0, stream, mask, S, bound_dev);
 }
 
 cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S, int hidden,

@@ -168,6 +168,10 @@ int bt_stack_forward_padded(bt_handle h, int n_layers, const void* input, const 
  * bytetransformer/src/attention_nofused.cu:78-95, th_op/bert_transformer_ext.h:83-107).  Any
  * [B,S,S] mask is honoured element by element (prefix-LM, block-diagonal, ...), not only row 0.
  * `attention_bias` is fp16 [head_num, seq_len, seq_len] or NULL.  Workspace: bt_workspace_bytes().
+ * A key whose mask value is exactly 0 contributes an exponential of 0, so key tiles behind the last
+ * non-zero mask entry of a tile of 128 query rows are not computed; a query row whose mask is all
+ * zero has every score shifted alike and therefore attends to ALL keys, as the formula says (this
+ * assumes |attention_bias| far below 10000).
  * Rows that a right-padding mask would have dropped hold finite but meaningless values, as in
  * the reference's padded path; use bt_mask_is_right_padded() to route such masks to the packed
  * entry points instead. */

@@ -24,6 +24,11 @@ def _masks(kind, B, S, g):
             cuts = sorted(set([0, S] + torch.randint(1, S, (3,), generator=g).tolist()))
             for lo, hi in zip(cuts[:-1], cuts[1:]):
                 m[b, lo:hi, lo:hi] = 1.0
+    elif kind == "causal_blank_rows":   # a few query rows may see nothing at all
+        m = torch.tril(torch.ones(S, S)).expand(B, S, S).clone()
+        m[:, 5, :] = 0.0
+        if S > 140:
+            m[0, 130:140, :] = 0.0
     elif kind == "right_padded":
         lens = torch.randint(1, S + 1, (B,), generator=g)
         m = ((torch.arange(S)[None, :] < lens[:, None]).float().unsqueeze(1)).expand(B, S, S).clone()
@@ -60,6 +65,14 @@ def _run(dev, nh, B, S, kind, with_bias, n_layers, seed):
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_general_mask_one_layer(cuda_device, kind, with_bias):
     _run(cuda_device, 4, 3, 200, kind, with_bias, 1, seed=11)
+
+
+@pytest.mark.parametrize("S", [300, 77])
+def test_rows_that_see_no_key_attend_to_all_keys(cuda_device, S):
+    """A row whose mask is all zero has every score shifted by the same -10000, so its softmax runs over ALL
+    keys (the reference's arithmetic mask): the key tiles of its query tile must not be cut short, while the
+    other query tiles of a causal mask stop at the diagonal.  Every row is compared."""
+    _run(cuda_device, 4, 2, S, "causal_blank_rows", False, 2, seed=19)
 
 
 def test_general_mask_seq_len_not_multiple_of_8(cuda_device):
