@@ -102,9 +102,6 @@ def load(path: str | None = None) -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the library does not export it
         fn.restype = res
         fn.argtypes = args
-    if hasattr(lib, "bt_debug_tmem_read_probe"):
-        lib.bt_debug_tmem_read_probe.restype = _i
-        lib.bt_debug_tmem_read_probe.argtypes = [_i, _i, _i, _i, C.c_void_p, C.c_void_p, C.c_void_p]
     if hasattr(lib, "bt_debug_set"):
         lib.bt_debug_set.restype = _i
         lib.bt_debug_set.argtypes = [_i, C.c_longlong]

@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 
-CU_SOURCES = ["offsets.cu", "eltwise.cu", "embed_pool.cu", "tmem_probe.cu", "gemm_sm100.cu", "mha_sm100.cu", "encoder.cu"]
+CU_SOURCES = ["offsets.cu", "eltwise.cu", "embed_pool.cu", "gemm_sm100.cu", "mha_sm100.cu", "encoder.cu"]
 CORE_LIB = os.path.join(LIB_DIR, "libbt_b200.so")
 THS_LIB = os.path.join(LIB_DIR, "libths_bytetransformer.so")
 
@@ -40,6 +40,34 @@ def _newer(target: str, deps) -> bool:
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
+def source_hash() -> str:
+    """Digest of the sources the core library is built from (first 12 hex digits of a SHA-256 over file
+    names and contents).  It is compiled into `bt_version()`; a library whose digest differs from the
+    sources beside it is rebuilt, whatever the file times say."""
+    import hashlib
+    h = hashlib.sha256()
+    files = [os.path.join(CSRC, f) for f in CU_SOURCES] + [os.path.join(CSRC, "common.cuh"),
+                                                         os.path.join(CSRC, "kernels.h"),
+                                                         os.path.join(ROOT, "include", "bt_b200.h")]
+    for f in sorted(files):
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:12]
+
+
+def built_hash(lib_path: str = None) -> str:
+    """The digest a built core library reports (text after 'src:' in bt_version()), or '' if it cannot be loaded."""
+    import ctypes
+    try:
+        lib = ctypes.CDLL(lib_path or CORE_LIB)
+        lib.bt_version.restype = ctypes.c_char_p
+        v = lib.bt_version().decode()
+    except (OSError, AttributeError):
+        return ""
+    return v.split("src:", 1)[1].strip() if "src:" in v else ""
+
+
 def _run(cmd, verbose):
     if verbose:
         print("+", " ".join(cmd), flush=True)
@@ -58,13 +86,18 @@ def build_core(force: bool = False, verbose: bool = False) -> str:
                os.path.join(ROOT, "include", "bt_b200.h")]
     objs = []
     procs = []
+    digest = source_hash()
+    stamp = os.path.join(OBJ_DIR, "source_hash.txt")
+    stale = not os.path.exists(stamp) or open(stamp).read().strip() != digest
     for src in CU_SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(o)
-        if not force and _newer(o, [s] + headers):
+        # encoder.cu carries the digest: it is compiled again whenever any source changed
+        if not force and _newer(o, [s] + headers) and not (stale and src == "encoder.cu"):
             continue
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+              ['-DBT_SOURCE_HASH="%s"' % digest, "-c", s, "-o", o]
         if verbose:
             print("+", " ".join(cmd), flush=True)
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -77,6 +110,8 @@ def build_core(force: bool = False, verbose: bool = False) -> str:
     if force or procs or not _newer(CORE_LIB, objs):
         _run([_nvcc(), "-shared", "-o", CORE_LIB] + objs +
              ["-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"], verbose)
+    with open(stamp, "w") as fh:
+        fh.write(digest + "\n")
     return CORE_LIB
 
 

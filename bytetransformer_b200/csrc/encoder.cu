@@ -51,17 +51,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static EncodeTiledFn lookup_encode_fn() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess)
+    return reinterpret_cast<EncodeTiledFn>(p);
+  return nullptr;
+}
 static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+  static const EncodeTiledFn fn = lookup_encode_fn();  // initialised once, also when threads race here
   return fn;
 }
 
@@ -202,6 +201,19 @@ static int fail_cuda(bt_handle h, cudaError_t e, const char* where) {
   return BT_ERR_CUDA;
 }
 
+// A handle belongs to one device: its status word, its cached tensor maps and (for the static-scratch
+// entry) the scratch array are addresses on that device, while kernels go to whichever device is current.
+static int check_device(bt_handle h) {
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return fail(h, BT_ERR_CUDA, "cudaGetDevice failed");
+  if (cur != h->device) {
+    h->err = "handle belongs to device " + std::to_string(h->device) + ", current device is " + std::to_string(cur);
+    return BT_ERR_INVALID_ARG;
+  }
+  return BT_OK;
+}
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Split-K of the fp32-sum GEMMs is considered up to kSplitKMaxRows allocated rows; the partial sums of
@@ -315,6 +327,7 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   a.batch_idx = batch_idx;
   a.batch = B;
   a.max_len = max_len;
+  a.rows = rows;
   a.head_num = h->cfg.head_num;
   a.hidden = h->hidden;
   a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(h->cfg.size_per_head)) / h->cfg.tao;
@@ -441,6 +454,9 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
   if (!input || !mask || !out || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (input == out) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
   if (n_layers <= 0) return fail(h, BT_ERR_INVALID_ARG, "n_layers must be positive");
+  if (!aligned16(input) || !aligned16(mask) || !aligned16(out))
+    return fail(h, BT_ERR_INVALID_ARG, "input, attr_mask and output must be 16-byte aligned");
+  if ((rc = check_device(h)) != BT_OK) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const size_t rows = static_cast<size_t>(B) * S;
   Workspace need = carve(nullptr, rows, h->hidden, h->ffn, B + 1, rows);
@@ -488,6 +504,8 @@ static int stack_general(bt_handle h, int first_layer, int n_layers, const void*
   if (n_layers <= 0) return fail(h, BT_ERR_INVALID_ARG, "n_layers must be positive");
   if ((reinterpret_cast<uintptr_t>(mask) & 15u) != 0 || (reinterpret_cast<uintptr_t>(attention_bias) & 15u) != 0)
     return fail(h, BT_ERR_INVALID_ARG, "mask and attention_bias must be 16-byte aligned");
+  if (!aligned16(input) || !aligned16(out)) return fail(h, BT_ERR_INVALID_ARG, "input and output must be 16-byte aligned");
+  if ((rc = check_device(h)) != BT_OK) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const size_t rows = static_cast<size_t>(B) * S;
   Workspace need = carve(nullptr, rows, h->hidden, h->ffn, B + 1, rows);
@@ -530,7 +548,12 @@ using namespace bt;
 
 extern "C" {
 
-const char* bt_version(void) { return "bt_b200 0.1 (sm_100a, tcgen05/TMEM/TMA)"; }
+// BT_SOURCE_HASH: digest of the library's sources, passed by the build (bytetransformer_b200/build.py), so
+// that a binary built from other sources than the ones beside it can be told apart.
+#ifndef BT_SOURCE_HASH
+#define BT_SOURCE_HASH "unknown"
+#endif
+const char* bt_version(void) { return "bt_b200 0.2 (sm_100a, tcgen05/TMEM/TMA) src:" BT_SOURCE_HASH; }
 
 int bt_create(const bt_config* cfg, bt_handle* out) {
   if (!cfg || !out) return BT_ERR_INVALID_ARG;
@@ -630,6 +653,10 @@ const char* bt_last_error(bt_handle h) { return h ? h->err.c_str() : "null handl
 
 int bt_device_status(bt_handle h, void* stream, int* status) {
   if (!h || !status) return BT_ERR_INVALID_ARG;
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int v = 0;
   cudaError_t e = cudaMemcpyAsync(&v, h->status, sizeof(int), cudaMemcpyDeviceToHost, s);
@@ -667,6 +694,7 @@ int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void
 int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* pooled, int batch_size, int seq_len,
               int hidden, void* stream) {
   if (!encoder_out || !W || !bias || !pooled || batch_size <= 0 || seq_len <= 0 || hidden <= 0) return BT_ERR_INVALID_ARG;
+  if (!aligned16(encoder_out) || !aligned16(W) || !aligned16(bias) || !aligned16(pooled)) return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_pooler(reinterpret_cast<const __half*>(encoder_out), reinterpret_cast<const __half*>(W),
                                 reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(pooled), batch_size,
                                 seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
@@ -676,6 +704,10 @@ int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* po
 
 int bt_selftest_bounded_wait(bt_handle h, long long max_cycles, int* gave_up_dev, void* stream) {
   if (!h) return BT_ERR_INVALID_ARG;
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   cudaError_t e = launch_bounded_wait_selftest(h->status, max_cycles, gave_up_dev, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(h, e, "self-test launch");
   return BT_OK;
@@ -720,6 +752,7 @@ int bt_layer_forward_padded_static(bt_handle h, int layer, const void* input, co
   size_t need = 0;
   int rc = bt_workspace_bytes(h, batch_size, seq_len, &need);
   if (rc != BT_OK) return rc;
+  if ((rc = check_device(h)) != BT_OK) return rc;  // the scratch address below is only valid on the handle's device
   if (need > static_cast<size_t>(BT_STATIC_SCRATCH_BYTES))
     return fail(h, BT_ERR_WORKSPACE,
                 "batch_size*seq_len needs more scratch than the built-in BT_STATIC_SCRATCH_BYTES; "
@@ -772,6 +805,12 @@ int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, con
   if (batch_size <= 0 || batch_size > 65535 || total_tokens <= 0 || max_len <= 0 || n_layers <= 0)
     return fail(h, BT_ERR_INVALID_ARG, "bad batch_size / total_tokens / max_len / n_layers");
   if (x_packed == out_packed) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
+  if (!aligned16(x_packed) || !aligned16(out_packed))
+    return fail(h, BT_ERR_INVALID_ARG, "x_packed and out_packed must be 16-byte aligned");
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   Workspace need = carve(nullptr, static_cast<size_t>(total_tokens), h->hidden, h->ffn, 0, 0);
   if (workspace_bytes < need.bytes) return fail(h, BT_ERR_WORKSPACE, "workspace smaller than bt_workspace_bytes_packed()");
@@ -794,7 +833,8 @@ int bt_stack_forward_packed(bt_handle h, int n_layers, const void* x_packed, con
 }
 
 int bt_build_offsets(const void* attr_mask, int batch_size, int seq_len, int* batch_idx, int* word_idx, void* stream) {
-  if (!attr_mask || !batch_idx || !word_idx || batch_size <= 0 || seq_len <= 0) return BT_ERR_INVALID_ARG;
+  if (!attr_mask || !batch_idx || !word_idx || batch_size <= 0 || seq_len <= 0 || !aligned16(attr_mask))
+    return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_build_offsets(reinterpret_cast<const __half*>(attr_mask), batch_size, seq_len, batch_idx,
                                        word_idx, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
@@ -804,7 +844,7 @@ int bt_pack_rows(const void* padded, void* packed, const int* batch_idx, const i
                  int seq_len, int hidden, void* stream) {
   (void)word_idx;  // right padding makes each sequence one contiguous run; batch_idx is enough
   if (!padded || !packed || !batch_idx || batch_size <= 0 || batch_size > 65535 || seq_len <= 0 || hidden <= 0 ||
-      hidden % 8 != 0)
+      hidden % 8 != 0 || !aligned16(padded) || !aligned16(packed))
     return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_pack_rows(reinterpret_cast<const __half*>(padded), reinterpret_cast<__half*>(packed),
                                    batch_idx, batch_size, seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
@@ -814,7 +854,7 @@ int bt_pack_rows(const void* padded, void* packed, const int* batch_idx, const i
 int bt_restore_rows(const void* packed, void* padded, const int* batch_idx, int batch_size, int seq_len, int hidden,
                     void* stream) {
   if (!packed || !padded || !batch_idx || batch_size <= 0 || batch_size > 65535 || seq_len <= 0 || hidden <= 0 ||
-      hidden % 8 != 0)
+      hidden % 8 != 0 || !aligned16(packed) || !aligned16(padded))
     return BT_ERR_INVALID_ARG;
   cudaError_t e = launch_restore_rows(reinterpret_cast<const __half*>(packed), reinterpret_cast<__half*>(padded),
                                       batch_idx, batch_size, seq_len, hidden, reinterpret_cast<cudaStream_t>(stream));
@@ -830,6 +870,10 @@ int bt_gemm(bt_handle h, const void* A, const void* W, void* out, const void* bi
   if (epilogue < BT_EPI_NONE || epilogue > BT_EPI_BIAS_RESIDUAL_F32OUT) return fail(h, BT_ERR_INVALID_ARG, "bad epilogue");
   if (epilogue != BT_EPI_NONE && !bias) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs bias");
   if ((epilogue == BT_EPI_BIAS_RESIDUAL || epilogue == BT_EPI_BIAS_RESIDUAL_F32OUT) && !residual) return fail(h, BT_ERR_INVALID_ARG, "epilogue needs residual");
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   pdl_next_launch_plain();  // W may come straight from the caller's kernel before: see kernels.h
   return run_gemm(h, BT_PROF_GEMM_OTHER, reinterpret_cast<const __half*>(A), W, reinterpret_cast<__half*>(out), bias,
                   reinterpret_cast<const __half*>(residual), m_dev, m_rows, N, K, epilogue, gelu_kind,
@@ -844,6 +888,10 @@ int bt_gemm_layernorm(bt_handle h, const void* A, const void* W, const void* bia
     return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (m_rows <= 0 || N <= 0 || K <= 0 || N % 256 != 0 || N > 1024 || K % 64 != 0)
     return fail(h, BT_ERR_INVALID_ARG, "bt_gemm_layernorm needs m_rows > 0, N % 256 == 0, N <= 1024, K % 64 == 0");
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   // scratch: [m_rows][N/128] tagged partials of 16 bytes, zeroed here; this launch is number 1 on it
   cudaError_t me = cudaMemsetAsync(scratch_f32, 0, static_cast<size_t>(m_rows) * (N / 128) * 16,
                                    reinterpret_cast<cudaStream_t>(stream));
@@ -877,6 +925,11 @@ int bt_attention(bt_handle h, const void* qkv, void* ctx, const int* batch_idx, 
   if (!h) return BT_ERR_INVALID_ARG;
   if (!qkv || !ctx || !batch_idx || batch_size <= 0 || batch_size > 65535 || max_len <= 0 || rows_allocated <= 0)
     return fail(h, BT_ERR_INVALID_ARG, "bad argument to bt_attention");
+  if (!aligned16(qkv) || !aligned16(ctx)) return fail(h, BT_ERR_INVALID_ARG, "qkv and ctx must be 16-byte aligned");
+  {
+    const int rc = check_device(h);
+    if (rc != BT_OK) return rc;
+  }
   return run_mha(h, reinterpret_cast<const __half*>(qkv), reinterpret_cast<__half*>(ctx), batch_idx, batch_size,
                  max_len, rows_allocated, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -108,6 +108,7 @@ struct MhaLaunch {
   const int* batch_idx;
   int batch;
   int max_len;         // upper bound of every sequence length
+  int rows = 0;        // rows allocated in qkv / ctx
   int head_num;
   int hidden;          // H = head_num * 64
   float scale_log2e;   // log2(e) / sqrt(64) / tao

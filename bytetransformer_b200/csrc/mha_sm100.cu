@@ -3,14 +3,14 @@
 // Stands in for the reference's packed attention kernels
 // (bytetransformer/src/attention_fused.cu:295-414 for short sequences,
 // bytetransformer/src/attention_fused_long.cu:171-312 and the grouped-GEMM path
-// of bytetransformer/src/cutlass_attention.cu:150-210 for long ones).  One
-// templated kernel, two instantiations:
-//   TILES = 1  128 query rows per CTA, 192 threads, two CTAs per SM overlap each
-//              other's phases (the default: fastest at every length 64..1024);
-//   TILES = 2  256 query rows per CTA as two 128-row tiles that ping-pong on the
-//              tensor core, 320 threads, one CTA per SM (selectable).
-// Both run an online softmax over 128-key tiles, so no S x S logits ever reach
-// HBM and any length works.
+// of bytetransformer/src/cutlass_attention.cu:150-210 for long ones).  Two kernels:
+//   mha_fwd_kernel         one CTA per (128 query rows, head, sequence), 192 threads, two CTAs per SM.
+//                          Used while the longest sequence fits two key tiles' worth of work per item
+//                          (max_len <= 192) and for the general-mask variant.
+//   mha_persistent_kernel  persistent CTAs walking a static list of (sequence, query tile, head) items,
+//                          256 threads, two CTAs per SM; everything longer.
+// Both run an online softmax over 128-key tiles, so no S x S logits ever reach HBM and any length
+// works.
 //
 // Input is the packed QKV activation [rows, 3H] with bias already added by the
 // QKV GEMM epilogue; head h of Q/K/V is the 64-column slice at h*64 / H+h*64 /
@@ -19,26 +19,13 @@
 // no counterpart here).  Only `batch_idx` tells where sequences start and end;
 // as in the reference's packed kernels the mask tensor is not consulted again.
 //
-// Roles: warp 0 TMA loads, warp 1 tcgen05.mma issue (+ tensor-memory allocation),
-// then one warpgroup of 4 softmax warps per query tile (one query row per thread).
-//   S = Q K^T      128x128x64, both operands from shared memory -> tensor memory,
-//                  128 fp32 columns per tile
-//   P = 2^(c*S-m)  fp16 pairs written back into tensor memory over the upper half of
-//                  S (columns 64..127, key k in cell 64 + k/2) with tcgen05.st; the
-//                  softmax walks S from the last 32-column chunk to the first, so a
-//                  cell is only overwritten after it was read
+// Common to both kernels: one warp issues TMA loads, one thread issues the tcgen05 MMAs (and its warp
+// owns the tensor-memory allocation), four softmax warps own one query row per thread.
+//   S = Q K^T      128x128x64, both operands from shared memory -> tensor memory, 128 fp32 columns
+//   P = 2^(c*S-m)  fp16 pairs written to tensor memory with tcgen05.st
 //   O += P V       128x64x128 with the A operand (P) read from tensor memory and V
 //                  consumed MN-major from shared memory exactly as it lies in the QKV
-//                  buffer -> 64 fp32 columns per tile
-// The persistent kernel for long sequences (further down) uses the free 64 columns of its 256
-// for P instead (S 0..127, O 128..191, P 192..255): S stays intact, so the next S = Q K^T is
-// issued before O += P V, and every key tile is read from tensor memory only once (the
-// probabilities are formed with the reference of the earlier tiles and the tile is redone only
-// when the row maximum jumped past the threshold).  The softmax is a chain of dependent
-// latencies (tcgen05.ld, wait, arithmetic, tcgen05.st, barrier) run by two warps per scheduler
-// (S, O and P take 256 of the 512 tensor-memory columns, so two CTAs fit on an SM), not a
-// bandwidth problem: a read-only loop (tmem_probe.cu) gets 120-370 B/clk per SM out of tensor memory,
-// the softmax consumes ~48.  Touching every score once instead of twice shortened that chain.
+//                  buffer -> 64 fp32 columns
 // P never touches shared memory.  O stays in tensor memory across key tiles.  The
 // exponent reference m only moves when the running maximum grows by more than a
 // threshold (then the O row is rescaled in tensor memory); otherwise P simply grows
@@ -47,6 +34,18 @@
 // Keys beyond the sequence end are masked by selection (never by arithmetic on
 // the fetched values) and their V rows are zeroed in shared memory, so rows of
 // neighbouring sequences or never-written workspace cannot leak in.
+// Offsets that do not describe rows inside the allocation (negative, decreasing, longer than max_len,
+// past the last row) make the sequence a no-op and set kStatusBadOffsets: nothing outside the
+// buffers is read or written.
+//
+// What the measurements on B200 say about the softmax (it, not the tensor core, bounds both kernels:
+// the MMAs of a 128x128 tile take ~540 clocks when two CTAs interleave them, a tile takes ~1900):
+// the special-function unit delivers one warp-wide ex2 per 4 clocks and scheduler, but a single warp
+// only reaches one per ~10 clocks (two warps 6.9, three 4.9), and tensor memory holds S, O and P for
+// two CTAs, i.e. two softmax warps per scheduler.  Halving the exponential work (ex2.f16x2 runs at
+// half rate, so it gains nothing; a polynomial on the FMA pipe for a quarter of the elements: 5 %
+// slower), 256-row ping-pong tiles and two threads per row with an exchange through shared memory
+// (25 % slower) were measured and dropped.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -54,24 +53,25 @@ namespace bt {
 
 namespace {
 
+long long g_dbg_force_kernel = 0;  // 0 = by shape, 1 = one CTA per item, 3 = persistent
+
 constexpr int kQRows = 128;
 constexpr int kKvRows = 128;
 constexpr int kHeadDim = 64;
 constexpr int kTileBytes = 128 * kHeadDim * 2;  // 16 KiB: Q, K or V tile
 
-template <int TILES>
+// One CTA per item: shared-memory and tensor-memory layout.
 struct MhaCfg {
   static constexpr int kStages = 3;
-  static constexpr int kThreads = 64 + 128 * TILES;
+  static constexpr int kThreads = 192;
   static constexpr int kSmemQ = 0;
-  static constexpr int kSmemK = kSmemQ + TILES * kTileBytes;
+  static constexpr int kSmemK = kSmemQ + kTileBytes;
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
   static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
   static constexpr int kSmemBytes = kSmemBar + 256;
-  static constexpr int kTmemCols = TILES == 2 ? 512 : 256;
-  static constexpr uint32_t kTmemO = TILES * 128;  // S tiles first, then O tiles
-  static constexpr uint32_t kTmemPOff = 64;        // P aliases columns 64..127 of its S tile
-  static constexpr int kMinBlocks = TILES == 2 ? 1 : 2;
+  static constexpr int kTmemCols = 256;
+  static constexpr uint32_t kTmemO = 128;    // the S tile first, then the O tile
+  static constexpr uint32_t kTmemPOff = 64;  // P aliases columns 64..127 of S
 };
 
 struct MhaArgs {
@@ -80,7 +80,8 @@ struct MhaArgs {
   int hidden;
   float scale_log2e;
   int* status;
-  long long* timing;  // diagnostics: per CTA and key-tile step, clock64 stamps (null = off)
+  int rows;     // rows allocated in qkv / ctx
+  int max_len;  // upper bound of every sequence length
   // General-mask variant (GENERAL = true): every sequence has `gen_seq_len` rows; the score of
   // (query q, key k) gets  attn_bias[head, q, k] + (1 - mask[b, q, k]) * -10000  added after scaling,
   // the rule of the reference's unfused softmax (bytetransformer/include/softmax.h:41-45).
@@ -94,12 +95,6 @@ struct MhaArgs {
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// two exponentials per special-function op, fp16 in / fp16 out
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
   return y;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -158,52 +153,30 @@ __device__ __forceinline__ float tile_row_max(uint32_t t_s, int kv_valid) {
   return fmaxf(mx, chunk_max<MASKED>(vb, 96, kv_valid));
 }
 
-// One 32-column chunk of S -> 16 cells of fp16 pairs, plus this chunk's row sum.
-//   EXP16 = false: 2^x in fp32 (one special-function op per key), fp32 row sum.
-//   EXP16 = true : x is rounded to fp16 first and two exponentials share one op; the row
-//                  sum is formed from the fp16 results (pairwise tree, then fp32).
-template <bool MASKED, bool EXP16>
+// One 32-column chunk of S -> 16 cells of fp16 pairs, plus this chunk's row sum (2^x in fp32, one
+// special-function op per key, fp32 row sum).
+template <bool MASKED>
 __device__ __forceinline__ float chunk_probs(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
                                              uint32_t (&out)[16]) {
-  if (EXP16) {
-    __half2 acc[4];
+  float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float x0 = fmaf(__uint_as_float(v[2 * i]), c, -m_ref);
-      float x1 = fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref);
-      if (MASKED) {
-        // 2^-inf = 0 for keys that do not exist
-        x0 = (cbase + 2 * i < kv_valid) ? x0 : -INFINITY;
-        x1 = (cbase + 2 * i + 1 < kv_valid) ? x1 : -INFINITY;
-      }
-      out[i] = ex2_f16x2(pack_half2(x0, x1));
-      const __half2 h = *reinterpret_cast<const __half2*>(&out[i]);
-      acc[i & 3] = (i < 4) ? h : __hadd2(acc[i & 3], h);
+  for (int i = 0; i < 16; ++i) {
+    float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -m_ref));
+    float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref));
+    if (MASKED) {
+      p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
+      p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
     }
-    const float2 s01 = __half22float2(__hadd2(acc[0], acc[1]));
-    const float2 s23 = __half22float2(__hadd2(acc[2], acc[3]));
-    return (s01.x + s01.y) + (s23.x + s23.y);
-  } else {
-    float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -m_ref));
-      float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref));
-      if (MASKED) {
-        p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
-        p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
-      }
-      l0 += p0;
-      l1 += p1;
-      out[i] = pack_half2(p0, p1);
-    }
-    return l0 + l1;
+    l0 += p0;
+    l1 += p1;
+    out[i] = pack_half2(p0, p1);
   }
+  return l0 + l1;
 }
 
 // Second pass over one S tile, from the last chunk to the first; P chunk c lands in cells
 // [64 + 16c, 64 + 16c + 16) of the same tile, which lie in chunks that were already read.
-template <bool MASKED, bool EXP16>
+template <bool MASKED>
 __device__ __forceinline__ float tile_probs(uint32_t t_s, int kv_valid, float c, float m_ref) {
   const uint32_t t_p = t_s + 64;
   uint32_t va[32], vb[32], pk[16];
@@ -211,18 +184,18 @@ __device__ __forceinline__ float tile_probs(uint32_t t_s, int kv_valid, float c,
   tmem_ld_32x32(t_s + 96, va);
   tmem_ld_wait();
   tmem_ld_32x32(t_s + 64, vb);  // in flight while chunk 3 is processed
-  l += chunk_probs<MASKED, EXP16>(va, 96, kv_valid, c, m_ref, pk);
+  l += chunk_probs<MASKED>(va, 96, kv_valid, c, m_ref, pk);
   tmem_ld_wait();               // chunk 2 is in registers: its cells may now be overwritten
   tmem_st_32x16(t_p + 48, pk);
   tmem_ld_32x32(t_s + 32, va);
-  l += chunk_probs<MASKED, EXP16>(vb, 64, kv_valid, c, m_ref, pk);
+  l += chunk_probs<MASKED>(vb, 64, kv_valid, c, m_ref, pk);
   tmem_ld_wait();
   tmem_st_32x16(t_p + 32, pk);
   tmem_ld_32x32(t_s, vb);
-  l += chunk_probs<MASKED, EXP16>(va, 32, kv_valid, c, m_ref, pk);
+  l += chunk_probs<MASKED>(va, 32, kv_valid, c, m_ref, pk);
   tmem_ld_wait();
   tmem_st_32x16(t_p + 16, pk);
-  l += chunk_probs<MASKED, EXP16>(vb, 0, kv_valid, c, m_ref, pk);
+  l += chunk_probs<MASKED>(vb, 0, kv_valid, c, m_ref, pk);
   tmem_st_32x16(t_p, pk);
   tmem_st_wait();
   return l;
@@ -276,73 +249,14 @@ __device__ __forceinline__ void tile_add_mask_bias(uint32_t t_s, const __half* m
   tmem_st_wait();
 }
 
-// One 32-column chunk with the exponent reference of the EARLIER key tiles: probabilities, their
-// sum, and the largest exponent seen (to tell afterwards whether the reference was good enough).
-template <bool MASKED>
-__device__ __forceinline__ float chunk_probs_track(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
-                                                   uint32_t (&out)[16], float& xmax) {
-  float l0 = 0.f, l1 = 0.f, x0m = xmax, x1m = xmax;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    float x0 = fmaf(__uint_as_float(v[2 * i]), c, -m_ref);
-    float x1 = fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref);
-    if (MASKED) {
-      x0 = (cbase + 2 * i < kv_valid) ? x0 : -INFINITY;
-      x1 = (cbase + 2 * i + 1 < kv_valid) ? x1 : -INFINITY;
-    }
-    x0m = fmaxf(x0m, x0);
-    x1m = fmaxf(x1m, x1);
-    const float p0 = ex2_approx(x0);
-    const float p1 = ex2_approx(x1);
-    l0 += p0;
-    l1 += p1;
-    out[i] = pack_half2(p0, p1);
-  }
-  xmax = fmaxf(x0m, x1m);
-  return l0 + l1;
-}
-
-// Same pass with P in its own tensor-memory columns (`t_p`, 64 cells): the chunk order is free and
-// nothing of S is overwritten, so the next S = Q K^T may be issued as soon as this pass has read S.
-template <bool MASKED>
-__device__ __forceinline__ float tile_probs_sep(uint32_t t_s, uint32_t t_p, int kv_valid, float c, float m_ref) {
-  uint32_t va[32], vb[32], pk[16];
-  float l = 0.f;
-  tmem_ld_32x32(t_s, va);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 32, vb);
-  l += chunk_probs<MASKED, false>(va, 0, kv_valid, c, m_ref, pk);
-  tmem_st_32x16(t_p, pk);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 64, va);
-  l += chunk_probs<MASKED, false>(vb, 32, kv_valid, c, m_ref, pk);
-  tmem_st_32x16(t_p + 16, pk);
-  tmem_ld_wait();
-  tmem_ld_32x32(t_s + 96, vb);
-  l += chunk_probs<MASKED, false>(va, 64, kv_valid, c, m_ref, pk);
-  tmem_st_32x16(t_p + 32, pk);
-  tmem_ld_wait();
-  l += chunk_probs<MASKED, false>(vb, 96, kv_valid, c, m_ref, pk);
-  tmem_st_32x16(t_p + 48, pk);
-  tmem_st_wait();
-  return l;
-}
-
-__device__ __forceinline__ void stamp(long long* timing, int j, int slot) {
-  if (timing != nullptr && j < 8) {
-    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-    if (cta < 4096) timing[(static_cast<size_t>(cta) * 8 + j) * 8 + slot] = clock64();
-  }
-}
-
-template <int TILES, bool EXP16, bool GENERAL = false>
-__global__ void __launch_bounds__(MhaCfg<TILES>::kThreads, MhaCfg<TILES>::kMinBlocks)
+template <bool GENERAL>
+__global__ void __launch_bounds__(MhaCfg::kThreads, 2)
 mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
-  using Cfg = MhaCfg<TILES>;
+  using Cfg = MhaCfg;
+  constexpr int TILES = 1;  // query tiles per CTA (the loops over `t` below have one trip)
   constexpr int kStages = Cfg::kStages;
-  // With fp16 exponents the reference may lag the running maximum by at most 2^1 (keeps the
-  // rounding of the exponent small); with fp32 exponents by 2^8.
-  constexpr float kRescaleThreshold = EXP16 ? 1.0f : 8.0f;
+  // the exponent reference may lag the running maximum by at most 2^8
+  constexpr float kRescaleThreshold = 8.0f;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   pdl_launch_dependents();
@@ -352,6 +266,11 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
   const int seq_start = __ldg(args.batch_idx + b);
   const int L = __ldg(args.batch_idx + b + 1) - seq_start;
   const int q0 = blockIdx.x * (kQRows * TILES);
+  if (seq_start < 0 || L < 0 || L > args.max_len || seq_start > args.rows - L) {
+    // offsets that do not describe rows of the allocation: nothing is read or written for this sequence
+    if (threadIdx.x == 0 && args.status != nullptr) atomicCAS(args.status, 0, kStatusBadOffsets);
+    return;
+  }
   if (q0 >= L) return;  // whole CTA leaves before any barrier / allocation exists
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0 && args.status != nullptr) atomicCAS(args.status, 0, kStatusMhaLoadTimeout + 0x10);
@@ -478,7 +397,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         // ---- tile 0: O0 += P0 V(j), then S0(j+1).  The MMAs of one thread execute in issue
         // order, so S0(j+1) cannot overwrite P0(j) (same columns) before PV0(j) has read it.
         if (!mbar_wait_bounded(&p_full[0], jpar, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        stamp(args.timing, j, 4);
         if (!mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
         tc_fence_after();
         issue_pv(0, st, j > 0);
@@ -495,7 +413,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
         }
         umma_commit(&kv_empty[st]);  // every MMA that reads K/V stage `st` has been issued
         if (n_tiles == 2 && more) issue_s(1, st_n);
-        stamp(args.timing, j, 5);
         st = st_n;
         ph = ph_n;
       }
@@ -525,7 +442,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           break;
         }
         tc_fence_after();
-        if (warp == 2 && lane == 0) stamp(args.timing, j, 0);
         if (GENERAL) {
           const int S = args.gen_seq_len;
           const int q_row = q0 + t * kQRows + r;
@@ -558,10 +474,9 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
             m_ref = m_new;
           }
         }
-        if (warp == 2 && lane == 0) stamp(args.timing, j, 1);
         // pass 2: probabilities -> fp16 pairs -> tensor memory (over S), row sum
-        l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
-                           : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
+        l_run += full_tile ? tile_probs<false>(t_s, kv_valid, c, m_ref)
+                           : tile_probs<true>(t_s, kv_valid, c, m_ref);
         if (!full_tile && t == 0) {
           // tail tile: blank the V rows of keys that do not belong to this sequence
           // (tile 0's PV is issued before tile 1's, so tile 0's warpgroup does it for both)
@@ -576,7 +491,6 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           }
           fence_proxy_async_smem();
         }
-        if (warp == 2 && lane == 0) stamp(args.timing, j, 2);
         tc_fence_before();
         mbar_arrive(&p_full[t]);
         if (++stage == kStages) {
@@ -624,13 +538,31 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Persistent variant: each CTA (192 threads, two per SM) walks a static list of work items
-// (sequence, 128-row query tile, head), item n going to CTA n mod gridDim.x.  Barriers,
-// tensor memory and the launch are paid once per CTA instead of once per item, and the
-// loader runs ahead: the next item's Q/K/V tiles are requested while the current item's last
-// key tiles are still being processed.  Per item the MMAs are those of mha_fwd_kernel<1>; the
-// softmax follows the PSEP / ONEPASS scheme described at the kernel (default) or, selectable, the
-// two-pass scheme of mha_fwd_kernel<1> (same tile_row_max / tile_probs).
+// Persistent kernel: each CTA (256 threads, two per SM) walks a static list of work items
+// (sequence, 128-row query tile, head).  Barriers, tensor memory and the launch are paid once per
+// CTA instead of once per item, and the loader runs ahead: the next item's Q/K/V tiles are requested
+// while the current item's last key tiles are still being processed.
+//
+// Tensor memory: S columns 0..127, O 128..191, P 192..255 (P has its own columns, so S is never
+// overwritten by P).  A softmax thread reads its whole row of S (128 fp32 values) into registers in one
+// go and at once hands S back (`s_free`): the tensor core forms S(j+1) = Q K(j+1)^T while the
+// exponentials of tile j are still being computed, so the MMA round trip (commit, issue, four MMAs,
+// commit) is off the softmax warps' critical path.  With the row in registers the row maximum is exact
+// before the first exponential, and all 128 exponentials are formed before P is touched, by which time
+// the P V MMAs of the previous key tile (the owners of P and O until they retire) are long done.
+// From the first load of S to the last store of P the code is one straight line: keys that do not
+// exist in a sequence's last tile are set to -inf beforehand (probability 0) rather than skipped,
+// because a branch per 32-key chunk cost more (the scheduler cannot overlap across it) than the
+// exponentials it saved.
+//
+// Warps 0-3 softmax (one warpgroup, 216 registers each after setmaxnreg), warp 4 loads, warp 5 issues
+// the MMAs, warps 6-7 only give their registers away (setmaxnreg works on whole warpgroups).  The two
+// single-thread roles sleep between polls of a barrier so that they leave the issue slots of the
+// schedulers they share with softmax warps alone.
+//
+// Items go to the CTAs in snake order (round k: item k*G + c for even k, k*G + G-1-c for odd k, G CTAs):
+// with sequences sorted by length (longest first), which is how callers batch them, the items of a round
+// get cheaper from first to last, and the snake evens out the per-CTA sums.
 // ------------------------------------------------------------------------------------------
 struct MhaPersistentArgs {
   __half* ctx;
@@ -640,21 +572,30 @@ struct MhaPersistentArgs {
   int hidden;
   float scale_log2e;
   int* status;
+  int rows;     // rows allocated in qkv / ctx
+  int max_len;  // upper bound of every sequence length
 };
 
-// Finds item n = (sequence b, query tile qt, head h); items are numbered sequence by
-// sequence, inside a sequence query tile by query tile, heads fastest.  `cur_b` / `cur_first`
-// is the caller's cursor (first item index of sequence cur_b); n never decreases.
-__device__ __forceinline__ bool decode_item(const int* __restrict__ batch_idx, int B, int heads, int n, int& cur_b,
-                                            int& cur_first, int& seq_start, int& L, int& qt, int& h) {
-  while (cur_b < B) {
-    seq_start = __ldg(batch_idx + cur_b);
-    L = __ldg(batch_idx + cur_b + 1) - seq_start;
-    const int items = ((L + kQRows - 1) / kQRows) * heads;
+// Finds item n = (sequence b, query tile qt, head h); items are numbered sequence by sequence, inside
+// a sequence query tile by query tile, heads fastest.  `cur_b` / `cur_first` is the caller's cursor
+// (first item index of sequence cur_b); n never decreases.  A sequence whose offsets are not
+// 0 <= start, 0 <= L <= max_len, start + L <= rows is left out (it yields no items, so nothing is read
+// or written outside the buffers) and, when `report` is set (one thread per CTA), kStatusBadOffsets is
+// recorded.
+__device__ __forceinline__ bool decode_item(const MhaPersistentArgs& a, int n, int& cur_b, int& cur_first,
+                                            int& seq_start, int& L, int& qt, int& h, bool report) {
+  while (cur_b < a.batch) {
+    seq_start = __ldg(a.batch_idx + cur_b);
+    L = __ldg(a.batch_idx + cur_b + 1) - seq_start;
+    if (seq_start < 0 || L < 0 || L > a.max_len || seq_start > a.rows - L) {
+      if (report && a.status != nullptr) atomicCAS(a.status, 0, kStatusBadOffsets);
+      L = 0;
+    }
+    const int items = ((L + kQRows - 1) / kQRows) * a.heads;
     if (n < cur_first + items) {
       const int r = n - cur_first;
-      qt = r / heads;
-      h = r - qt * heads;
+      qt = r / a.heads;
+      h = r - qt * a.heads;
       return true;
     }
     cur_first += items;
@@ -662,26 +603,78 @@ __device__ __forceinline__ bool decode_item(const int* __restrict__ batch_idx, i
   }
   return false;
 }
+__device__ __forceinline__ int snake_item(int round, int cta, int ctas) {
+  return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
+}
 
-// PSEP = true: P lives in its own 64 tensor-memory columns instead of over the upper half of S.  The
-// MMA warp can then issue S(j+1) = Q K(j+1)^T BEFORE O += P(j) V(j): the next softmax starts after
-// four MMAs instead of twelve, and P V runs in its shadow.  The softmax waits for `pv_done` of the
-// previous key tile before it rescales O or overwrites P.
-// ONEPASS (needs PSEP): key tiles after the first are read from tensor memory ONCE: probabilities are
-// formed with the reference of the earlier tiles while the largest exponent is tracked; only when that
-// exceeds the threshold (the row maximum jumped by more than 2^8) is the tile redone with a new
-// reference, which is possible because S is still intact.  The second read of every score (load, wait,
-// arithmetic) was the longest avoidable piece of the softmax's latency chain.
-template <bool EXP16, bool PSEP = false, bool ONEPASS = false>
-__global__ void __launch_bounds__(192, 2)
+// tcgen05.ld 32x32b.x32 into elements [B, B + 32) of a 128-element register array (no address of the array
+// is formed, so it stays in registers).
+template <int B>
+__device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t (&r)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[B + 0]), "=r"(r[B + 1]), "=r"(r[B + 2]), "=r"(r[B + 3]), "=r"(r[B + 4]), "=r"(r[B + 5]), "=r"(r[B + 6]),
+        "=r"(r[B + 7]), "=r"(r[B + 8]), "=r"(r[B + 9]), "=r"(r[B + 10]), "=r"(r[B + 11]), "=r"(r[B + 12]), "=r"(r[B + 13]),
+        "=r"(r[B + 14]), "=r"(r[B + 15]), "=r"(r[B + 16]), "=r"(r[B + 17]), "=r"(r[B + 18]), "=r"(r[B + 19]), "=r"(r[B + 20]),
+        "=r"(r[B + 21]), "=r"(r[B + 22]), "=r"(r[B + 23]), "=r"(r[B + 24]), "=r"(r[B + 25]), "=r"(r[B + 26]), "=r"(r[B + 27]),
+        "=r"(r[B + 28]), "=r"(r[B + 29]), "=r"(r[B + 30]), "=r"(r[B + 31])
+      : "r"(taddr)
+      : "memory");
+}
+template <int B>
+__device__ __forceinline__ void tmem_st_32x16_at(uint32_t taddr, const uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[B + 0]), "r"(r[B + 1]), "r"(r[B + 2]), "r"(r[B + 3]), "r"(r[B + 4]), "r"(r[B + 5]), "r"(r[B + 6]), "r"(r[B + 7]),
+      "r"(r[B + 8]), "r"(r[B + 9]), "r"(r[B + 10]), "r"(r[B + 11]), "r"(r[B + 12]), "r"(r[B + 13]), "r"(r[B + 14]),
+      "r"(r[B + 15])
+      : "memory");
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Bounded wait for the single-thread roles (loader, MMA issuer): between polls the thread sleeps, so that
+// its polling does not take issue slots from the softmax warp that shares its scheduler.
+__device__ __forceinline__ bool mbar_wait_role(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    __nanosleep(40);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 63u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > (1ll << 31)) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+constexpr int kPersistentThreads = 256;
+constexpr int kPersistentSmemBytes = 7 * kTileBytes + 256;
+
+__global__ void __launch_bounds__(kPersistentThreads, 2)
 mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {
   constexpr int kStages = 3;
   constexpr int kSmemQ = 0;
   constexpr int kSmemK = kSmemQ + kTileBytes;
   constexpr int kSmemV = kSmemK + kStages * kTileBytes;
   constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-  constexpr uint32_t kTmemS = 0, kTmemP = PSEP ? 192 : 64, kTmemO = 128;
-  constexpr float kRescaleThreshold = EXP16 ? 1.0f : 8.0f;
+  constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemP = 192;
+  constexpr float kRescaleThreshold = 8.0f;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   pdl_launch_dependents();
@@ -691,11 +684,12 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   uint64_t* k_full = bars + 2;                  // [kStages]
   uint64_t* v_full = bars + 2 + kStages;        // [kStages]
   uint64_t* kv_empty = bars + 2 + 2 * kStages;  // [kStages]
-  uint64_t* s_full = bars + 2 + 3 * kStages;
-  uint64_t* p_full = bars + 3 + 3 * kStages;
-  uint64_t* o_done = bars + 4 + 3 * kStages;
-  uint64_t* pv_done = bars + 5 + 3 * kStages;   // PSEP: the P V MMAs of a key tile have retired
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 3 * kStages);
+  uint64_t* s_full = bars + 2 + 3 * kStages;    // S(j) is in tensor memory
+  uint64_t* s_free = bars + 3 + 3 * kStages;    // the softmax warps hold S(j) in registers (4 arrivals)
+  uint64_t* p_full = bars + 4 + 3 * kStages;    // P(j) is in tensor memory, V rows blanked (4 arrivals)
+  uint64_t* pv_done = bars + 5 + 3 * kStages;   // O += P(j) V(j) has retired
+  uint64_t* o_done = bars + 6 + 3 * kStages;    // the item's last P V has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 3 * kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -711,15 +705,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(o_done, 1);
+    mbar_init(s_free, 4);
+    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
+    mbar_init(o_done, 1);
     *abort_flag = smem_ok ? 0 : 1;
     fence_mbar_init();
     if (!smem_ok && args.status != nullptr) atomicCAS(args.status, 0, kStatusMhaLoadTimeout + 0x10);
     tma_prefetch_desc(&tm_qkv);
   }
-  if (warp == 1) {
+  if (warp == 5) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
@@ -729,262 +724,211 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();  // batch_idx and the QKV buffer come from earlier kernels
 
-  const int B = args.batch, heads = args.heads;
+  const int G = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   int cur_b = 0, cur_first = 0, seq_start = 0, L = 0, qt = 0, head = 0;
 
-  if (!smem_ok) {
-    // fall through to the teardown
-  } else if (warp == 0) {
-    // ------------------------------------------------------------------ loads
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t item = 0;
-      bool ok = true;
-      for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
-           n += gridDim.x, ++item) {
-        const int n_kv = (L + kKvRows - 1) / kKvRows;
-        if (!mbar_wait_bounded(q_empty, (item & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) break;
-        mbar_arrive_expect_tx(q_full, kTileBytes);
-        tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, head * kHeadDim, seq_start + qt * kQRows);
-        for (int j = 0; j < n_kv; ++j) {
-          if (!mbar_wait_bounded(&kv_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
-            ok = false;
+  if (warp >= 4) {
+    setmaxnreg_dec<40>();
+    if (!smem_ok) {
+      // fall through to the teardown
+    } else if (warp == 4) {
+      // ------------------------------------------------------------------ loads
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, true);
+             ++round) {
+          const int n_kv = (L + kKvRows - 1) / kKvRows;
+          if (!mbar_wait_role(q_empty, (static_cast<uint32_t>(round) & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout))
             break;
-          }
-          const int row = seq_start + j * kKvRows;
-          mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
-          tma_load_2d(smem + kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], args.hidden + head * kHeadDim, row);
-          mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
-          tma_load_2d(smem + kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], 2 * args.hidden + head * kHeadDim,
-                      row);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+          mbar_arrive_expect_tx(q_full, kTileBytes);
+          tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, head * kHeadDim, seq_start + qt * kQRows);
+          for (int j = 0; j < n_kv; ++j) {
+            if (!mbar_wait_role(&kv_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
+              ok = false;
+              break;
+            }
+            const int row = seq_start + j * kKvRows;
+            mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
+            tma_load_2d(smem + kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], args.hidden + head * kHeadDim, row);
+            mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
+            tma_load_2d(smem + kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], 2 * args.hidden + head * kHeadDim,
+                        row);
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
-    }
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issue
-    if (lane == 0) {
-      constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
-      constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
-      constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
-      constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
-      const uint32_t s_q = smem_u32(smem + kSmemQ);
-      const uint32_t s_k = smem_u32(smem + kSmemK);
-      const uint32_t s_v = smem_u32(smem + kSmemV);
-      auto issue_s = [&](int stage) {
-        const uint32_t sk = s_k + stage * kTileBytes;
+    } else if (warp == 5) {
+      // -------------------------------------------------------------- MMA issue
+      if (lane == 0) {
+        constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
+        constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
+        constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
+        constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
+        const uint32_t s_q = smem_u32(smem + kSmemQ);
+        const uint32_t s_k = smem_u32(smem + kSmemK);
+        const uint32_t s_v = smem_u32(smem + kSmemV);
+        auto issue_s = [&](int stage) {
+          const uint32_t sk = s_k + stage * kTileBytes;
 #pragma unroll
-        for (int k = 0; k < kHeadDim / 16; ++k)
-          umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
-                      k != 0 ? 1u : 0u);
-        umma_commit(s_full);
-      };
-      int st = 0;
-      uint32_t ph = 0;
-      uint32_t step = 0, item = 0;
-      bool ok = true;
-      for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
-           n += gridDim.x, ++item) {
-        const int n_kv = (L + kKvRows - 1) / kKvRows;
-        if (!mbar_wait_bounded(q_full, item & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        if (!mbar_wait_bounded(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-        tc_fence_after();
-        issue_s(st);
-        if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
-        for (int j = 0; j < n_kv; ++j, ++step) {
-          const int st_n = (st + 1 == kStages) ? 0 : st + 1;
-          const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
-          // P of this step is ready; it also tells that the softmax warps have finished the
-          // previous item's O read-out, so the first PV of an item may overwrite O.
-          if (!mbar_wait_bounded(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          if (PSEP && j + 1 < n_kv) {
-            // the softmax has read S(j) completely and P(j) sits elsewhere: S(j+1) goes first
-            if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            issue_s(st_n);
-            if (j + 2 == n_kv) umma_commit(q_empty);
-          }
-          if (!mbar_wait_bounded(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
-            ok = false;
-            break;
-          }
+          for (int k = 0; k < kHeadDim / 16; ++k)
+            umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
+                        k != 0 ? 1u : 0u);
+          umma_commit(s_full);
+        };
+        int st = 0;
+        uint32_t ph = 0;
+        uint32_t step = 0;
+        bool ok = true;
+        for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+             ++round) {
+          const int n_kv = (L + kKvRows - 1) / kKvRows;
+          // S(0) overwrites the S columns: the softmax warps must hold the previous item's last S in registers
+          if (step > 0 && !mbar_wait_role(s_free, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+          if (!mbar_wait_role(q_full, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
+          if (!mbar_wait_role(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
           tc_fence_after();
-          const uint32_t sv = s_v + st * kTileBytes;
-          // only the 16-key steps that hold keys of this sequence (in the last tile the softmax leaves
-          // the P columns of 32-key chunks without any key unwritten)
-          const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
-#pragma unroll
-          for (int kk = 0; kk < kKvRows / 16; ++kk)
-            if (kk < kk_n)
-              umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
-                          (j > 0 || kk != 0) ? 1u : 0u);
-          if (PSEP) umma_commit(pv_done);
-          if (!PSEP && j + 1 < n_kv) {
-            if (!mbar_wait_bounded(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+          issue_s(st);
+          if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
+          for (int j = 0; j < n_kv; ++j, ++step) {
+            const int st_n = (st + 1 == kStages) ? 0 : st + 1;
+            const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
+            if (j + 1 < n_kv) {
+              // S(j) sits in the softmax warps' registers: S(j+1) goes now, long before P(j) is ready
+              if (!mbar_wait_role(s_free, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
+                  !mbar_wait_role(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              issue_s(st_n);
+              if (j + 2 == n_kv) umma_commit(q_empty);
+            }
+            // P(j) is ready; this also tells that the softmax warps have finished the previous item's O
+            // read-out, so the first P V of an item may overwrite O.
+            if (!mbar_wait_role(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
+                !mbar_wait_role(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
               ok = false;
               break;
             }
             tc_fence_after();
-            issue_s(st_n);  // executes after the PV above (issue order), so P is not overwritten early
-            if (j + 2 == n_kv) umma_commit(q_empty);
+            const uint32_t sv = s_v + st * kTileBytes;
+            // only the 16-key steps that hold keys of this sequence
+            const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
+#pragma unroll
+            for (int kk = 0; kk < kKvRows / 16; ++kk)
+              if (kk < kk_n)
+                umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
+                            (j > 0 || kk != 0) ? 1u : 0u);
+            umma_commit(pv_done);
+            umma_commit(&kv_empty[st]);
+            st = st_n;
+            ph = ph_n;
           }
-          umma_commit(&kv_empty[st]);
-          st = st_n;
-          ph = ph_n;
+          if (ok) umma_commit(o_done);
         }
-        if (ok) umma_commit(o_done);
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    // ---------------------------------------------------------------- softmax (warps 0..3)
+    setmaxnreg_inc<216>();
+    const int r = warp * 32 + lane;  // query row inside the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
     const uint32_t t_s = t_lane + kTmemS;
     const uint32_t t_o = t_lane + kTmemO;
+    const uint32_t t_p = t_lane + kTmemP;
     const float c = args.scale_log2e;
     int stage = 0;
     uint32_t phase = 0;
-    uint32_t step = 0, item = 0;
-    bool ok = true;
-    for (int n = blockIdx.x; ok && decode_item(args.batch_idx, B, heads, n, cur_b, cur_first, seq_start, L, qt, head);
-         n += gridDim.x, ++item) {
+    uint32_t step = 0;
+    bool ok = smem_ok;
+    for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+         ++round) {
       const int n_kv = (L + kKvRows - 1) / kKvRows;
       float m_ref = -INFINITY;
       float l_run = 0.f;
       for (int j = 0; j < n_kv; ++j, ++step) {
         const int kv_valid = min(kKvRows, L - j * kKvRows);
-        const bool full_tile = kv_valid == kKvRows;
         if (!mbar_wait_bounded(s_full, step & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (ONEPASS) {
-          // ---- optimistic single pass with the reference of the earlier tiles (first tile of an item:
-          // with the maximum of its first 32 keys)
-          const uint32_t t_p = t_lane + kTmemP;
-          uint32_t va[32], vb[32], pk0[16], pk1[16];
-          float xmax = -INFINITY, l_tile = 0.f;
-          if (full_tile) {
-            tmem_ld_32x32(t_s, va);
-            tmem_ld_wait();
-            tmem_ld_32x32(t_s + 32, vb);
-            if (j == 0) m_ref = c * (chunk_max<false>(va, 0, kv_valid));
-            l_tile += chunk_probs_track<false>(va, 0, kv_valid, c, m_ref, pk0, xmax);
-            tmem_ld_wait();
-            tmem_ld_32x32(t_s + 64, va);
-            l_tile += chunk_probs_track<false>(vb, 32, kv_valid, c, m_ref, pk1, xmax);
-            // P (and O) belong to the P V MMAs of the previous key tile until those have retired; the first
-            // two chunks were computed in the meantime.  (First tile of an item: the wait for the previous
-            // item's O at its end already covered that.)
-            if (j > 0) {
-              if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-            }
-            tmem_st_32x16(t_p, pk0);
-            tmem_st_32x16(t_p + 16, pk1);
-            tmem_ld_wait();
-            tmem_ld_32x32(t_s + 96, vb);
-            l_tile += chunk_probs_track<false>(va, 64, kv_valid, c, m_ref, pk0, xmax);
-            tmem_st_32x16(t_p + 32, pk0);
-            tmem_ld_wait();
-            l_tile += chunk_probs_track<false>(vb, 96, kv_valid, c, m_ref, pk1, xmax);
-            tmem_st_32x16(t_p + 48, pk1);
-          } else {
-            // last tile of the sequence: only the 32-key chunks that hold at least one key are read and
-            // exponentiated; the P columns of the others stay unwritten (the P V steps stop before them)
-            const int n_chunks = (kv_valid + 31) >> 5;
-            for (int ch = 0; ch < n_chunks; ++ch) {
-              tmem_ld_32x32(t_s + ch * 32, va);
-              tmem_ld_wait();
-              if (j == 0 && ch == 0) m_ref = c * chunk_max<true>(va, 0, kv_valid);
-              l_tile += chunk_probs_track<true>(va, ch * 32, kv_valid, c, m_ref, pk0, xmax);
-              if (ch == 0 && j > 0) {
-                if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-              }
-              tmem_st_32x16(t_p + ch * 16, pk0);
-            }
-            if (!ok) break;
-          }
-          if (__any_sync(0xffffffffu, xmax > kRescaleThreshold)) {
-            // the reference was too low for some row of this warp: move it, rescale O and the running
-            // sum, and form this tile's probabilities again from S (rows that did not need it get f = 1)
-            const float m_new = m_ref + fmaxf(xmax, 0.f);
-            const float f = ex2_approx(m_ref - m_new);
+        uint32_t s[128];
+        tmem_ld_32x32_at<0>(t_s, s);
+        tmem_ld_32x32_at<32>(t_s + 32, s);
+        tmem_ld_32x32_at<64>(t_s + 64, s);
+        tmem_ld_32x32_at<96>(t_s + 96, s);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        if (kv_valid != kKvRows) {
+          // last tile of the sequence: keys that do not exist get -inf (probability 0), by selection
 #pragma unroll
-            for (int cb = 0; cb < (j > 0 ? kHeadDim : 0); cb += 32) {  // (no O yet on the first tile)
-              uint32_t v[32];
-              tmem_ld_32x32(t_o + cb, v);
-              tmem_ld_wait();
+          for (int i = 0; i < 128; ++i) s[i] = (i < kv_valid) ? s[i] : 0xff800000u;
+        }
+        // ---- exact row maximum
+        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-              tmem_st_32x32(t_o + cb, v);
-            }
-            l_run *= f;
-            m_ref = m_new;
-            tmem_st_wait();
-            l_tile = full_tile ? tile_probs_sep<false>(t_s, t_p, kv_valid, c, m_ref)
-                               : tile_probs_sep<true>(t_s, t_p, kv_valid, c, m_ref);
-          } else {
-            tmem_st_wait();
+        for (int i = 0; i < 128; i += 4) {
+          mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        }
+        const float m_new = fmaxf(m_ref, c * fmaxf(mx0, mx1));
+        bool pv_waited = (j == 0);  // (first tile of an item: the wait for the previous item's O covered it)
+        if (j == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, (m_new - m_ref) > kRescaleThreshold)) {
+          // O belongs to the P V MMAs of the previous key tile until those have retired
+          if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+            ok = false;
+            break;
           }
-          l_run += l_tile;
-        } else {
-        const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
-        if (PSEP && j > 0) {
-          // O and P still belong to the P V MMAs of the previous key tile until those have retired
+          tc_fence_after();
+          pv_waited = true;
+          const float f = ex2_approx(m_ref - m_new);
+#pragma unroll
+          for (int cb = 0; cb < kHeadDim; cb += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_o + cb, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st_32x32(t_o + cb, v);
+          }
+          l_run *= f;
+          m_ref = m_new;
+        }
+        // ---- probabilities: fp16 pairs for P's own columns, fp32 row sum
+        float l0 = 0.f, l1 = 0.f;
+        uint32_t pk[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), c, -m_ref));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), c, -m_ref));
+          l0 += p0;
+          l1 += p1;
+          pk[i] = pack_half2(p0, p1);
+        }
+        l_run += l0 + l1;
+        if (!pv_waited) {
+          // P belongs to the P V MMAs of the previous key tile until those have retired
           if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
             ok = false;
             break;
           }
           tc_fence_after();
         }
-        if (j == 0) {
-          m_ref = mx;
-        } else {
-          const float m_new = fmaxf(m_ref, mx);
-          const bool need = (m_new - m_ref) > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, need)) {
-            const float f = ex2_approx(m_ref - m_new);
-#pragma unroll
-            for (int cb = 0; cb < kHeadDim; cb += 32) {
-              uint32_t v[32];
-              tmem_ld_32x32(t_o + cb, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-              tmem_st_32x32(t_o + cb, v);
-            }
-            l_run *= f;
-            m_ref = m_new;
-          }
-        }
-        if (PSEP)
-          l_run += full_tile ? tile_probs_sep<false>(t_s, t_lane + kTmemP, kv_valid, c, m_ref)
-                             : tile_probs_sep<true>(t_s, t_lane + kTmemP, kv_valid, c, m_ref);
-        else
-          l_run += full_tile ? tile_probs<false, EXP16>(t_s, kv_valid, c, m_ref)
-                             : tile_probs<true, EXP16>(t_s, kv_valid, c, m_ref);
-        }
-        if (!full_tile) {
+        tmem_st_32x16_at<0>(t_p, pk);
+        tmem_st_32x16_at<16>(t_p + 16, pk);
+        tmem_st_32x16_at<32>(t_p + 32, pk);
+        tmem_st_32x16_at<48>(t_p + 48, pk);
+        if (kv_valid != kKvRows) {
           // tail tile: blank the V rows of keys that do not belong to this sequence
           if (!mbar_wait_bounded(&v_full[stage], phase, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
             ok = false;
@@ -997,14 +941,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           }
           fence_proxy_async_smem();
         }
+        tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(p_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
-      if (!ok || !mbar_wait_bounded(o_done, item & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+      if (!ok || !mbar_wait_bounded(o_done, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
         ok = false;
         break;
       }
@@ -1013,21 +959,28 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
       const float inv = 1.0f / l_run;
       uint4* dst = reinterpret_cast<uint4*>(args.ctx + static_cast<size_t>(seq_start + q_row) * args.hidden +
                                             head * kHeadDim);
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(t_o, va);
+      tmem_ld_32x32(t_o + 32, vb);
+      tmem_ld_wait();
+      if (q_row < L) {
 #pragma unroll
-      for (int cb = 0; cb < kHeadDim; cb += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_o + cb, v);
-        tmem_ld_wait();
-        if (q_row < L) {
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_half2(__uint_as_float(va[u * 8 + 0]) * inv, __uint_as_float(va[u * 8 + 1]) * inv);
+          w.y = pack_half2(__uint_as_float(va[u * 8 + 2]) * inv, __uint_as_float(va[u * 8 + 3]) * inv);
+          w.z = pack_half2(__uint_as_float(va[u * 8 + 4]) * inv, __uint_as_float(va[u * 8 + 5]) * inv);
+          w.w = pack_half2(__uint_as_float(va[u * 8 + 6]) * inv, __uint_as_float(va[u * 8 + 7]) * inv);
+          dst[u] = w;
+        }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 w;
-            w.x = pack_half2(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
-            w.y = pack_half2(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
-            w.z = pack_half2(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
-            w.w = pack_half2(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
-            dst[(cb >> 3) + u] = w;
-          }
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_half2(__uint_as_float(vb[u * 8 + 0]) * inv, __uint_as_float(vb[u * 8 + 1]) * inv);
+          w.y = pack_half2(__uint_as_float(vb[u * 8 + 2]) * inv, __uint_as_float(vb[u * 8 + 3]) * inv);
+          w.z = pack_half2(__uint_as_float(vb[u * 8 + 4]) * inv, __uint_as_float(vb[u * 8 + 5]) * inv);
+          w.w = pack_half2(__uint_as_float(vb[u * 8 + 6]) * inv, __uint_as_float(vb[u * 8 + 7]) * inv);
+          dst[4 + u] = w;
         }
       }
     }
@@ -1038,15 +991,13 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   if (*abort_flag != 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
-  if (warp == 1) {
+  if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
 }
 
-template <bool EXP16, bool PSEP = false, bool ONEPASS = false>
 cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
-  constexpr int kSmemBytes = 7 * kTileBytes + 256;
   static bool attr_set[64] = {};
   static int sms[64] = {};
   int dev = 0;
@@ -1054,7 +1005,7 @@ cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!attr_set[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(mha_persistent_kernel<EXP16, PSEP, ONEPASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaFuncSetAttribute(mha_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistentSmemBytes);
     if (e != cudaSuccess) return e;
     if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)
       sms[dev] = 148;
@@ -1068,36 +1019,31 @@ cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   args.hidden = a.hidden;
   args.scale_log2e = a.scale_log2e;
   args.status = a.status;
+  args.rows = a.rows;
+  args.max_len = a.max_len;
   const long long items_max =
       static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);  // upper bound
   long long grid = 2LL * sms[dev];
   if (grid > items_max) grid = items_max;
   if (grid < 1) grid = 1;
-  return launch_pdl(mha_persistent_kernel<EXP16, PSEP, ONEPASS>, dim3(static_cast<unsigned>(grid)), dim3(192), kSmemBytes, stream,
-                    a.tm_qkv, args);
+  return launch_pdl(mha_persistent_kernel, dim3(static_cast<unsigned>(grid)), dim3(kPersistentThreads), kPersistentSmemBytes,
+                    stream, a.tm_qkv, args);
 }
 
-template <int TILES, bool EXP16>
-cudaError_t launch_tiles(const MhaLaunch& a, const MhaArgs& args, cudaStream_t stream) {
-  using Cfg = MhaCfg<TILES>;
+template <bool GENERAL>
+cudaError_t launch_per_item(const MhaLaunch& a, const MhaArgs& args, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mha_fwd_kernel<TILES, EXP16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    cudaError_t e =
+        cudaFuncSetAttribute(mha_fwd_kernel<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, MhaCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  const int rows_per_cta = kQRows * TILES;
-  dim3 grid((a.max_len + rows_per_cta - 1) / rows_per_cta, a.head_num, a.batch);
-  return launch_pdl(mha_fwd_kernel<TILES, EXP16>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
+  dim3 grid((a.max_len + kQRows - 1) / kQRows, a.head_num, a.batch);
+  return launch_pdl(mha_fwd_kernel<GENERAL>, grid, dim3(MhaCfg::kThreads), MhaCfg::kSmemBytes, stream, a.tm_qkv, args);
 }
-
-long long g_dbg_force_tiles = 0;
-long long* g_dbg_timing = nullptr;
-constexpr int kTimingCtas = 4096, kTimingSteps = 8, kTimingSlots = 8;
-long long g_dbg_exp16 = 0;  // 0 = default (fp32 exponentials), 1 = fp16x2 exponentials
 
 }  // namespace
 
@@ -1109,65 +1055,28 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.hidden = a.hidden;
   args.scale_log2e = a.scale_log2e;
   args.status = a.status;
-  args.timing = g_dbg_timing;
+  args.rows = a.rows;
+  args.max_len = a.max_len;
   args.gen_mask = a.gen_mask;
   args.gen_bias = a.gen_bias;
   args.gen_seq_len = a.max_len;
   args.gen_inv_scale = a.gen_inv_scale;
   args.gen_kv_bound = a.gen_kv_bound;
-  if (a.gen_mask != nullptr) {
-    // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
-    using Cfg = MhaCfg<1>;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(mha_fwd_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           Cfg::kSmemBytes);
-      if (e != cudaSuccess) return e;
-      attr_set[dev] = true;
-    }
-    dim3 grid((a.max_len + kQRows - 1) / kQRows, a.head_num, a.batch);
-    return launch_pdl(mha_fwd_kernel<1, false, true>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, a.tm_qkv, args);
-  }
-  // Measured on B200 (18.9k packed tokens, 12 heads): the one-tile variant with two
-  // co-resident CTAs per SM is faster at every length from 64 to 1024, so it is the
-  // default; the two-tile variant stays selectable.
-  const bool exp16 = g_dbg_exp16 == 1;
-  // Default: the persistent kernel once sequences span more than two key tiles (measured at
-  // 18.9k tokens: +4..7 % at lengths 384..1024, +12 % on lengths uniform in [16,1024]); for
-  // short sequences one CTA per item is faster (lengths 64 / 128: 77 vs 89 us, 40 vs 47 us).
-  // With fewer than ~600 items (two per persistent CTA) the static item lists are too short to
-  // balance and the hardware's own block scheduling of one CTA per item is as good or better
-  // (12 layers, batch 1, 307 of 512 tokens: 0.756 vs 0.785 ms; batch 16 at max_seq 512: 1.544 vs 1.503 ms).
-  const long long items_max = static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);
-  if (g_dbg_force_tiles == 0 && a.max_len > 256 && items_max >= 600)
-    return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false, true, true>(a, stream);
-  if (g_dbg_force_tiles == 3) return exp16 ? launch_persistent<true>(a, stream) : launch_persistent<false, true, true>(a, stream);
-  if (g_dbg_force_tiles == 6) return launch_persistent<false>(a, stream);  // P over the upper half of S, two reads of S per key tile
-  if (g_dbg_force_tiles == 4) return launch_persistent<false, true>(a, stream);  // P in its own columns, S(j+1) before P V(j)
-  if (g_dbg_force_tiles == 5) return launch_persistent<false, true, true>(a, stream);  // + one read of S per key tile
-  int tiles = 1;
-  if (g_dbg_force_tiles == 1 || g_dbg_force_tiles == 2) tiles = static_cast<int>(g_dbg_force_tiles);
-  if (tiles == 1) return exp16 ? launch_tiles<1, true>(a, args, stream) : launch_tiles<1, false>(a, args, stream);
-  return exp16 ? launch_tiles<2, true>(a, args, stream) : launch_tiles<2, false>(a, args, stream);
+  // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
+  if (a.gen_mask != nullptr) return launch_per_item<true>(a, args, stream);
+  // Measured on B200 (12 heads): with sequences of up to 128 tokens one CTA per item is faster (18.9k
+  // tokens of 64 / 128: 77 / 40 us against 93 / 49), at 256 the two are level, beyond that the
+  // persistent kernel wins whatever the number of items (one sequence of 614: 12.8 against 14.0 us;
+  // 16 sequences up to 512: 24.4 against 27.4; 64 up to 384: 57 against 66; 18 of 1024: 101 against 120).
+  const bool persistent = g_dbg_force_kernel == 3 || (g_dbg_force_kernel == 0 && a.max_len > 192);
+  return persistent ? launch_persistent(a, stream) : launch_per_item<false>(a, args, stream);
 }
 
 }  // namespace bt
 
-// Diagnostics hooks (not part of the stable ABI): attention variant (0 = default: persistent
-// for max_len > 256, else one CTA per item; 1 / 2 = one CTA per item with one / two query
-// tiles; 3 = always persistent) and exponential flavour (0 = fp32, 1 = fp16x2).
-extern "C" int bt_debug_set_mha_tiles(long long tiles) {
-  bt::g_dbg_force_tiles = tiles;
-  return 0;
-}
-// Device buffer of 4096 CTAs x 8 steps x 8 slots of long long for clock64 stamps (null = off).
-extern "C" int bt_debug_set_mha_timing(long long* device_buffer) {
-  bt::g_dbg_timing = device_buffer;
-  return 0;
-}
-extern "C" int bt_debug_set_mha_exp16(long long on) {
-  bt::g_dbg_exp16 = on;
+// Diagnostics hook (process-global, for tests and measurements; not part of the stable ABI): attention
+// kernel 0 = chosen by shape, 1 = one CTA per item, 3 = persistent.
+extern "C" int bt_debug_set_mha_tiles(long long kernel) {
+  bt::g_dbg_force_kernel = kernel;
   return 0;
 }

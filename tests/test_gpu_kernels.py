@@ -338,11 +338,10 @@ def test_gemm_pair_twice_bit_identical_and_equal_to_single(enc, cuda_device):
     assert torch.equal(o1, o3)          # same accumulation order: K is walked identically
 
 
-@pytest.mark.parametrize("tiles,exp16", [(0, 0), (3, 0), (3, 1), (4, 0), (5, 0), (1, 0), (2, 0), (1, 1), (2, 1)])
-def test_attention_variants(enc, cuda_device, tiles, exp16):
-    """The persistent kernel (0) and the one-CTA-per-item kernels with one / two query tiles
-    per CTA (1, 2), each with both exponential flavours (fp32, and
-    fp16x2 where two exponentials share one special-function op) against the oracle."""
+@pytest.mark.parametrize("kernel", [0, 1, 3], ids=["by_shape", "cta_per_item", "persistent"])
+def test_attention_variants(enc, cuda_device, kernel):
+    """Both attention kernels (one CTA per item, persistent) forced for the same ragged batch, and the
+    choice by shape, against the oracle; twice, bit-identical (race check)."""
     from bytetransformer_b200 import _abi
     from oracle.bert_oracle import attention_packed
     lib = _abi.load()
@@ -352,17 +351,51 @@ def test_attention_variants(enc, cuda_device, tiles, exp16):
     g = torch.Generator().manual_seed(4242)
     qkv = (torch.randn(T, 3 * enc.hidden, generator=g) * 1.5).half()   # logits with std ~ 2.8: sharp softmax
     want = attention_packed(qkv.float(), cu.tolist(), enc.head_num, enc.head_size)
-    lib.bt_debug_set_mha_tiles(tiles)
-    lib.bt_debug_set_mha_exp16(exp16)
+    lib.bt_debug_set_mha_tiles(kernel)
     try:
         got = enc.attention(qkv.to(cuda_device), torch.from_numpy(cu).to(cuda_device), max(lens))
         got2 = enc.attention(qkv.to(cuda_device), torch.from_numpy(cu).to(cuda_device), max(lens))
     finally:
         lib.bt_debug_set_mha_tiles(0)
-        lib.bt_debug_set_mha_exp16(0)
     assert torch.equal(got, got2)
-    mx, mn = assert_close_fp16(got, want, f"attention tiles{tiles} exp16={exp16}", max_abs=8e-3, mean_abs=4e-4)
-    print(f"attention tiles{tiles} exp16={exp16}: max-abs {mx:.3e} mean-abs {mn:.3e}")
+    assert enc.device_status() == 0
+    mx, mn = assert_close_fp16(got, want, f"attention kernel {kernel}", max_abs=8e-3, mean_abs=4e-4)
+    print(f"attention kernel {kernel}: max-abs {mx:.3e} mean-abs {mn:.3e}")
+
+
+@pytest.mark.parametrize("kernel", [1, 3], ids=["cta_per_item", "persistent"])
+def test_attention_rejects_offsets_outside_the_allocation(enc, cuda_device, kernel):
+    """cu_seqlens that do not describe rows of the buffers (a sequence running past the last row, one longer
+    than max_len, a decreasing offset) must not be followed: the kernel leaves those sequences out, reports
+    the bad-offsets status, and the rows of the well-formed sequences still come out right."""
+    from bytetransformer_b200 import _abi
+    from oracle.bert_oracle import attention_packed
+    lib = _abi.load()
+    good = [200, 130, 300]
+    T = sum(good)
+    g = torch.Generator().manual_seed(99)
+    qkv = torch.randn(T, 3 * enc.hidden, generator=g).half()
+    want = attention_packed(qkv.float(), np.concatenate([[0], np.cumsum(good)]).tolist(), enc.head_num, enc.head_size)
+    qkv_dev = qkv.to(cuda_device)
+    lib.bt_debug_set_mha_tiles(kernel)
+    try:
+        for bad_cu, ok_rows in (([0, 200, 330, 900], slice(0, 330)),        # last sequence runs past the 630 rows
+                                ([0, 200, 100, 630], slice(0, 200)),        # decreasing offset
+                                ([0, 200, 330, 630, 630 + 5000], slice(0, 630))):  # longer than max_len and the buffer
+            cu = torch.tensor(bad_cu, dtype=torch.int32, device=cuda_device)
+            out = torch.zeros(T, enc.hidden, dtype=torch.float16, device=cuda_device)
+            rc = lib.bt_attention(enc._h, qkv_dev.data_ptr(), out.data_ptr(), cu.data_ptr(), len(bad_cu) - 1,
+                                  300, T, torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert enc.device_status() == 0x301
+            assert torch.isfinite(out).all()
+            if bad_cu[:3] == [0, 200, 330]:
+                assert_close_fp16(out[ok_rows].cpu(), want[ok_rows], "rows of the well-formed sequences",
+                                  max_abs=8e-3, mean_abs=4e-4)
+    finally:
+        lib.bt_debug_set_mha_tiles(0)
+    assert enc.device_status() == 0
 
 
 @pytest.mark.parametrize("M,N,K,gb32,m_valid", [
@@ -422,12 +455,3 @@ def test_expired_wait_is_reported_and_the_context_stays_usable(enc, cuda_device)
     assert enc.device_status() == 0                     # read-and-clear
     _gemm_case(enc, cuda_device, 300, 768, 768, _abi.BT_EPI_BIAS)
     assert enc.device_status() == 0
-
-
-def test_tensor_memory_read_rate_is_far_above_what_the_kernels_consume(cuda_device):
-    """The GEMM epilogues and the attention softmax consume their tiles at roughly 48 B/clk per SM; a loop
-    that only reads tensor memory gets several times that, so they are not bounded by tensor-memory
-    bandwidth (the figure this test guards is quoted where the kernels are described)."""
-    from bytetransformer_b200.tmem_probe import read_rate
-    assert read_rate(0, 4, device=cuda_device) > 80.0    # measured 123
-    assert read_rate(2, 8, device=cuda_device) > 150.0   # measured 370
