@@ -112,30 +112,30 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU oracle timing
-def cpu_oracle_tokens_per_sec(lengths, target_seconds=12.0, reps=1):
-    """Times the CPU oracle (fp32 PyTorch encoder, 12 layers) on the first sequences of
-    the workload until about `target_seconds` of work; returns (tokens/s, sample text, cores)."""
+CPU_SAMPLE_SEQS = 32   # the CPU arm times the first 32 sequences of the workload (18,645 tokens), always the same ones
+
+
+def host_threads() -> int:
+    """The host threads this process may use (its CPU affinity), whatever OMP_NUM_THREADS says: torchrun
+    exports OMP_NUM_THREADS=1 to its children, which would otherwise shrink the CPU arm to one thread."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_oracle_sample(lengths, reps=1):
+    """Times the CPU oracle (the reference's fp32 PyTorch encoder restated, 12 layers) on the first
+    CPU_SAMPLE_SEQS sequences of the workload with every host thread the process may use.
+    Returns (tokens/s, sample text, threads, tokens, seconds)."""
     from oracle.bert_oracle import encoder_stack_packed
     from bytetransformer_b200.workloads import BERT_BASE, make_weights
+    cores = host_threads()
+    torch.set_num_threads(cores)
     layers = [[t.float() for t in w] for w in make_weights(BERT_BASE, seed=7)]
-    cores = torch.get_num_threads()
     g = torch.Generator().manual_seed(3)
-    # probe: one sequence
-    order = list(range(len(lengths)))
-    probe_len = int(lengths[order[0]])
-    x = torch.randn(probe_len, BERT_BASE.hidden, generator=g)
-    with torch.no_grad():
-        t0 = time.perf_counter()
-        encoder_stack_packed(x, [0, probe_len], layers, BERT_BASE.head_num, 64, ln_eps=1e-6)
-        dt = time.perf_counter() - t0
-    rate = probe_len / dt
-    n_tok_target = max(probe_len, int(rate * target_seconds))
-    ids, tok = [], 0
-    for i in order:
-        if tok + int(lengths[i]) > n_tok_target and ids:
-            break
-        ids.append(i)
-        tok += int(lengths[i])
+    ids = list(range(min(CPU_SAMPLE_SEQS, len(lengths))))
+    tok = int(sum(int(lengths[i]) for i in ids))
     cu = np.concatenate([[0], np.cumsum([int(lengths[i]) for i in ids])]).tolist()
     x = torch.randn(tok, BERT_BASE.hidden, generator=g)
     best = None
@@ -145,7 +145,7 @@ def cpu_oracle_tokens_per_sec(lengths, target_seconds=12.0, reps=1):
             encoder_stack_packed(x, cu, layers, BERT_BASE.head_num, 64, ln_eps=1e-6)
             dt = time.perf_counter() - t0
             best = dt if best is None else min(best, dt)
-    sample = f"first {len(ids)} sequences ({tok} tokens) of the workload, 12 layers, fp32, {best:.2f} s"
+    sample = f"first {len(ids)} sequences ({tok} tokens) of the workload, 12 layers, fp32, {cores} threads"
     return tok / best, sample, cores, tok, best
 
 
@@ -155,13 +155,11 @@ def run_reference_arm(args):
         return 0
     from bytetransformer_b200.workloads import lengths_for
     lengths = lengths_for(WORKLOAD)
-    cores = torch.get_num_threads()
-    # every step is a bounded sample (about 6 s of CPU work)
+    # every step is the same bounded sample (a few seconds of CPU work)
     per_step = []
-    sample = ""
-    tok = 0
+    sample, cores = "", host_threads()
     for i in range(args.warmup + args.steps):
-        tps, sample, cores, tok, dt = cpu_oracle_tokens_per_sec(lengths, target_seconds=6.0)
+        _, sample, cores, tok, dt = cpu_oracle_sample(lengths)
         if i >= args.warmup:
             per_step.append((tok, dt))
     tot_tok = sum(t for t, _ in per_step)
@@ -190,12 +188,15 @@ def main():
     ap.add_argument("--no-kernel-events", action="store_true", help="do not bracket kernels with events in the timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the other BASELINE configurations (N = 1 extra key)")
     ap.add_argument("--token-budget", type=int, default=0)
     ap.add_argument("--fused-ln", type=int, default=-1,
                     help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
     ap.add_argument("--max-seqs", type=int, default=0,
                     help="profiling aid: keep only the first N sequences of the workload (small ncu captures)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only the first L layers")
+    ap.add_argument("--sorted-batches", action="store_true",
+                    help="A/B aid: micro-batches of similar lengths instead of the same mix of lengths in each")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -232,7 +233,7 @@ def main():
         from bytetransformer_b200 import _abi
         _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
     budget = args.token_budget or DEFAULT_TOKEN_BUDGET
-    runner = PackedRunner(enc, lengths, mine, token_budget=budget)
+    runner = PackedRunner(enc, lengths, mine, token_budget=budget, mix=not args.sorted_batches)
     xs, outs = runner.make_device_inputs(seed=rank)
 
     barrier = ranks.barrier
@@ -334,8 +335,18 @@ def main():
     # ---- CPU baseline (rank 0, N = 1 only) ---------------------------------------------
     cpu = None
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
-        tps, sample, cores, _, _ = cpu_oracle_tokens_per_sec(lengths, target_seconds=12.0)
+        tps, sample, cores, _, _ = cpu_oracle_sample(lengths_for(WORKLOAD), reps=2)
         cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    # ---- the other BASELINE configurations (rank 0, N = 1 only): extra key, the headline is untouched ----
+    configs = None
+    if rank == 0 and n_gpus == 1 and not args.no_configs and not (args.max_seqs or args.layers):
+        from bytetransformer_b200.latency_bench import baseline_configs
+        enc.close()
+        del xs, outs
+        runner.workspace = None
+        torch.cuda.empty_cache()
+        configs = baseline_configs({"tflops": peaks["tflops"], "hbm_gbs": peaks["hbm_gbs"]}, device=dev, iters=20, warmup=5)
 
     if rank == 0:
         line = {
@@ -352,6 +363,7 @@ def main():
                        "ms_per_step_with_kernel_events": ms_events_region},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
             "kernels": kernels,
+            "configs": configs,
         }
         print(json.dumps(line), flush=True)
     ranks.close()

@@ -577,29 +577,49 @@ struct MhaPersistentArgs {
 };
 
 // Finds item n = (sequence b, query tile qt, head h); items are numbered sequence by sequence, inside
-// a sequence query tile by query tile, heads fastest.  `cur_b` / `cur_first` is the caller's cursor
-// (first item index of sequence cur_b); n never decreases.  A sequence whose offsets are not
-// 0 <= start, 0 <= L <= max_len, start + L <= rows is left out (it yields no items, so nothing is read
-// or written outside the buffers) and, when `report` is set (one thread per CTA), kStatusBadOffsets is
-// recorded.
+// a sequence query tile by query tile, heads fastest.  Called by all 32 lanes of a warp together: the
+// lanes look at 32 sequences at a time (one coalesced read of their offsets, a warp scan of their item
+// counts), because a loop over single sequences pays one L2 round trip per sequence, which with many
+// short sequences cost more than the attention itself.  `cur_b` / `cur_first` is the caller's cursor
+// (first item index of sequence cur_b, the same in all lanes); n never decreases.  A sequence whose
+// offsets are not 0 <= start, 0 <= L <= max_len, start + L <= rows is left out (it yields no items, so
+// nothing is read or written outside the buffers) and, when `report` is set (one warp per CTA),
+// kStatusBadOffsets is recorded.
 __device__ __forceinline__ bool decode_item(const MhaPersistentArgs& a, int n, int& cur_b, int& cur_first,
                                             int& seq_start, int& L, int& qt, int& h, bool report) {
+  const int lane = static_cast<int>(threadIdx.x & 31u);
   while (cur_b < a.batch) {
-    seq_start = __ldg(a.batch_idx + cur_b);
-    L = __ldg(a.batch_idx + cur_b + 1) - seq_start;
-    if (seq_start < 0 || L < 0 || L > a.max_len || seq_start > a.rows - L) {
-      if (report && a.status != nullptr) atomicCAS(a.status, 0, kStatusBadOffsets);
-      L = 0;
+    const int b = cur_b + lane;
+    int start = 0, len = 0;
+    if (b < a.batch) {
+      start = __ldg(a.batch_idx + b);
+      len = __ldg(a.batch_idx + b + 1) - start;
+      if (start < 0 || len < 0 || len > a.max_len || start > a.rows - len) {
+        if (report && a.status != nullptr) atomicCAS(a.status, 0, kStatusBadOffsets);
+        len = 0;
+      }
     }
-    const int items = ((L + kQRows - 1) / kQRows) * a.heads;
-    if (n < cur_first + items) {
+    const int items = ((len + kQRows - 1) / kQRows) * a.heads;
+    int incl = items;  // inclusive prefix sum over the 32 sequences
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    const unsigned found = __ballot_sync(0xffffffffu, b < a.batch && n < cur_first + incl);
+    if (found != 0u) {
+      const int src = __ffs(found) - 1;
+      seq_start = __shfl_sync(0xffffffffu, start, src);
+      L = __shfl_sync(0xffffffffu, len, src);
+      cur_first += __shfl_sync(0xffffffffu, incl - items, src);
+      cur_b += src;
       const int r = n - cur_first;
       qt = r / a.heads;
       h = r - qt * a.heads;
       return true;
     }
-    cur_first += items;
-    ++cur_b;
+    cur_first += __shfl_sync(0xffffffffu, incl, 31);
+    cur_b += 32;
   }
   return false;
 }
@@ -733,15 +753,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
       // fall through to the teardown
     } else if (warp == 4) {
       // ------------------------------------------------------------------ loads
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, true);
-             ++round) {
+      // (the whole warp finds the items, lane 0 does the rest)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, true);
+           ++round) {
+        if (lane == 0) {
           const int n_kv = (L + kKvRows - 1) / kKvRows;
-          if (!mbar_wait_role(q_empty, (static_cast<uint32_t>(round) & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout))
-            break;
+          ok = mbar_wait_role(q_empty, (static_cast<uint32_t>(round) & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout);
+          if (ok) {
           mbar_arrive_expect_tx(q_full, kTileBytes);
           tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, head * kHeadDim, seq_start + qt * kQRows);
           for (int j = 0; j < n_kv; ++j) {
@@ -760,77 +781,80 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
               phase ^= 1u;
             }
           }
+          }
         }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     } else if (warp == 5) {
       // -------------------------------------------------------------- MMA issue
-      if (lane == 0) {
-        constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
-        constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
-        constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
-        constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
-        const uint32_t s_q = smem_u32(smem + kSmemQ);
-        const uint32_t s_k = smem_u32(smem + kSmemK);
-        const uint32_t s_v = smem_u32(smem + kSmemV);
-        auto issue_s = [&](int stage) {
-          const uint32_t sk = s_k + stage * kTileBytes;
+      // (the whole warp finds the items, lane 0 does the rest)
+      constexpr uint64_t kDescK = make_smem_desc_hi(16, 1024);
+      constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
+      constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
+      constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
+      const uint32_t s_q = smem_u32(smem + kSmemQ);
+      const uint32_t s_k = smem_u32(smem + kSmemK);
+      const uint32_t s_v = smem_u32(smem + kSmemV);
+      auto issue_s = [&](int stage) {
+        const uint32_t sk = s_k + stage * kTileBytes;
 #pragma unroll
-          for (int k = 0; k < kHeadDim / 16; ++k)
-            umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
-                        k != 0 ? 1u : 0u);
-          umma_commit(s_full);
-        };
-        int st = 0;
-        uint32_t ph = 0;
-        uint32_t step = 0;
-        bool ok = true;
-        for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
-             ++round) {
-          const int n_kv = (L + kKvRows - 1) / kKvRows;
-          // S(0) overwrites the S columns: the softmax warps must hold the previous item's last S in registers
-          if (step > 0 && !mbar_wait_role(s_free, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-          if (!mbar_wait_role(q_full, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-          if (!mbar_wait_role(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) break;
-          tc_fence_after();
-          issue_s(st);
-          if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
-          for (int j = 0; j < n_kv; ++j, ++step) {
-            const int st_n = (st + 1 == kStages) ? 0 : st + 1;
-            const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
-            if (j + 1 < n_kv) {
-              // S(j) sits in the softmax warps' registers: S(j+1) goes now, long before P(j) is ready
-              if (!mbar_wait_role(s_free, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
-                  !mbar_wait_role(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-              issue_s(st_n);
-              if (j + 2 == n_kv) umma_commit(q_empty);
-            }
-            // P(j) is ready; this also tells that the softmax warps have finished the previous item's O
-            // read-out, so the first P V of an item may overwrite O.
-            if (!mbar_wait_role(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
-                !mbar_wait_role(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) {
-              ok = false;
-              break;
-            }
+        for (int k = 0; k < kHeadDim / 16; ++k)
+          umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
+                      k != 0 ? 1u : 0u);
+        umma_commit(s_full);
+      };
+      int st = 0;
+      uint32_t ph = 0;
+      uint32_t step = 0;
+      // one item: every MMA of it, issued by lane 0; false when a wait gave up
+      auto issue_item = [&](int round) -> bool {
+        const int n_kv = (L + kKvRows - 1) / kKvRows;
+        // S(0) overwrites the S columns: the softmax warps must hold the previous item's last S in registers
+        if (step > 0 && !mbar_wait_role(s_free, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
+        if (!mbar_wait_role(q_full, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
+        if (!mbar_wait_role(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
+        tc_fence_after();
+        issue_s(st);
+        if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
+        for (int j = 0; j < n_kv; ++j, ++step) {
+          const int st_n = (st + 1 == kStages) ? 0 : st + 1;
+          const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
+          if (j + 1 < n_kv) {
+            // S(j) sits in the softmax warps' registers: S(j+1) goes now, long before P(j) is ready
+            if (!mbar_wait_role(s_free, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
+                !mbar_wait_role(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout))
+              return false;
             tc_fence_after();
-            const uint32_t sv = s_v + st * kTileBytes;
-            // only the 16-key steps that hold keys of this sequence
-            const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
-#pragma unroll
-            for (int kk = 0; kk < kKvRows / 16; ++kk)
-              if (kk < kk_n)
-                umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
-                            (j > 0 || kk != 0) ? 1u : 0u);
-            umma_commit(pv_done);
-            umma_commit(&kv_empty[st]);
-            st = st_n;
-            ph = ph_n;
+            issue_s(st_n);
+            if (j + 2 == n_kv) umma_commit(q_empty);
           }
-          if (ok) umma_commit(o_done);
+          // P(j) is ready; this also tells that the softmax warps have finished the previous item's O
+          // read-out, so the first P V of an item may overwrite O.
+          if (!mbar_wait_role(p_full, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout) ||
+              !mbar_wait_role(&v_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout))
+            return false;
+          tc_fence_after();
+          const uint32_t sv = s_v + st * kTileBytes;
+          // only the 16-key steps that hold keys of this sequence
+          const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
+#pragma unroll
+          for (int kk = 0; kk < kKvRows / 16; ++kk)
+            if (kk < kk_n)
+              umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
+                          (j > 0 || kk != 0) ? 1u : 0u);
+          umma_commit(pv_done);
+          umma_commit(&kv_empty[st]);
+          st = st_n;
+          ph = ph_n;
         }
+        umma_commit(o_done);
+        return true;
+      };
+      bool ok = true;
+      for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+           ++round) {
+        if (lane == 0) ok = issue_item(round);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
   } else {
@@ -1064,11 +1088,14 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.gen_kv_bound = a.gen_kv_bound;
   // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
   if (a.gen_mask != nullptr) return launch_per_item<true>(a, args, stream);
-  // Measured on B200 (12 heads): with sequences of up to 128 tokens one CTA per item is faster (18.9k
-  // tokens of 64 / 128: 77 / 40 us against 93 / 49), at 256 the two are level, beyond that the
-  // persistent kernel wins whatever the number of items (one sequence of 614: 12.8 against 14.0 us;
-  // 16 sequences up to 512: 24.4 against 27.4; 64 up to 384: 57 against 66; 18 of 1024: 101 against 120).
-  const bool persistent = g_dbg_force_kernel == 3 || (g_dbg_force_kernel == 0 && a.max_len > 192);
+  // Measured on B200 (12 heads, 18.9k tokens): the persistent kernel is ahead at every length (sequences
+  // of 64 / 128 / 256 / 384 / 1024 tokens: 70 / 40 / 47 / 57 / 105 us against 77 / 40 / 52 / 62 / 120) and for
+  // few long sequences (one of 614 tokens: 12.8 against 14.0 us; 16 up to 512: 24 against 27); only a handful
+  // of short items, fewer than the persistent CTAs, is served faster by one CTA per item (16 sequences up
+  // to 64 tokens: 7.0 against 8.3 us).
+  const long long items_max = static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);
+  const bool persistent =
+      g_dbg_force_kernel == 3 || (g_dbg_force_kernel == 0 && (a.max_len > kQRows || items_max > 296));
   return persistent ? launch_persistent(a, stream) : launch_per_item<false>(a, args, stream);
 }
 

@@ -42,6 +42,74 @@ def lengths(batch: int, seq: int, seed: int):
     return torch.randint(max(1, 2 * avg - seq), seq + 1, (batch,), generator=g)
 
 
+def measure_config(name, shape, lens, max_seq, layers=None, iters=20, warmup=5, device=None, peaks=None, enc=None):
+    """One BASELINE configuration through the one-call padded stack (`bt_stack_forward_padded`): median
+    milliseconds per forward (CUDA events, L2 flushed before every timed iteration), valid tokens/s,
+    algorithmic TFLOP/s and two roofline fractions - of the dense tensor peak, and of HBM bandwidth for the
+    bytes every forward has to stream at least once (the layers' weights), which is what bounds the
+    few-token configurations.  `shape` is a workloads.ModelShape, `lens` the valid lengths."""
+    import numpy as np
+    from .encoder import Encoder
+    from .workloads import attention_flops_per_layer, gemm_flops_per_layer, make_weights
+    dev = device or torch.device("cuda:0")
+    layers = layers or shape.layers
+    own = enc is None
+    if own:
+        import copy
+        sh = copy.copy(shape)
+        sh.layers = layers
+        enc = Encoder(shape.head_num, 64, make_weights(sh, seed=7, device=dev))
+    lens_t = torch.as_tensor(np.asarray(lens), dtype=torch.long)
+    B, S, H = int(lens_t.numel()), int(max_seq), shape.hidden
+    T = int(lens_t.sum())
+    g = torch.Generator().manual_seed(S + B)
+    x = torch.randn(B, S, H, generator=g).half().to(dev)
+    mask = (torch.arange(S)[None, :] < lens_t[:, None]).unsqueeze(1).expand(B, S, S).contiguous().half().to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
+    times = []
+    for i in range(warmup + iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        enc.forward(x, mask, n_layers=layers)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    status = enc.device_status()
+    if own:
+        enc.close()
+    ms = statistics.median(times)
+    fl = layers * (gemm_flops_per_layer(T, H) + attention_flops_per_layer(lens_t.numpy(), H))
+    weight_bytes = layers * 24.0 * H * H
+    out = {"config": name, "model": shape.name, "layers": layers, "batch": B, "max_seq": S, "valid_tokens": T,
+           "ms": ms, "min_ms": min(times), "tokens_per_s": T / ms * 1e3, "algorithmic_tflops": fl / ms / 1e9,
+           "weight_gbs": weight_bytes / ms / 1e6, "device_status": status}
+    if peaks:
+        out["frac_of_tensor_peak"] = out["algorithmic_tflops"] / peaks["tflops"]
+        out["frac_of_hbm_peak_weights_only"] = out["weight_gbs"] / peaks["hbm_gbs"]
+    return out
+
+
+def baseline_configs(peaks=None, device=None, iters=20, warmup=5):
+    """The BASELINE configurations that fit one GPU besides the whole-box one, each through the padded
+    drop-in entry point: c1 (one layer, batch 16, max_seq 64), c2 (12 layers, batch 1, max_seq 64 / 512 /
+    1024 at 0.6 x valid), c3 (12 layers, batch 16, max_seq 512) and c4 (BERT-large, 24 layers, batch 64,
+    max_seq 384)."""
+    from .workloads import BERT_BASE, BERT_LARGE, lengths_for
+    out = {}
+    out["c1_1L_b16_s64"] = measure_config("c1", BERT_BASE, lengths_for("single_layer_b16_s64"), 64, layers=1,
+                                          iters=iters, warmup=warmup, device=device, peaks=peaks)
+    for S in (64, 512, 1024):
+        out[f"c2_12L_b1_s{S}"] = measure_config("c2", BERT_BASE, lengths_for(f"b1_sweep_s{S}"), S, iters=iters,
+                                                 warmup=warmup, device=device, peaks=peaks)
+    out["c3_12L_b16_s512"] = measure_config("c3", BERT_BASE, lengths_for("b16_s512"), 512, iters=iters, warmup=warmup,
+                                            device=device, peaks=peaks)
+    out["c4_large_24L_b64_s384"] = measure_config("c4", BERT_LARGE, lengths_for("large_b64_s384"), 384,
+                                                  iters=max(5, iters // 2), warmup=3, device=device, peaks=peaks)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=16)
@@ -64,11 +132,23 @@ def main():
                          "with the same right-padded mask, or with a causal mask over the valid keys")
     ap.add_argument("--front-back", action="store_true",
                     help="also time the embedding + LayerNorm front end (30522-word table) and the pooler for each shape")
+    ap.add_argument("--baseline-configs", action="store_true",
+                    help="instead of a sweep: the BASELINE configurations c1-c4 (BERT-base and BERT-large), one JSON line each")
     ap.add_argument("--breakdown", action="store_true",
                     help="add per-kernel-kind microseconds per forward (CUDA events around every launch, L2 warm)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
+    if args.baseline_configs:
+        import os
+        peaks = None
+        p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            d = json.load(open(p))
+            peaks = {"tflops": float(d["bf16_tflops_sustained"]), "hbm_gbs": float(d["hbm_gbs"])}
+        for k, v in baseline_configs(peaks, iters=args.iters, warmup=args.warmup).items():
+            print(json.dumps({"name": k, **v}), flush=True)
+        return 0
     from .encoder import Encoder
     from .workloads import BERT_BASE, attention_flops_per_layer, gemm_flops_per_layer, make_weights
     dev = torch.device("cuda:0")

@@ -21,11 +21,11 @@ DEFAULT_TOKEN_BUDGET = 148 * 128  # one 128-row GEMM tile per SM and tile column
 
 class PackedRunner:
     def __init__(self, enc: Encoder, lengths: Sequence[int], seq_ids: Sequence[int],
-                 token_budget: int = DEFAULT_TOKEN_BUDGET):
+                 token_budget: int = DEFAULT_TOKEN_BUDGET, mix: bool = True):
         self.enc = enc
         self.device = enc.device
         self.hidden = enc.hidden
-        self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget)
+        self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget, mix=mix)
         self.tokens = int(sum(mb.tokens for mb in self.batches))
         self.max_tokens = max([mb.tokens for mb in self.batches] + [1])
         self.max_batch = max([len(mb.seq_ids) for mb in self.batches] + [1])
