@@ -684,32 +684,36 @@ __device__ __forceinline__ bool mbar_wait_role(uint64_t* bar, uint32_t parity, v
 }
 
 constexpr int kPersistentThreads = 256;
-constexpr int kPersistentSmemBytes = 7 * kTileBytes + 256;
+constexpr int kPersistentStages = 2;  // Q, K and V tiles each
+// Q, K, V rings, the softmax warps' output staging (4 x 32 rows x 128 B), barriers
+constexpr int kPersistentSmemBytes = 3 * kPersistentStages * kTileBytes + kTileBytes + 256;
 
 __global__ void __launch_bounds__(kPersistentThreads, 2)
 mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {
-  constexpr int kStages = 3;
+  constexpr int kStages = kPersistentStages;
   constexpr int kSmemQ = 0;
-  constexpr int kSmemK = kSmemQ + kTileBytes;
+  constexpr int kSmemK = kSmemQ + kStages * kTileBytes;
   constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+  constexpr int kSmemOut = kSmemV + kStages * kTileBytes;
+  constexpr int kSmemBar = kSmemOut + kTileBytes;
   constexpr uint32_t kTmemS = 0, kTmemO = 128, kTmemP = 192;
   constexpr float kRescaleThreshold = 8.0f;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   pdl_launch_dependents();
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
-  uint64_t* q_full = bars;
-  uint64_t* q_empty = bars + 1;
-  uint64_t* k_full = bars + 2;                  // [kStages]
-  uint64_t* v_full = bars + 2 + kStages;        // [kStages]
-  uint64_t* kv_empty = bars + 2 + 2 * kStages;  // [kStages]
-  uint64_t* s_full = bars + 2 + 3 * kStages;    // S(j) is in tensor memory
-  uint64_t* s_free = bars + 3 + 3 * kStages;    // the softmax warps hold S(j) in registers (4 arrivals)
-  uint64_t* p_full = bars + 4 + 3 * kStages;    // P(j) is in tensor memory, V rows blanked (4 arrivals)
-  uint64_t* pv_done = bars + 5 + 3 * kStages;   // O += P(j) V(j) has retired
-  uint64_t* o_done = bars + 6 + 3 * kStages;    // the item's last P V has retired
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 3 * kStages);
+  uint64_t* q_full = bars;                     // [kStages] by item
+  uint64_t* q_empty = bars + kStages;          // [kStages] the item's last Q K^T has retired
+  uint64_t* k_full = bars + 2 * kStages;       // [kStages] by key-tile step
+  uint64_t* k_empty = bars + 3 * kStages;      // [kStages] the Q K^T that read the stage has retired
+  uint64_t* v_full = bars + 4 * kStages;       // [kStages] by key-tile step
+  uint64_t* v_empty = bars + 5 * kStages;      // [kStages] the P V that read the stage has retired
+  uint64_t* s_full = bars + 6 * kStages;       // S(j) is in tensor memory
+  uint64_t* s_free = s_full + 1;               // the softmax warps hold S(j) in registers (4 arrivals)
+  uint64_t* p_full = s_full + 2;               // P(j) is in tensor memory, V rows blanked (4 arrivals)
+  uint64_t* pv_done = s_full + 3;              // O += P(j) V(j) has retired
+  uint64_t* o_done = s_full + 4;               // the item's last P V has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -717,12 +721,13 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
   const bool smem_ok = (smem_u32(smem) & 1023u) == 0u;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
     for (int s = 0; s < kStages; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
       mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(s_free, 4);
@@ -761,18 +766,24 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
            ++round) {
         if (lane == 0) {
           const int n_kv = (L + kKvRows - 1) / kKvRows;
-          ok = mbar_wait_role(q_empty, (static_cast<uint32_t>(round) & 1u) ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout);
+          const int qb = round % kStages;
+          const uint32_t qph = static_cast<uint32_t>(round / kStages) & 1u;
+          ok = mbar_wait_role(&q_empty[qb], qph ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout);
           if (ok) {
-          mbar_arrive_expect_tx(q_full, kTileBytes);
-          tma_load_2d(smem + kSmemQ, &tm_qkv, q_full, head * kHeadDim, seq_start + qt * kQRows);
+          mbar_arrive_expect_tx(&q_full[qb], kTileBytes);
+          tma_load_2d(smem + kSmemQ + qb * kTileBytes, &tm_qkv, &q_full[qb], head * kHeadDim, seq_start + qt * kQRows);
           for (int j = 0; j < n_kv; ++j) {
-            if (!mbar_wait_role(&kv_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
+            const int row = seq_start + j * kKvRows;
+            if (!mbar_wait_role(&k_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
               ok = false;
               break;
             }
-            const int row = seq_start + j * kKvRows;
             mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
             tma_load_2d(smem + kSmemK + stage * kTileBytes, &tm_qkv, &k_full[stage], args.hidden + head * kHeadDim, row);
+            if (!mbar_wait_role(&v_empty[stage], phase ^ 1u, abort_flag, args.status, kStatusMhaLoadTimeout)) {
+              ok = false;
+              break;
+            }
             mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
             tma_load_2d(smem + kSmemV + stage * kTileBytes, &tm_qkv, &v_full[stage], 2 * args.hidden + head * kHeadDim,
                         row);
@@ -792,30 +803,44 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
       constexpr uint64_t kDescV = make_smem_desc_hi(kTileBytes, 1024);
       constexpr uint32_t kIdescS = make_idesc_f16(128, 128, 0, 0);
       constexpr uint32_t kIdescO = make_idesc_f16(128, 64, 0, 1);
-      const uint32_t s_q = smem_u32(smem + kSmemQ);
+      const uint32_t s_q0 = smem_u32(smem + kSmemQ);
       const uint32_t s_k = smem_u32(smem + kSmemK);
       const uint32_t s_v = smem_u32(smem + kSmemV);
-      auto issue_s = [&](int stage) {
+      // S = Q(item `round`) K(stage)^T
+      auto issue_s = [&](int round, int stage) {
+        const uint32_t s_q = s_q0 + (round % kStages) * kTileBytes;
         const uint32_t sk = s_k + stage * kTileBytes;
 #pragma unroll
         for (int k = 0; k < kHeadDim / 16; ++k)
           umma_f16_ss(tmem_base + kTmemS, smem_desc(kDescK, s_q + k * 32), smem_desc(kDescK, sk + k * 32), kIdescS,
                       k != 0 ? 1u : 0u);
         umma_commit(s_full);
+        umma_commit(&k_empty[stage]);
       };
+      // the item's Q tile is free once its last Q K^T has been issued (and, by the commit, has retired)
+      auto release_q = [&](int round) { umma_commit(&q_empty[round % kStages]); };
+      auto q_ready = [&](int round) { return static_cast<uint32_t>(round / kStages) & 1u; };
       int st = 0;
       uint32_t ph = 0;
       uint32_t step = 0;
-      // one item: every MMA of it, issued by lane 0; false when a wait gave up
-      auto issue_item = [&](int round) -> bool {
-        const int n_kv = (L + kKvRows - 1) / kKvRows;
+      // The first S = Q K^T of an item whose predecessor could not issue it ahead (lane 0).
+      auto issue_first_s = [&](int round, int len) -> bool {
         // S(0) overwrites the S columns: the softmax warps must hold the previous item's last S in registers
         if (step > 0 && !mbar_wait_role(s_free, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
-        if (!mbar_wait_role(q_full, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
+        if (!mbar_wait_role(&q_full[round % kStages], q_ready(round), abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
         if (!mbar_wait_role(&k_full[st], ph, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
         tc_fence_after();
-        issue_s(st);
-        if (n_kv == 1) umma_commit(q_empty);  // the item's last (only) QK^T has been issued
+        issue_s(round, st);
+        if (len <= kKvRows) release_q(round);  // the item's last (only) QK^T has been issued
+        return true;
+      };
+      // Everything else of an item (lane 0): per key tile the NEXT S as soon as the softmax warps hold the
+      // current one in registers, then O += P V.  On the item's last tile the next S is the first of the
+      // CTA's next item, if its Q and K tiles have landed by then (`next_s_issued`): an item boundary then
+      // costs the softmax warps no S round trip.  false when a wait gave up.
+      auto issue_rest = [&](int round, int len, bool have_next, int len_next, bool& next_s_issued) -> bool {
+        const int n_kv = (len + kKvRows - 1) / kKvRows;
+        next_s_issued = false;
         for (int j = 0; j < n_kv; ++j, ++step) {
           const int st_n = (st + 1 == kStages) ? 0 : st + 1;
           const uint32_t ph_n = (st + 1 == kStages) ? (ph ^ 1u) : ph;
@@ -825,8 +850,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
                 !mbar_wait_role(&k_full[st_n], ph_n, abort_flag, args.status, kStatusMhaMmaTimeout))
               return false;
             tc_fence_after();
-            issue_s(st_n);
-            if (j + 2 == n_kv) umma_commit(q_empty);
+            issue_s(round, st_n);
+            if (j + 2 == n_kv) release_q(round);
+          } else if (have_next) {
+            if (!mbar_wait_role(s_free, step & 1u, abort_flag, args.status, kStatusMhaMmaTimeout)) return false;
+            if (mbar_test_wait(&q_full[(round + 1) % kStages], q_ready(round + 1)) && mbar_test_wait(&k_full[st_n], ph_n)) {
+              tc_fence_after();
+              issue_s(round + 1, st_n);
+              if (len_next <= kKvRows) release_q(round + 1);
+              next_s_issued = true;
+            }
           }
           // P(j) is ready; this also tells that the softmax warps have finished the previous item's O
           // read-out, so the first P V of an item may overwrite O.
@@ -836,14 +869,14 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           tc_fence_after();
           const uint32_t sv = s_v + st * kTileBytes;
           // only the 16-key steps that hold keys of this sequence
-          const int kk_n = (min(kKvRows, L - j * kKvRows) + 15) >> 4;
+          const int kk_n = (min(kKvRows, len - j * kKvRows) + 15) >> 4;
 #pragma unroll
           for (int kk = 0; kk < kKvRows / 16; ++kk)
             if (kk < kk_n)
               umma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + kk * 8, smem_desc(kDescV, sv + kk * 2048), kIdescO,
                           (j > 0 || kk != 0) ? 1u : 0u);
           umma_commit(pv_done);
-          umma_commit(&kv_empty[st]);
+          umma_commit(&v_empty[st]);
           st = st_n;
           ph = ph_n;
         }
@@ -851,10 +884,20 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
         return true;
       };
       bool ok = true;
-      for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
-           ++round) {
-        if (lane == 0) ok = issue_item(round);
+      bool have = decode_item(args, snake_item(0, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+      int len = L;
+      bool s_issued = false;  // S(0) of the item about to start has been issued already
+      for (int round = 0; ok && have; ++round) {
+        if (lane == 0 && !s_issued) ok = issue_first_s(round, len);
+        // the item after this one is found while this item's first tile is on its way
+        const bool have_next = decode_item(args, snake_item(round + 1, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+        const int len_next = L;
+        bool next_s_issued = false;
+        if (lane == 0 && ok) ok = issue_rest(round, len, have_next, len_next, next_s_issued);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        s_issued = __shfl_sync(0xffffffffu, next_s_issued ? 1 : 0, 0) != 0;
+        have = have_next;
+        len = len_next;
       }
     }
   } else {
@@ -870,8 +913,8 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
     uint32_t phase = 0;
     uint32_t step = 0;
     bool ok = smem_ok;
-    for (int round = 0; ok && decode_item(args, snake_item(round, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
-         ++round) {
+    bool have = decode_item(args, snake_item(0, cta, G), cur_b, cur_first, seq_start, L, qt, head, false);
+    for (int round = 0; ok && have; ++round) {
       const int n_kv = (L + kKvRows - 1) / kKvRows;
       float m_ref = -INFINITY;
       float l_run = 0.f;
@@ -974,39 +1017,59 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           phase ^= 1u;
         }
       }
-      if (!ok || !mbar_wait_bounded(o_done, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
+      if (!ok) break;
+      // the next item is found while the last P V of this one runs
+      int seq_start_n = 0, L_n = 0, qt_n = 0, head_n = 0;
+      have = decode_item(args, snake_item(round + 1, cta, G), cur_b, cur_first, seq_start_n, L_n, qt_n, head_n, false);
+      if (!mbar_wait_bounded(o_done, static_cast<uint32_t>(round) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int q_row = qt * kQRows + r;
+      // O / row sum -> fp16 -> this warp's 32 x 128 B staging rows (16-byte units swizzled by the row) ->
+      // global memory with eight threads per row: a store instruction then covers four whole 128-byte
+      // lines instead of 16 bytes of 32 different lines (those took ~2k clocks of the load/store pipe per item).
       const float inv = 1.0f / l_run;
-      uint4* dst = reinterpret_cast<uint4*>(args.ctx + static_cast<size_t>(seq_start + q_row) * args.hidden +
-                                            head * kHeadDim);
+      uint8_t* stage_out = smem + kSmemOut + warp * (32 * 128);
       uint32_t va[32], vb[32];
       tmem_ld_32x32(t_o, va);
       tmem_ld_32x32(t_o + 32, vb);
       tmem_ld_wait();
-      if (q_row < L) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_half2(__uint_as_float(va[u * 8 + 0]) * inv, __uint_as_float(va[u * 8 + 1]) * inv);
-          w.y = pack_half2(__uint_as_float(va[u * 8 + 2]) * inv, __uint_as_float(va[u * 8 + 3]) * inv);
-          w.z = pack_half2(__uint_as_float(va[u * 8 + 4]) * inv, __uint_as_float(va[u * 8 + 5]) * inv);
-          w.w = pack_half2(__uint_as_float(va[u * 8 + 6]) * inv, __uint_as_float(va[u * 8 + 7]) * inv);
-          dst[u] = w;
-        }
+      for (int u = 0; u < 4; ++u) {
+        uint4 w;
+        w.x = pack_half2(__uint_as_float(va[u * 8 + 0]) * inv, __uint_as_float(va[u * 8 + 1]) * inv);
+        w.y = pack_half2(__uint_as_float(va[u * 8 + 2]) * inv, __uint_as_float(va[u * 8 + 3]) * inv);
+        w.z = pack_half2(__uint_as_float(va[u * 8 + 4]) * inv, __uint_as_float(va[u * 8 + 5]) * inv);
+        w.w = pack_half2(__uint_as_float(va[u * 8 + 6]) * inv, __uint_as_float(va[u * 8 + 7]) * inv);
+        *reinterpret_cast<uint4*>(stage_out + lane * 128 + ((u ^ (lane & 7)) << 4)) = w;
+      }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_half2(__uint_as_float(vb[u * 8 + 0]) * inv, __uint_as_float(vb[u * 8 + 1]) * inv);
-          w.y = pack_half2(__uint_as_float(vb[u * 8 + 2]) * inv, __uint_as_float(vb[u * 8 + 3]) * inv);
-          w.z = pack_half2(__uint_as_float(vb[u * 8 + 4]) * inv, __uint_as_float(vb[u * 8 + 5]) * inv);
-          w.w = pack_half2(__uint_as_float(vb[u * 8 + 6]) * inv, __uint_as_float(vb[u * 8 + 7]) * inv);
-          dst[4 + u] = w;
+      for (int u = 0; u < 4; ++u) {
+        uint4 w;
+        w.x = pack_half2(__uint_as_float(vb[u * 8 + 0]) * inv, __uint_as_float(vb[u * 8 + 1]) * inv);
+        w.y = pack_half2(__uint_as_float(vb[u * 8 + 2]) * inv, __uint_as_float(vb[u * 8 + 3]) * inv);
+        w.z = pack_half2(__uint_as_float(vb[u * 8 + 4]) * inv, __uint_as_float(vb[u * 8 + 5]) * inv);
+        w.w = pack_half2(__uint_as_float(vb[u * 8 + 6]) * inv, __uint_as_float(vb[u * 8 + 7]) * inv);
+        *reinterpret_cast<uint4*>(stage_out + lane * 128 + (((4 + u) ^ (lane & 7)) << 4)) = w;
+      }
+      __syncwarp();
+      {
+        const int sub = lane >> 3, unit = lane & 7;  // row within a group of four, 16-byte unit of the row
+        const int row0 = qt * kQRows + warp * 32;     // first query row of this warp's slab, within the sequence
+        __half* out_base = args.ctx + static_cast<size_t>(seq_start + row0) * args.hidden + head * kHeadDim + unit * 8;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int row = 4 * k + sub;
+          const uint4 w = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((unit ^ (row & 7)) << 4));
+          if (row0 + row < L) *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(row) * args.hidden) = w;
         }
       }
+      __syncwarp();  // the staging rows are rewritten at the end of the next item
+      seq_start = seq_start_n;
+      L = L_n;
+      qt = qt_n;
+      head = head_n;
     }
     tc_fence_before();
   }

@@ -69,7 +69,13 @@ class LayerEncoder {
   LayerEncoder(const LayerEncoder&) = delete;
   LayerEncoder& operator=(const LayerEncoder&) = delete;
 
-  Tensor forward(const Tensor& input, const Tensor& attr_mask) {
+  // is_remove_padding = true: the packed path (lengths = valid keys of mask row 0, right padding, padding
+  // rows of the output zero).  false, or an attention_bias: the reference's padded semantics - nothing is
+  // packed, the whole [B,S,S] mask is applied element by element as (1 - mask) * -10000, the optional
+  // [head_num,S,S] bias is added to the scaled scores, every output row is computed
+  // (bytetransformer/th_op/bert_transformer_ext.h:80-111, bytetransformer/include/softmax.h:41-45).
+  Tensor forward(const Tensor& input, const Tensor& attr_mask, bool is_remove_padding = true,
+                 const Tensor& attention_bias = Tensor()) {
     TORCH_CHECK(input.dim() == 3, "input must be [batch, seq_len, hidden]");
     const int batch = static_cast<int>(input.size(0));
     const int seq = static_cast<int>(input.size(1));
@@ -84,6 +90,20 @@ class LayerEncoder {
     TORCH_CHECK(rc == BT_OK, "bt_workspace_bytes failed: ", bt_last_error(handle_));
     Tensor buf = torch::empty({static_cast<int64_t>(bytes)}, torch::dtype(torch::kInt8).device(input.device()));
     cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+    if (!is_remove_padding || attention_bias.defined()) {
+      const void* bias = nullptr;
+      if (attention_bias.defined()) {
+        TORCH_CHECK(attention_bias.is_cuda() && attention_bias.is_contiguous() &&
+                        attention_bias.scalar_type() == input.scalar_type() && attention_bias.dim() == 3 &&
+                        attention_bias.size(1) == seq && attention_bias.size(2) == seq,
+                    "attention_bias must be a contiguous CUDA tensor [head_num, seq_len, seq_len] of the input's type");
+        bias = attention_bias.data_ptr();
+      }
+      rc = bt_layer_forward_padded_general(handle_, 0, input.data_ptr(), attr_mask.data_ptr(), bias, out.data_ptr(),
+                                           buf.data_ptr(), bytes, batch, seq, stream);
+      TORCH_CHECK(rc == BT_OK, "bt_layer_forward_padded_general failed: ", bt_last_error(handle_));
+      return out;
+    }
     rc = bt_layer_forward_padded(handle_, 0, input.data_ptr(), attr_mask.data_ptr(), out.data_ptr(), buf.data_ptr(),
                                  bytes, batch, seq, stream);
     TORCH_CHECK(rc == BT_OK, "bt_layer_forward_padded failed: ", bt_last_error(handle_));
@@ -124,8 +144,7 @@ Tensor TransformerEncoder(int64_t head_num, int64_t head_size, Tensor qkv_kernel
                           Tensor output_kernel, Tensor output_bias, Tensor output_layernorm_gamma,
                           Tensor output_layernorm_beta, Tensor input, Tensor attr_mask, bool is_remove_padding,
                           bool use_fused_attention) {
-  (void)is_remove_padding;    // accepted for compatibility: execution is always padding-free
-  (void)use_fused_attention;  // and attention always fused
+  (void)use_fused_attention;  // accepted for compatibility: attention is fused on both paths, with equal results
   std::vector<Tensor> weights{qkv_kernel,   qkv_bias,      attr_output_kernel,          attr_output_bias,
                               attr_output_layernorm_gamma, attr_output_layernorm_beta,  inter_kernel,
                               inter_bias,   output_kernel, output_bias,                 output_layernorm_gamma,
@@ -135,7 +154,7 @@ Tensor TransformerEncoder(int64_t head_num, int64_t head_size, Tensor qkv_kernel
   BT_CHECK_INPUT(input, st);
   BT_CHECK_INPUT(attr_mask, st);
   LayerEncoder enc(head_num, head_size, weights);
-  return enc.forward(input, attr_mask);
+  return enc.forward(input, attr_mask, is_remove_padding);
 }
 
 class BertTransformer : public torch::jit::CustomClassHolder {
@@ -159,11 +178,19 @@ class BertTransformer : public torch::jit::CustomClassHolder {
   Tensor forward(Tensor input, Tensor attr_mask) { return forwardv2(input, attr_mask, true, true); }
 
   Tensor forwardv2(Tensor input, Tensor attr_mask, bool is_remove_padding, bool use_fused_attention) {
-    (void)is_remove_padding;
     (void)use_fused_attention;
     BT_CHECK_INPUT(input, st_);
     BT_CHECK_INPUT(attr_mask, st_);
-    return enc_->forward(input, attr_mask);
+    return enc_->forward(input, attr_mask, is_remove_padding);
+  }
+
+  // The reference's encoder object takes an optional attention_bias [head_num,S,S] that its operator
+  // schema does not expose (bytetransformer/th_op/bert_transformer_ext.h:83,106); this method does.
+  Tensor forward_with_bias(Tensor input, Tensor attr_mask, Tensor attention_bias) {
+    BT_CHECK_INPUT(input, st_);
+    BT_CHECK_INPUT(attr_mask, st_);
+    BT_CHECK_INPUT(attention_bias, st_);
+    return enc_->forward(input, attr_mask, false, attention_bias);
   }
 
   // 12 weight tensors + int64 [head_num, head_size], the reference's pickle state
@@ -197,6 +224,7 @@ static auto bert_transformer_class =
                               Tensor, Tensor, Tensor, Tensor>())
         .def("forward", &BertTransformer::forward)
         .def("forwardv2", &BertTransformer::forwardv2)
+        .def("forward_with_bias", &BertTransformer::forward_with_bias)
         .def_pickle(
             [](const c10::intrusive_ptr<BertTransformer>& self) -> std::vector<Tensor> {
               return self->get_pickle_info();

@@ -419,16 +419,18 @@ def bert_transformer(head_num: int, head_size: int,
                      use_fused_attention: bool = True, *, ln_eps: float = 1e-6, gelu: str = "erf"):
     """Drop-in for `torch.ops.ByteTransformer.BertTransformer` (ths_op_f.cc:85-95).
 
-    `is_remove_padding` and `use_fused_attention` are accepted for signature
-    compatibility; this library always runs padding-free with fused attention
-    (both settings give the same result on valid rows, padding rows are zero).
-    The encoder object is built per call, as the reference does
-    (bert_transformer_ext.h:86-110)."""
+    is_remove_padding=True: the packed path (lengths = valid keys of mask row 0, right padding, padding rows
+    of the output zero).  False: the reference's padded semantics (nothing packed, the whole [B,S,S] mask
+    applied element by element, every output row computed), which is what a causal or block-diagonal mask
+    needs.  `use_fused_attention` is accepted for signature compatibility: attention is fused on both paths.
+    The encoder object is built per call, as the reference does (bert_transformer_ext.h:86-110)."""
     w = [qkv_kernel, qkv_bias, attr_output_kernel, attr_output_bias, attr_output_layernorm_gamma,
          attr_output_layernorm_beta, inter_kernel, inter_bias, output_kernel, output_bias,
          output_layernorm_gamma, output_layernorm_beta]
     enc = Encoder(head_num, head_size, [w], ln_eps=ln_eps, gelu=gelu)
     try:
+        if not is_remove_padding:
+            return enc.forward_general(input, attr_mask, n_layers=1)
         return enc.forward_layer(0, input, attr_mask)
     finally:
         enc.close()

@@ -9,12 +9,15 @@
 // stream); the object stores raw weight pointers only.  Differences:
 //   * only OperationType::HALF runs (the FP32 template is not built for sm_100a);
 //     constructing the FP32 variant throws std::runtime_error;
-//   * `use_fused_attention` / `is_remove_padding` are accepted and ignored (execution
-//     is always padding-free with fused attention); `cublas_handle`, `cublas_Algo`,
-//     `position_ids`, `token_type_ids` are accepted and unused, as in the reference
-//     for the latter two; a non-NULL `attention_bias` selects the general-mask path (whole
-//     [B,S,S] mask honoured, no padding removal, every output row computed), which is where
-//     the reference applies it too (its unfused softmax);
+//   * `is_remove_padding = false` or a non-NULL `attention_bias` selects the general-mask path: nothing
+//     is packed, the whole [B,S,S] mask is applied element by element as (1 - mask) * -10000, every
+//     output row is computed - the reference's padded path, which is also where it applies the bias
+//     (its unfused softmax).  `is_remove_padding = true` packs by the valid keys of mask row 0 whatever
+//     the batch size (the reference turns packing off for batches of one or two,
+//     bytetransformer/include/bert_transformer.h:135-136; on right-padded masks the valid rows agree).
+//     `use_fused_attention` is accepted and ignored (attention is fused on both paths, equal results);
+//     `cublas_handle`, `cublas_Algo`, `position_ids`, `token_type_ids` are accepted and unused, as in
+//     the reference for the latter two;
 //   * errors surface as std::runtime_error with the library's message, never exit().
 #pragma once
 
@@ -99,9 +102,9 @@ class BertTransformer {
   BertTransformer(const int max_batch_size, const int head_num, const int size_per_head, const int max_seq_len,
                   const bool use_fused_attention = true, const bool is_remove_padding = true,
                   const bool use_fp32 = false, const ModelType model_type = ModelType::Bert)
-      : max_batch_size_(max_batch_size), max_seq_len_(max_seq_len), use_fp32_(use_fp32) {
-    (void)use_fused_attention;
-    (void)is_remove_padding;
+      : max_batch_size_(max_batch_size), max_seq_len_(max_seq_len), use_fp32_(use_fp32),
+        is_remove_padding_(is_remove_padding) {
+    (void)use_fused_attention;  // attention is fused on both paths, with equal results
     (void)model_type;
     if (OpType != OperationType::HALF)
       throw std::runtime_error("bt_b200: only OperationType::HALF is built for sm_100a");
@@ -162,8 +165,9 @@ class BertTransformer {
   void infer(BertTransformerInferParam<DataType_> infer_param) {
     if (!handle_) throw std::runtime_error("bt_b200: initialize() must be called before infer()");
     if (buf_bytes_ == 0) cal_bufsize();
-    if (infer_param.attention_bias != NULL) {
-      // the reference's unfused attention: whole [B,S,S] mask, additive bias, no padding removal
+    if (!is_remove_padding_ || infer_param.attention_bias != NULL) {
+      // the reference's padded path: nothing is packed, the whole [B,S,S] mask is applied element by element
+      // as (1 - mask) * -10000, the optional bias is added, every output row is computed
       check(bt_layer_forward_padded_general(handle_, 0, infer_param.input_tensor, infer_param.atten_mask,
                                             infer_param.attention_bias, infer_param.transformer_output, infer_param.buf,
                                             buf_bytes_, infer_param.batch_size, infer_param.seq_len, infer_param.stream),
@@ -187,6 +191,7 @@ class BertTransformer {
   BertTransformerParam<OpType> param_;
   int max_batch_size_, max_seq_len_;
   bool use_fp32_;
+  bool is_remove_padding_;
   size_t buf_bytes_ = 0;
 };
 

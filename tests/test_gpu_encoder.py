@@ -179,6 +179,50 @@ def test_config4_bert_large_shapes_sampled(cuda_device):
     _run_case(cuda_device, 8, 384, 16, 3, lens, "normal", seed=9)
 
 
+def test_config4_bert_large_full_size(cuda_device):
+    """BASELINE configuration 4 at full size through the padded drop-in entry point: BERT-large (24 layers,
+    hidden 1024, 16 heads), batch 64, max_seq 384, lengths from the seeded truncated normal (13.7k valid
+    tokens: the GEMM + LayerNorm kernels with four column tiles per row tile, 24 layers of error
+    accumulation).  The CPU oracle cannot run the whole batch in test time, so:
+      (a) the batch is run again with its sequences in reverse order: every sequence's rows must come out
+          bit-identical, padding rows exact zeros;
+      (b) all outputs are finite and every valid row is normalised (gamma 1, beta 0);
+      (c) the longest, a middle and the shortest sequence are checked against the oracle run on that
+          sequence alone (max-abs 2e-2, mean-abs 1e-3, the tolerance of the fp16 path)."""
+    from bytetransformer_b200.encoder import Encoder
+    from bytetransformer_b200.workloads import BERT_LARGE, lengths_for, make_weights
+    from oracle.bert_oracle import build_attr_mask
+    dev = cuda_device
+    H, nh, S = BERT_LARGE.hidden, BERT_LARGE.head_num, 384
+    lens = torch.as_tensor(lengths_for("large_b64_s384"))
+    B = int(lens.numel())
+    assert B == 64 and int(lens.max()) <= S
+    weights = make_weights(BERT_LARGE, seed=7, device="cpu")
+    assert len(weights) == 24
+    enc = Encoder(nh, 64, [[t.to(dev) for t in layer] for layer in weights])
+    g = torch.Generator().manual_seed(4004)
+    x = torch.randn(B, S, H, generator=g).half()
+    mask = build_attr_mask(lens, S, torch.float16)
+    out = enc.forward(x.to(dev), mask.to(dev)).cpu()
+    rev = torch.arange(B - 1, -1, -1)
+    out_rev = enc.forward(x[rev].contiguous().to(dev), mask[rev].contiguous().to(dev)).cpu()
+    assert enc.device_status() == 0
+    enc.close()
+    assert torch.equal(out, out_rev[rev]), "rows depend on the position of their sequence in the batch"
+    v = _valid(lens.tolist(), S)
+    assert (out[~v] == 0).all(), "padding rows must be exact zeros"
+    of = out[v].float()
+    assert torch.isfinite(of).all()
+    assert of.mean(dim=1).abs().max().item() < 5e-3
+    assert (of.var(dim=1, unbiased=False) - 1.0).abs().max().item() < 2e-2
+    order = torch.argsort(lens, stable=True)
+    layers32 = [[t.float() for t in layer] for layer in weights]
+    for b in (int(order[-1]), int(order[B // 2]), int(order[0])):
+        L = int(lens[b])
+        want = _oracle(x[b, :L].float()[None], torch.ones(1, L, L), layers32, nh, 64, ln_eps=1e-6)[-1][0]
+        assert_close_fp16(out[b, :L], want, f"config 4, sequence {b} of {L} tokens, 24 layers")
+
+
 def test_packed_entry_matches_padded(cuda_device):
     """bt_stack_forward_packed on x[T,H] + cu_seqlens gives the rows of the padded call."""
     from bytetransformer_b200.encoder import Encoder, build_offsets, pack_rows
@@ -284,5 +328,5 @@ def test_whole_box_workload_full_size_properties(cuda_device):
     layers32 = [[t.float() for t in layer] for layer in weights]
     for sid, (xs, got) in kept.items():
         L = xs.shape[0]
-        want = _oracle(xs.float()[None], torch.ones(1, L, L), layers32, nh, 64)[-1][0]
+        want = _oracle(xs.float()[None], torch.ones(1, L, L), layers32, nh, 64, ln_eps=1e-6)[-1][0]
         assert_close_fp16(got, want, f"sequence {sid} of {L} tokens")

@@ -62,8 +62,10 @@ def test_functional_op_and_class_on_gpu(plugin, cuda_device):
     obj = torch.classes.ByteTransformer.BertTransformer(nh, 64, *wd)
     got2 = obj.forward(x.to(cuda_device), mask.to(cuda_device))
     assert torch.equal(got2, got)
+    # is_remove_padding = False: the padded path computes every row; on a right-padded mask its valid rows agree
     got3 = obj.forwardv2(x.to(cuda_device), mask.to(cuda_device), False, False)
-    assert torch.equal(got3, got)
+    assert_close_fp16(got3.cpu()[valid], want[valid], "th_op class, is_remove_padding=False")
+    assert_close_fp16(got3.cpu()[valid], got.cpu()[valid].float(), "padded path vs packed path", max_abs=8e-3, mean_abs=4e-4)
 
     # fp32 LayerNorm gamma/beta (use_fp32 of the reference) are accepted
     wd32 = to_device_weights(w, cuda_device, gb_fp32=True)
@@ -72,6 +74,34 @@ def test_functional_op_and_class_on_gpu(plugin, cuda_device):
 
     with pytest.raises(RuntimeError):
         torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd, x.float().to(cuda_device), mask.to(cuda_device), True, True)
+
+
+@pytest.mark.gpu
+def test_causal_mask_needs_and_gets_the_padded_path(plugin, cuda_device):
+    """A causal mask through the operator with is_remove_padding=False (the reference's padded semantics:
+    whole [B,S,S] mask applied element by element, bytetransformer/src/attention_fused.cu:234-237,
+    bytetransformer/include/softmax.h:41-45) against the oracle, through the functional op, the class's
+    forwardv2 and, with an additive bias, forward_with_bias."""
+    from oracle.bert_oracle import encoder_layer
+    g = torch.Generator().manual_seed(77)
+    nh, H, B, S = 12, 768, 3, 200
+    w = make_layer_weights(H, g)
+    x = torch.randn(B, S, H, generator=g).half()
+    mask = torch.tril(torch.ones(S, S)).expand(B, S, S).contiguous()
+    want = encoder_layer(x.float(), mask, fp16_round(w), nh, 64, ln_eps=1e-6)
+    wd = to_device_weights(w, cuda_device)
+    xd, md = x.to(cuda_device), mask.half().to(cuda_device)
+    got = torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd, xd, md, False, True)
+    assert_close_fp16(got.cpu(), want, "functional op, causal mask, is_remove_padding=False")
+    obj = torch.classes.ByteTransformer.BertTransformer(nh, 64, *wd)
+    assert torch.equal(obj.forwardv2(xd, md, False, True), got)
+    bias = (torch.randn(nh, S, S, generator=g) * 0.5).half()
+    want_b = encoder_layer(x.float(), mask, fp16_round(w), nh, 64, ln_eps=1e-6, attention_bias=bias.float())
+    got_b = obj.forward_with_bias(xd, md, bias.to(cuda_device))
+    assert_close_fp16(got_b.cpu(), want_b, "class forward_with_bias, causal mask")
+    # with packing on, the same mask means "length 1" (row 0 allows one key): not what a causal mask wants
+    packed = torch.ops.ByteTransformer.BertTransformer(nh, 64, *wd, xd, md, True, True)
+    assert (packed.cpu()[:, 1:] == 0).all()
 
 
 @pytest.mark.gpu

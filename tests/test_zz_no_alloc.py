@@ -40,9 +40,15 @@ def test_static_scratch_matches_workspace_call_twice(cuda_device):
     want = enc.forward_layer(0, x, mask)                      # existing entry point, caller workspace
     for attempt in range(2):
         out = torch.full_like(x, float("nan"))
+        torch.cuda.synchronize(cuda_device)
+        free_before = torch.cuda.mem_get_info(cuda_device)[0]  # cudaMemGetInfo: device-wide free bytes
         rc = lib.bt_layer_forward_padded_static(enc._h, 0, x.data_ptr(), mask.data_ptr(), out.data_ptr(), B, S, stream)
         assert rc == _abi.BT_OK, lib.bt_last_error(enc._h)
         torch.cuda.synchronize(cuda_device)
+        if attempt == 1:
+            # the property the entry point exists for: the call takes no device memory (the first call on a
+            # device may still load the kernels' code, so the second one is the one that is held to it)
+            assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
         # same kernels, same inputs: the tolerance the encoder tests use is far from needed
         d = (out.float() - want.float()).abs()
         assert torch.isfinite(out).all()
