@@ -46,6 +46,12 @@ class bt_layer_weights(C.Structure):
         "output_kernel", "output_bias", "output_layernorm_gamma", "output_layernorm_beta")]
 
 
+class bt_embedding_weights(C.Structure):
+    _fields_ = [("word_emb", C.c_void_p), ("pos_emb", C.c_void_p), ("type_emb", C.c_void_p), ("gamma", C.c_void_p),
+                ("beta", C.c_void_p), ("gamma_beta_fp32", C.c_int), ("vocab_size", C.c_int),
+                ("max_positions", C.c_int), ("type_vocab_size", C.c_int), ("eps", C.c_float)]
+
+
 _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); one entry per declaration in include/bt_b200.h
@@ -60,6 +66,8 @@ SIGNATURES = {
     "bt_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "bt_embedding_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "bt_pooler": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "bt_embedding_layernorm_packed": (_i, [C.POINTER(bt_embedding_weights), _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "bt_stack_forward_ids": (_i, [_vp, _i, C.POINTER(bt_embedding_weights), _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
     "bt_selftest_bounded_wait": (_i, [_vp, C.c_longlong, _vp, _vp]),
     "bt_layer_forward_padded": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _sz, _i, _i, _vp]),
     "bt_layer_forward_padded_static": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp]),

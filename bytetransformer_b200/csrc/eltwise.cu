@@ -221,7 +221,11 @@ cudaError_t launch_ln_nvec(int nvec_needed, dim3 grid, cudaStream_t stream, cons
   return cudaGetLastError();
 }
 
-__global__ void __launch_bounds__(256)
+// x[row, :] = gelu(x[row, :] + bias), in place.  A thread owns one 16-byte column vector (its bias slice
+// is read once) and walks down the rows, four rows per trip so that four loads are in flight; the exact-form
+// GELU costs one special-function op per element (gelu_erf_fast).  blockIdx.x selects the column block,
+// blockIdx.y the first row.
+__global__ void __launch_bounds__(128)
 add_bias_gelu_kernel(uint4* __restrict__ x, const uint4* __restrict__ bias, const int* __restrict__ m_dev,
                      int m_rows, int nvec, int gelu_kind) {
   pdl_launch_dependents();
@@ -231,22 +235,41 @@ add_bias_gelu_kernel(uint4* __restrict__ x, const uint4* __restrict__ bias, cons
     const int md = __ldg(m_dev);
     M = md < M ? md : M;
   }
-  const long long total = static_cast<long long>(M) * nvec;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int v = static_cast<int>(i % nvec);
-    float f[8], b[8];
-    unpack8(x[i], f);
-    unpack8(__ldg(bias + v), b);
-    if (gelu_kind == BT_GELU_TANH) {
+  const int v = static_cast<int>(blockIdx.x * blockDim.x + threadIdx.x);
+  if (v >= nvec) return;
+  float b[8];
+  unpack8(__ldg(bias + v), b);
+  const int stride = static_cast<int>(gridDim.y);
+  for (int r0 = static_cast<int>(blockIdx.y); r0 < M; r0 += 4 * stride) {
+    uint4 in[4];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] = gelu_tanh(f[k] + b[k]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + b[k]);
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + u * stride;
+      if (r < M) in[u] = x[static_cast<size_t>(r) * nvec + v];
     }
-    x[i] = pack8(f);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + u * stride;
+      if (r < M) {
+        float f[8];
+        unpack8(in[u], f);
+        if (gelu_kind == BT_GELU_TANH) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = gelu_tanh(f[k] + b[k]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = gelu_erf_fast(f[k] + b[k]);
+        }
+        x[static_cast<size_t>(r) * nvec + v] = pack8(f);
+      }
+    }
   }
+}
+
+__device__ __forceinline__ float exp2f_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // One warp per logits row; logits are laid out [nh, B, S, S] as in the reference
@@ -268,6 +291,7 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
   const __half* mp = mask + (static_cast<long long>(b) * S + i) * S;
   if (VEC) {
     const int nvec = S / 8;
+    const float scale_l2 = scale * 1.4426950408889634f;
     float val[4][8];
     float mx = -INFINITY;
 #pragma unroll
@@ -277,9 +301,10 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
         float m[8];
         unpack8(*(reinterpret_cast<const uint4*>(lp) + v), val[it]);
         unpack8(__ldg(reinterpret_cast<const uint4*>(mp) + v), m);
+        // in units of log2: logit * scale * log2(e) + (1 - mask) * (-10000 * log2(e)); exp(x) = 2^(x log2 e)
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          val[it][k] = fmaf(val[it][k], scale, (1.0f - m[k]) * -10000.0f);
+          val[it][k] = fmaf(val[it][k], scale_l2, fmaf(m[k], 14426.950408889634f, -14426.950408889634f));
           mx = fmaxf(mx, val[it][k]);
         }
       }
@@ -291,7 +316,7 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
       if (it * 32 + lane < nvec) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          val[it][k] = __expf(val[it][k] - mx);
+          val[it][k] = exp2f_fast(val[it][k] - mx);
           sum += val[it][k];
         }
       }
@@ -390,11 +415,13 @@ cudaError_t launch_add_bias_gelu(__half* x, const __half* bias, const int* m_dev
                                  cudaStream_t stream) {
   if (n % 8 != 0 || m_rows <= 0) return cudaErrorInvalidValue;
   const int nvec = n / 8;
-  long long total = static_cast<long long>(m_rows) * nvec;
-  long long g = (total + 256 * 2 - 1) / (256 * 2);
-  if (g < 1) g = 1;
-  if (g > 148 * 16) g = 148 * 16;
-  return launch_pdl(add_bias_gelu_kernel, dim3(static_cast<unsigned>(g)), dim3(256), 0, stream,
+  const unsigned gx = static_cast<unsigned>((nvec + 127) / 128);
+  // enough row groups for ~16 CTAs per SM, never more than rows
+  long long gy = (148LL * 16 + gx - 1) / gx;
+  if (gy > m_rows) gy = m_rows;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  return launch_pdl(add_bias_gelu_kernel, dim3(gx, static_cast<unsigned>(gy)), dim3(128), 0, stream,
                     reinterpret_cast<uint4*>(x), reinterpret_cast<const uint4*>(bias), m_dev, m_rows, nvec, gelu_kind);
 }
 

@@ -29,20 +29,28 @@ embedding_layernorm_kernel(const __half* __restrict__ word_emb, const __half* __
                            const void* __restrict__ beta, const int* __restrict__ token_ids,
                            const int* __restrict__ type_ids, const int* __restrict__ position_ids,
                            __half* __restrict__ out, int rows, int seq_len, int hidden, int vocab, int max_pos,
-                           int n_types, float eps) {
+                           int n_types, float eps, const int* __restrict__ word_idx, const int* __restrict__ t_dev) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nvec = hidden >> 3;
   const float inv_h = 1.0f / static_cast<float>(hidden);
+  // Packed output (word_idx != null): output row r is the r-th valid token, whose ids sit at padded
+  // position word_idx[r]; rows from *t_dev (the packed token count) on do not exist.  The padded
+  // [B,S,H] tensor is then never written nor read again by a pack step.
+  if (word_idx != nullptr) {
+    const int t = __ldg(t_dev);
+    rows = t < rows ? t : rows;
+  }
   for (int row = blockIdx.x * kEmbWarps + warp; row < rows; row += gridDim.x * kEmbWarps) {
+    const int src = word_idx != nullptr ? __ldg(word_idx + row) : row;
     // ids outside their table are clamped (the tables are the caller's; no fault on bad input)
-    int tok = __ldg(token_ids + row);
+    int tok = __ldg(token_ids + src);
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-    int pos = position_ids != nullptr ? __ldg(position_ids + row) : row % seq_len;
+    int pos = position_ids != nullptr ? __ldg(position_ids + src) : src % seq_len;
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-    int typ = type_ids != nullptr ? __ldg(type_ids + row) : 0;
+    int typ = type_ids != nullptr ? __ldg(type_ids + src) : 0;
     typ = typ < 0 ? 0 : (typ >= n_types ? n_types - 1 : typ);
     const uint4* w4 = reinterpret_cast<const uint4*>(word_emb + static_cast<size_t>(tok) * hidden);
     const uint4* p4 = reinterpret_cast<const uint4*>(pos_emb + static_cast<size_t>(pos) * hidden);
@@ -168,13 +176,13 @@ template <bool GB_FP32>
 cudaError_t launch_emb(int nvec_per_lane, dim3 grid, cudaStream_t stream, const __half* word_emb, const __half* pos_emb,
                        const __half* type_emb, const void* gamma, const void* beta, const int* token_ids,
                        const int* type_ids, const int* position_ids, __half* out, int rows, int seq_len, int hidden,
-                       int vocab, int max_pos, int n_types, float eps) {
+                       int vocab, int max_pos, int n_types, float eps, const int* word_idx, const int* t_dev) {
   dim3 block(kEmbWarps * 32);
   switch (nvec_per_lane) {
-    case 1: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 1>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps);
-    case 2: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 2>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps);
-    case 3: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 3>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps);
-    case 4: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 4>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps);
+    case 1: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 1>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev);
+    case 2: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 2>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev);
+    case 3: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 3>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev);
+    case 4: return launch_pdl(embedding_layernorm_kernel<GB_FP32, 4>, grid, block, 0, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -184,14 +192,16 @@ cudaError_t launch_emb(int nvec_per_lane, dim3 grid, cudaStream_t stream, const 
 cudaError_t launch_embedding_layernorm(const __half* word_emb, const __half* pos_emb, const __half* type_emb,
                                        const void* gamma, const void* beta, bool gb_fp32, const int* token_ids,
                                        const int* type_ids, const int* position_ids, __half* out, int rows, int seq_len,
-                                       int hidden, int vocab, int max_pos, int n_types, float eps, cudaStream_t stream) {
+                                       int hidden, int vocab, int max_pos, int n_types, float eps, cudaStream_t stream,
+                                       const int* word_idx, const int* t_dev) {
   if (rows <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 1024 || seq_len <= 0) return cudaErrorInvalidValue;
+  if ((word_idx == nullptr) != (t_dev == nullptr)) return cudaErrorInvalidValue;
   const int nvec_per_lane = (hidden / 8 + 31) / 32;
   long long g = (static_cast<long long>(rows) + kEmbWarps - 1) / kEmbWarps;
   if (g > 148 * 16) g = 148 * 16;
   dim3 grid(static_cast<unsigned>(g));
-  return gb_fp32 ? launch_emb<true>(nvec_per_lane, grid, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps)
-                 : launch_emb<false>(nvec_per_lane, grid, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps);
+  return gb_fp32 ? launch_emb<true>(nvec_per_lane, grid, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev)
+                 : launch_emb<false>(nvec_per_lane, grid, stream, word_emb, pos_emb, type_emb, gamma, beta, token_ids, type_ids, position_ids, out, rows, seq_len, hidden, vocab, max_pos, n_types, eps, word_idx, t_dev);
 }
 
 cudaError_t launch_pooler(const __half* y, const __half* W, const __half* bias, __half* pooled, int B, int seq_len,

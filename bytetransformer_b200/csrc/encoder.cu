@@ -447,15 +447,41 @@ static int check_shape(bt_handle h, int B, int S) {
   return BT_OK;
 }
 
+// Where the packed activation of a padded call comes from: the padded input tensor (pack), or token ids
+// through the embedding tables (the front end writes packed rows directly).
+struct IdsInput {
+  const bt_embedding_weights* emb;
+  const int* token_ids;
+  const int* type_ids;
+  const int* position_ids;
+};
+
+static int check_embedding(bt_handle h, const bt_embedding_weights* e, int hidden) {
+  if (!e || !e->word_emb || !e->pos_emb || !e->type_emb || !e->gamma || !e->beta)
+    return fail(h, BT_ERR_INVALID_ARG, "null embedding table / LayerNorm parameter");
+  if (e->vocab_size <= 0 || e->max_positions <= 0 || e->type_vocab_size <= 0 || !(e->eps >= 0.f))
+    return fail(h, BT_ERR_INVALID_ARG, "bad embedding table sizes or eps");
+  if (hidden <= 0 || hidden % 8 != 0 || hidden > 1024) return fail(h, BT_ERR_INVALID_ARG, "hidden must be a multiple of 8, at most 1024");
+  if (!aligned16(e->word_emb) || !aligned16(e->pos_emb) || !aligned16(e->type_emb) || !aligned16(e->gamma) ||
+      !aligned16(e->beta))
+    return fail(h, BT_ERR_INVALID_ARG, "embedding tables and LayerNorm parameters must be 16-byte aligned");
+  return BT_OK;
+}
+
 static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* input, const void* mask, void* out,
-                        void* workspace, size_t workspace_bytes, int B, int S, void* stream_v) {
+                        void* workspace, size_t workspace_bytes, int B, int S, void* stream_v,
+                        const IdsInput* ids = nullptr) {
   int rc = check_shape(h, B, S);
   if (rc != BT_OK) return rc;
-  if (!input || !mask || !out || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
+  if ((!input && !ids) || !mask || !out || !workspace) return fail(h, BT_ERR_INVALID_ARG, "null pointer argument");
   if (input == out) return fail(h, BT_ERR_INVALID_ARG, "input and output must not alias");
   if (n_layers <= 0) return fail(h, BT_ERR_INVALID_ARG, "n_layers must be positive");
   if (!aligned16(input) || !aligned16(mask) || !aligned16(out))
     return fail(h, BT_ERR_INVALID_ARG, "input, attr_mask and output must be 16-byte aligned");
+  if (ids != nullptr) {
+    if (!ids->token_ids) return fail(h, BT_ERR_INVALID_ARG, "null token_ids");
+    if ((rc = check_embedding(h, ids->emb, h->hidden)) != BT_OK) return rc;
+  }
   if ((rc = check_device(h)) != BT_OK) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const size_t rows = static_cast<size_t>(B) * S;
@@ -472,7 +498,15 @@ static int stack_padded(bt_handle h, int first_layer, int n_layers, const void* 
     e = launch_build_offsets(reinterpret_cast<const __half*>(mask), B, S, ws.batch_idx, ws.word_idx, stream);
   }
   if (e != cudaSuccess) return fail_cuda(h, e, "offsets launch");
-  {
+  if (ids != nullptr) {
+    const bt_embedding_weights& w = *ids->emb;
+    LaunchScope scope(h, BT_PROF_PACK, stream);
+    e = launch_embedding_layernorm(reinterpret_cast<const __half*>(w.word_emb), reinterpret_cast<const __half*>(w.pos_emb),
+                                   reinterpret_cast<const __half*>(w.type_emb), w.gamma, w.beta, w.gamma_beta_fp32 != 0,
+                                   ids->token_ids, ids->type_ids, ids->position_ids, ws.xa, static_cast<int>(rows), S,
+                                   h->hidden, w.vocab_size, w.max_positions, w.type_vocab_size, w.eps, stream, ws.word_idx,
+                                   ws.batch_idx + B);
+  } else {
     LaunchScope scope(h, BT_PROF_PACK, stream);
     e = launch_pack_rows(reinterpret_cast<const __half*>(input), ws.xa, ws.batch_idx, B, S, h->hidden, stream);
   }
@@ -689,6 +723,31 @@ int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void
       reinterpret_cast<__half*>(out), batch_size * seq_len, seq_len, hidden, vocab_size, max_positions, type_vocab_size,
       eps, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_embedding_layernorm_packed(const bt_embedding_weights* emb, const int* token_ids, const int* type_ids,
+                                  const int* position_ids, const int* batch_idx, const int* word_idx,
+                                  void* out_packed, int batch_size, int seq_len, int hidden, void* stream) {
+  if (!token_ids || !batch_idx || !word_idx || !out_packed || !aligned16(out_packed)) return BT_ERR_INVALID_ARG;
+  if (batch_size <= 0 || seq_len <= 0 || static_cast<long long>(batch_size) * seq_len > 0x7fffffffLL) return BT_ERR_INVALID_ARG;
+  const int rc = check_embedding(nullptr, emb, hidden);
+  if (rc != BT_OK) return rc;
+  cudaError_t e = launch_embedding_layernorm(
+      reinterpret_cast<const __half*>(emb->word_emb), reinterpret_cast<const __half*>(emb->pos_emb),
+      reinterpret_cast<const __half*>(emb->type_emb), emb->gamma, emb->beta, emb->gamma_beta_fp32 != 0, token_ids, type_ids,
+      position_ids, reinterpret_cast<__half*>(out_packed), batch_size * seq_len, seq_len, hidden, emb->vocab_size,
+      emb->max_positions, emb->type_vocab_size, emb->eps, reinterpret_cast<cudaStream_t>(stream), word_idx,
+      batch_idx + batch_size);
+  return e == cudaSuccess ? BT_OK : BT_ERR_CUDA;
+}
+
+int bt_stack_forward_ids(bt_handle h, int n_layers, const bt_embedding_weights* emb, const int* token_ids,
+                         const int* type_ids, const int* position_ids, const void* attr_mask, void* out,
+                         void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream) {
+  if (!h) return BT_ERR_INVALID_ARG;
+  IdsInput ids{emb, token_ids, type_ids, position_ids};
+  return stack_padded(h, 0, n_layers, nullptr, attr_mask, out, workspace, workspace_bytes, batch_size, seq_len, stream,
+                      &ids);
 }
 
 int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* pooled, int batch_size, int seq_len,

@@ -145,10 +145,13 @@ int* device_status_word();
 // ---- embedding front end / pooler back end -------------------------------------
 // out[row,:] = LayerNorm(word[token] + pos[position] + type[type]) * gamma + beta; position = row % seq_len
 // when position_ids is null, type 0 when type_ids is null; ids are clamped into their tables.
+// With `word_idx` / `t_dev` (both or neither): packed output - row r is the r-th valid token, its ids at
+// padded position word_idx[r], rows from *t_dev on are not written.
 cudaError_t launch_embedding_layernorm(const __half* word_emb, const __half* pos_emb, const __half* type_emb,
                                        const void* gamma, const void* beta, bool gb_fp32, const int* token_ids,
                                        const int* type_ids, const int* position_ids, __half* out, int rows, int seq_len,
-                                       int hidden, int vocab, int max_pos, int n_types, float eps, cudaStream_t stream);
+                                       int hidden, int vocab, int max_pos, int n_types, float eps, cudaStream_t stream,
+                                       const int* word_idx = nullptr, const int* t_dev = nullptr);
 // pooled[b,:] = tanh(y[b,0,:] * W + bias), W [hidden, hidden] row-major [in,out]
 cudaError_t launch_pooler(const __half* y, const __half* W, const __half* bias, __half* pooled, int B, int seq_len,
                           int hidden, cudaStream_t stream);

@@ -627,22 +627,6 @@ __device__ __forceinline__ int snake_item(int round, int cta, int ctas) {
   return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
 }
 
-// tcgen05.ld 32x32b.x32 into elements [B, B + 32) of a 128-element register array (no address of the array
-// is formed, so it stays in registers).
-template <int B>
-__device__ __forceinline__ void tmem_ld_32x32_at(uint32_t taddr, uint32_t (&r)[128]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[B + 0]), "=r"(r[B + 1]), "=r"(r[B + 2]), "=r"(r[B + 3]), "=r"(r[B + 4]), "=r"(r[B + 5]), "=r"(r[B + 6]),
-        "=r"(r[B + 7]), "=r"(r[B + 8]), "=r"(r[B + 9]), "=r"(r[B + 10]), "=r"(r[B + 11]), "=r"(r[B + 12]), "=r"(r[B + 13]),
-        "=r"(r[B + 14]), "=r"(r[B + 15]), "=r"(r[B + 16]), "=r"(r[B + 17]), "=r"(r[B + 18]), "=r"(r[B + 19]), "=r"(r[B + 20]),
-        "=r"(r[B + 21]), "=r"(r[B + 22]), "=r"(r[B + 23]), "=r"(r[B + 24]), "=r"(r[B + 25]), "=r"(r[B + 26]), "=r"(r[B + 27]),
-        "=r"(r[B + 28]), "=r"(r[B + 29]), "=r"(r[B + 30]), "=r"(r[B + 31])
-      : "r"(taddr)
-      : "memory");
-}
 template <int B>
 __device__ __forceinline__ void tmem_st_32x16_at(uint32_t taddr, const uint32_t (&r)[64]) {
   asm volatile(

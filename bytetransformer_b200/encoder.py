@@ -170,6 +170,36 @@ class Encoder:
                        ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
         return out
 
+    def forward_ids(self, emb: "EmbeddingWeights", token_ids: torch.Tensor, attr_mask: torch.Tensor,
+                    type_ids: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
+                    n_layers: Optional[int] = None) -> torch.Tensor:
+        """The whole model front to back: embeddings of the valid tokens straight into the packed
+        activation, all layers, scatter once (the padded input tensor never exists)."""
+        _check(token_ids, "token_ids", torch.int32)
+        _check(attr_mask, "attr_mask", torch.float16)
+        if token_ids.dim() != 2 or attr_mask.dim() != 3:
+            raise RuntimeError("token_ids must be [batch, seq_len], attr_mask [batch, seq_len, seq_len]")
+        B, S = int(token_ids.shape[0]), int(token_ids.shape[1])
+        if tuple(attr_mask.shape) != (B, S, S):
+            raise RuntimeError("attr_mask must be [batch, seq_len, seq_len]")
+        for t, n in ((type_ids, "type_ids"), (position_ids, "position_ids")):
+            if t is not None:
+                _check(t, n, torch.int32)
+                if tuple(t.shape) != (B, S):
+                    raise RuntimeError(f"{n} must be [batch, seq_len]")
+        nl = self.n_layers if n_layers is None else int(n_layers)
+        with torch.cuda.device(self.device):
+            out = torch.empty(B, S, self.hidden, dtype=torch.float16, device=self.device)
+            n = C.c_size_t()
+            self._call("bt_workspace_bytes", self._h, B, S, C.byref(n))
+            ws = self._workspace(n.value)
+            w = emb.as_struct()
+            self._call("bt_stack_forward_ids", self._h, nl, C.byref(w), token_ids.data_ptr(),
+                       type_ids.data_ptr() if type_ids is not None else None,
+                       position_ids.data_ptr() if position_ids is not None else None, attr_mask.data_ptr(),
+                       out.data_ptr(), ws.data_ptr(), ws.numel(), B, S, _stream_ptr(self.device))
+        return out
+
     def forward_general(self, x: torch.Tensor, attr_mask: torch.Tensor, attention_bias: Optional[torch.Tensor] = None,
                         n_layers: Optional[int] = None) -> torch.Tensor:
         """All layers with the reference's padded-path attention semantics: nothing is packed, the whole
@@ -285,6 +315,45 @@ def embedding_layernorm(word_emb: torch.Tensor, pos_emb: torch.Tensor, type_emb:
                                         float(eps), _stream_ptr(word_emb.device))
     if rc != 0:
         raise _abi.BtError(rc, "bt_embedding_layernorm")
+    return out
+
+
+class EmbeddingWeights:
+    """Tables and LayerNorm parameters of the embedding front end (fp16 tables, gamma/beta fp16 or fp32)."""
+
+    def __init__(self, word_emb, pos_emb, type_emb, gamma, beta, eps: float = 1e-6):
+        for t, n in ((word_emb, "word_emb"), (pos_emb, "pos_emb"), (type_emb, "type_emb")):
+            _check(t, n, torch.float16)
+        self.gb32 = gamma.dtype == torch.float32
+        _check(gamma, "gamma", torch.float32 if self.gb32 else torch.float16)
+        _check(beta, "beta", torch.float32 if self.gb32 else torch.float16)
+        self.tensors = (word_emb, pos_emb, type_emb, gamma, beta)   # keeps the device memory alive
+        self.eps = float(eps)
+
+    def as_struct(self) -> "_abi.bt_embedding_weights":
+        w, p, t, g, b = self.tensors
+        return _abi.bt_embedding_weights(w.data_ptr(), p.data_ptr(), t.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                         1 if self.gb32 else 0, int(w.shape[0]), int(p.shape[0]), int(t.shape[0]), self.eps)
+
+
+def embedding_layernorm_packed(emb: EmbeddingWeights, token_ids: torch.Tensor, batch_idx: torch.Tensor,
+                               word_idx: torch.Tensor, type_ids: Optional[torch.Tensor] = None,
+                               position_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Embedding + LayerNorm of the valid tokens only, packed: row r of the result is the token at padded
+    position word_idx[r] (offsets from build_offsets); rows from the token count on stay zero."""
+    _check(token_ids, "token_ids", torch.int32)
+    _check(batch_idx, "batch_idx", torch.int32)
+    _check(word_idx, "word_idx", torch.int32)
+    B, S = int(token_ids.shape[0]), int(token_ids.shape[1])
+    H = int(emb.tensors[0].shape[1])
+    out = torch.zeros(B * S, H, dtype=torch.float16, device=token_ids.device)
+    w = emb.as_struct()
+    rc = _abi.load().bt_embedding_layernorm_packed(
+        C.byref(w), token_ids.data_ptr(), type_ids.data_ptr() if type_ids is not None else None,
+        position_ids.data_ptr() if position_ids is not None else None, batch_idx.data_ptr(), word_idx.data_ptr(),
+        out.data_ptr(), B, S, H, _stream_ptr(token_ids.device))
+    if rc != _abi.BT_OK:
+        raise RuntimeError(f"bt_embedding_layernorm_packed failed ({_abi.ERROR_NAMES.get(rc, rc)})")
     return out
 
 

@@ -317,6 +317,37 @@ int bt_embedding_layernorm(const void* word_emb, const void* pos_emb, const void
 int bt_pooler(const void* encoder_out, const void* W, const void* bias, void* pooled, int batch_size,
               int seq_len, int hidden, void* stream);
 
+/* The embedding front end fused with packing (the fusion the reference's unused kernel hints at,
+ * bytetransformer/include/layernorm.h:219-240): the tables and LayerNorm parameters of the front end,
+ * fp16 tables row-major, gamma/beta fp16 or fp32 (gamma_beta_fp32), ids clamped into their tables. */
+typedef struct bt_embedding_weights {
+  const void* word_emb;     /* [vocab_size, hidden] */
+  const void* pos_emb;      /* [max_positions, hidden] */
+  const void* type_emb;     /* [type_vocab_size, hidden] */
+  const void* gamma;        /* [hidden] */
+  const void* beta;         /* [hidden] */
+  int gamma_beta_fp32;
+  int vocab_size;
+  int max_positions;
+  int type_vocab_size;
+  float eps;
+} bt_embedding_weights;
+/* bt_embedding_layernorm_packed: like bt_embedding_layernorm, but writes only the valid tokens, packed:
+ *   out_packed[r,:] for r < batch_idx[batch_size] is the row of the token at padded position word_idx[r]
+ *   (batch_idx / word_idx as bt_build_offsets produces them; the token count stays on the device).
+ *   out_packed must hold batch_size*seq_len rows at most; rows from the token count on are not written.
+ * bt_stack_forward_ids: the whole model front to back in one call - offsets from attr_mask, embeddings of
+ *   the valid tokens straight into the packed activation (the padded [B,S,H] input tensor never exists),
+ *   n_layers encoder layers, LayerNorm + scatter into out[batch_size, seq_len, hidden] with zero padding
+ *   rows.  token_ids int32 [batch_size, seq_len]; type_ids / position_ids may be NULL (type 0, position =
+ *   index in the sequence).  Workspace as for bt_stack_forward_padded (bt_workspace_bytes). */
+int bt_embedding_layernorm_packed(const bt_embedding_weights* emb, const int* token_ids, const int* type_ids,
+                                  const int* position_ids, const int* batch_idx, const int* word_idx,
+                                  void* out_packed, int batch_size, int seq_len, int hidden, void* stream);
+int bt_stack_forward_ids(bt_handle h, int n_layers, const bt_embedding_weights* emb, const int* token_ids,
+                         const int* type_ids, const int* position_ids, const void* attr_mask, void* out,
+                         void* workspace, size_t workspace_bytes, int batch_size, int seq_len, void* stream);
+
 /* on != 0: reset the counters and bracket every kernel the handle launches with
  * CUDA events on the launching stream; on == 0: stop timing (counting goes on).
  * Replaces the reference's unused timing events (src/bert_transformer.cu:89-93). */

@@ -58,3 +58,67 @@ def test_pooler(cuda_device, B, S, H):
     b = torch.empty(H).uniform_(-0.4, 0.4, generator=g).half()
     got = pooler(y.to(cuda_device), W.to(cuda_device), b.to(cuda_device))
     assert_close_fp16(got, ref(y, W, b), "pooler", max_abs=3e-3, mean_abs=3e-4)
+
+
+@pytest.mark.parametrize("B,S,H,gb32", [(6, 40, 768, False), (3, 129, 1024, True), (40, 17, 256, False)])
+def test_embedding_written_packed_matches_embedding_then_pack(cuda_device, B, S, H, gb32):
+    """The embedding front end fused with packing: rows of the valid tokens only, in packed order, bit for
+    bit the rows that the unfused embedding followed by pack_rows gives (same arithmetic, other placement),
+    and close to the fp32 definition; rows beyond the token count are not written."""
+    from bytetransformer_b200.encoder import (EmbeddingWeights, build_offsets, embedding_layernorm,
+                                              embedding_layernorm_packed, pack_rows)
+    from oracle.bert_oracle import build_attr_mask, build_offsets as ref_offsets, embedding_layernorm as ref
+    dev = cuda_device
+    g = torch.Generator().manual_seed(7 * B + S)
+    V, P, Tn = 500, 200, 2
+    word = torch.randn(V, H, generator=g).half()
+    pos = (torch.randn(P, H, generator=g) * 0.5).half()
+    typ = (torch.randn(Tn, H, generator=g) * 0.5).half()
+    gamma = torch.empty(H).uniform_(0.5, 1.5, generator=g)
+    beta = torch.empty(H).uniform_(-0.4, 0.4, generator=g)
+    gd, bd = (gamma, beta) if gb32 else (gamma.half(), beta.half())
+    tok = torch.randint(0, V, (B, S), generator=g, dtype=torch.int32)
+    tids = torch.randint(0, Tn, (B, S), generator=g, dtype=torch.int32)
+    lens = torch.randint(0, S + 1, (B,), generator=g)
+    lens[0] = S
+    mask = build_attr_mask(lens, S, torch.float16).to(dev)
+    bi, wi = build_offsets(mask)
+    T = int(bi[-1].item())
+    emb = EmbeddingWeights(word.to(dev), pos.to(dev), typ.to(dev), gd.to(dev), bd.to(dev), eps=1e-6)
+    got = embedding_layernorm_packed(emb, tok.to(dev), bi, wi, type_ids=tids.to(dev))
+    padded = embedding_layernorm(word.to(dev), pos.to(dev), typ.to(dev), gd.to(dev), bd.to(dev), tok.to(dev), tids.to(dev), None, eps=1e-6)
+    want_packed = pack_rows(padded, bi)[:T]
+    assert torch.equal(got[:T], want_packed)                     # bit-exact placement and values
+    assert (got[T:] == 0).all()                                  # nothing written past the token count
+    ref_bi, ref_wi = ref_offsets(mask.cpu().float())
+    full = ref(word, pos, typ, gd, bd, tok, tids, None, eps=1e-6).reshape(B * S, H)
+    assert_close_fp16(got[:T], full[torch.as_tensor(ref_wi[:T]).long()], "packed embedding vs fp32 definition",
+                      max_abs=4e-3, mean_abs=4e-4)
+
+
+def test_stack_from_token_ids_matches_embedding_then_stack(cuda_device):
+    """bt_stack_forward_ids = embedding + LayerNorm (packed) -> layers -> scatter, in one call: the same
+    numbers as the padded embedding followed by the padded stack (bit for bit: the packed rows are the
+    same values and the layers run on them identically)."""
+    from bytetransformer_b200.encoder import Encoder, EmbeddingWeights, embedding_layernorm
+    from helpers import make_layer_weights, to_device_weights
+    from oracle.bert_oracle import build_attr_mask
+    dev = cuda_device
+    g = torch.Generator().manual_seed(2024)
+    nh, H, B, S, V = 12, 768, 5, 96, 300
+    layers = [to_device_weights(make_layer_weights(H, g), dev) for _ in range(2)]
+    word = (torch.randn(V, H, generator=g)).half().to(dev)
+    pos = (torch.randn(S, H, generator=g) * 0.5).half().to(dev)
+    typ = (torch.randn(2, H, generator=g) * 0.5).half().to(dev)
+    gamma, beta = torch.ones(H).half().to(dev), torch.zeros(H).half().to(dev)
+    tok = torch.randint(0, V, (B, S), generator=g, dtype=torch.int32).to(dev)
+    lens = torch.tensor([96, 1, 0, 50, 77])
+    mask = build_attr_mask(lens, S, torch.float16).to(dev)
+    enc = Encoder(nh, 64, layers)
+    emb = EmbeddingWeights(word, pos, typ, gamma, beta, eps=1e-6)
+    got = enc.forward_ids(emb, tok, mask)
+    x = embedding_layernorm(word, pos, typ, gamma, beta, tok, eps=1e-6)
+    want = enc.forward(x, mask)
+    assert enc.device_status() == 0
+    enc.close()
+    assert torch.equal(got, want)
