@@ -272,9 +272,12 @@ __device__ __forceinline__ float exp2f_fast(float x) {
   return y;
 }
 
-// One warp per logits row; logits are laid out [nh, B, S, S] as in the reference
-// (softmax.h:33: ((head*B + b)*S + i)*S); S <= 1024.  VEC path: S % 8 == 0.
-template <bool VEC>
+// Logits are laid out [nh, B, S, S] as in the reference (softmax.h:33: ((head*B + b)*S + i)*S); S <= 1024.
+// VEC path (S % 8 == 0): a warp owns one (b, i) row of the mask and walks the nh heads' logits rows that
+// share it, so the additive term (1 - mask) * -10000 is read and converted once per nh rows; the next
+// head's row is requested before the current one is worked on.  Everything is in units of log2
+// (exp(x) = 2^(x log2 e)): one special-function op per element.  The other path: one warp per logits row.
+template <bool VEC, int NIT>
 __global__ void __launch_bounds__(128)
 masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ mask, int B, int nh, int S,
                       float scale) {
@@ -283,55 +286,74 @@ masked_softmax_kernel(__half* __restrict__ logits, const __half* __restrict__ ma
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * 4 + warp;
-  const long long rows = static_cast<long long>(B) * nh * S;
-  if (row >= rows) return;
-  const int i = static_cast<int>(row % S);
-  const int b = static_cast<int>((row / S) % B);
-  __half* lp = logits + row * S;
-  const __half* mp = mask + (static_cast<long long>(b) * S + i) * S;
   if (VEC) {
+    const long long mask_rows = static_cast<long long>(B) * S;
+    if (row >= mask_rows) return;
     const int nvec = S / 8;
     const float scale_l2 = scale * 1.4426950408889634f;
-    float val[4][8];
-    float mx = -INFINITY;
+    const long long head_stride = mask_rows * S;  // halves between the same (b, i) row of two heads
+    __half* lp = logits + row * S;
+    float add[NIT][8];
+    uint4 raw[2][NIT];  // the rows of the next two heads, in flight
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int v = it * 32 + lane;
       if (v < nvec) {
+        raw[0][it] = *(reinterpret_cast<const uint4*>(lp) + v);
+        if (nh > 1) raw[1][it] = *(reinterpret_cast<const uint4*>(lp + head_stride) + v);
         float m[8];
-        unpack8(*(reinterpret_cast<const uint4*>(lp) + v), val[it]);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(mp) + v), m);
-        // in units of log2: logit * scale * log2(e) + (1 - mask) * (-10000 * log2(e)); exp(x) = 2^(x log2 e)
+        unpack8(__ldg(reinterpret_cast<const uint4*>(mask + row * S) + v), m);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          val[it][k] = fmaf(val[it][k], scale_l2, fmaf(m[k], 14426.950408889634f, -14426.950408889634f));
-          mx = fmaxf(mx, val[it][k]);
-        }
+        for (int k = 0; k < 8; ++k) add[it][k] = fmaf(m[k], 14426.950408889634f, -14426.950408889634f);
       }
     }
-    mx = warp_max(mx);
-    float sum = 0.f;
+    for (int h = 0; h < nh; ++h, lp += head_stride) {
+      float val[NIT][8];
+      float mx = -INFINITY;
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      if (it * 32 + lane < nvec) {
+      for (int it = 0; it < NIT; ++it) {
+        const int v = it * 32 + lane;
+        if (v < nvec) {
+          unpack8(raw[0][it], val[it]);
+          raw[0][it] = raw[1][it];
+          if (h + 2 < nh) raw[1][it] = *(reinterpret_cast<const uint4*>(lp + 2 * head_stride) + v);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          val[it][k] = exp2f_fast(val[it][k] - mx);
-          sum += val[it][k];
+          for (int k = 0; k < 8; ++k) {
+            val[it][k] = fmaf(val[it][k], scale_l2, add[it][k]);
+            mx = fmaxf(mx, val[it][k]);
+          }
         }
       }
-    }
-    const float inv = 1.0f / (warp_sum(sum) + 1e-6f);
+      mx = warp_max(mx);
+      float sum = 0.f;
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int v = it * 32 + lane;
-      if (v < nvec) {
+      for (int it = 0; it < NIT; ++it) {
+        if (it * 32 + lane < nvec) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) val[it][k] *= inv;
-        *(reinterpret_cast<uint4*>(lp) + v) = pack8(val[it]);
+          for (int k = 0; k < 8; ++k) {
+            val[it][k] = exp2f_fast(val[it][k] - mx);
+            sum += val[it][k];
+          }
+        }
+      }
+      const float inv = 1.0f / (warp_sum(sum) + 1e-6f);
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        const int v = it * 32 + lane;
+        if (v < nvec) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) val[it][k] *= inv;
+          *(reinterpret_cast<uint4*>(lp) + v) = pack8(val[it]);
+        }
       }
     }
   } else {
+    const long long rows = static_cast<long long>(B) * nh * S;
+    if (row >= rows) return;
+    const int i = static_cast<int>(row % S);
+    const int b = static_cast<int>((row / S) % B);
+    __half* lp = logits + row * S;
+    const __half* mp = mask + (static_cast<long long>(b) * S + i) * S;
     float val[32];
     float mx = -INFINITY;
 #pragma unroll
@@ -429,9 +451,14 @@ cudaError_t launch_masked_softmax(__half* logits, const __half* mask, int B, int
                                   cudaStream_t stream) {
   if (S <= 0 || S > 1024 || B <= 0 || nh <= 0) return cudaErrorInvalidValue;
   const long long rows = static_cast<long long>(B) * nh * S;
+  if (S % 8 == 0) {  // a warp per mask row, looping over the heads
+    dim3 grid_v(static_cast<unsigned>((static_cast<long long>(B) * S + 3) / 4));
+    if (S <= 256) return launch_pdl(masked_softmax_kernel<true, 1>, grid_v, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
+    if (S <= 512) return launch_pdl(masked_softmax_kernel<true, 2>, grid_v, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
+    return launch_pdl(masked_softmax_kernel<true, 4>, grid_v, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
+  }
   dim3 grid(static_cast<unsigned>((rows + 3) / 4));
-  if (S % 8 == 0) return launch_pdl(masked_softmax_kernel<true>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
-  return launch_pdl(masked_softmax_kernel<false>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
+  return launch_pdl(masked_softmax_kernel<false, 4>, grid, dim3(128), 0, stream, logits, mask, B, nh, S, scale);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -156,7 +156,7 @@ def test_add_bias_gelu(cuda_device, kind):
     assert_close_fp16(got, want, "add_bias_gelu", max_abs=4e-3, mean_abs=3e-4)
 
 
-@pytest.mark.parametrize("B,nh,S", [(2, 3, 64), (2, 2, 13), (1, 2, 512)])
+@pytest.mark.parametrize("B,nh,S", [(2, 3, 64), (2, 2, 13), (1, 2, 512), (1, 1, 1024), (2, 1, 8), (1, 5, 264), (3, 2, 776)])
 def test_masked_softmax(cuda_device, B, nh, S):
     from bytetransformer_b200.encoder import masked_softmax_
     from oracle.bert_oracle import masked_softmax as ref
