@@ -747,9 +747,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 //         mean = avg(mean_i),  M2 = sum(M2_i) + 128 * sum((mean_i - mean)^2);
 //   4. second read of tensor memory: normalise, gamma / beta, fp16, staging, TMA store.
 // Accumulators are double buffered, so 1-4 of a tile overlap the main loop of the CTA's next
-// tile.  A CTA only ever waits for CTAs working on the same row tile, which never wait for
-// anything but that row tile in turn, so there is no circular wait whatever subset of the
-// grid is resident; the wait is bounded like every other wait of the library.
+// tile.  A CTA only ever waits for the C CTAs working on the same row tile, and those wait for
+// nothing but that row tile in turn, so the waits are never circular.  Progress does need those
+// C = N/256 neighbouring CTAs to be resident together: the grid never exceeds the SM count and a CTA
+// takes a whole SM, so they are as soon as the kernels before have left; should something else hold
+// SMs for long (another process, a hung kernel on another stream), the wait, bounded like every
+// other wait of the library, gives up and reports kStatusGemmEpilogueTimeout instead of spinning.
 // The scratch (16 * N/128 bytes per row) must not hold this launch's epoch in the low half of any
 // word beforehand: the caller zeroes it once and numbers the launches that share it 1, 2, 3, ...
 // ------------------------------------------------------------------------------------------

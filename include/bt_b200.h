@@ -14,6 +14,18 @@
  * serialised behind all earlier work of its stream the ordinary way; the others use programmatic
  * dependent launch among themselves.
  *
+ * Device: a handle belongs to the device it was created for (bt_config.device), and that device must
+ * be the calling thread's current CUDA device in every call that takes the handle: the library does
+ * not switch devices.  A call made with another device current returns BT_ERR_INVALID_ARG
+ * ("handle belongs to device X, current device is Y") before anything is launched.  Data pointers
+ * that the kernels read by tensor map or 16-byte accesses (activations, weights, masks, workspace)
+ * must be 16-byte aligned; a misaligned one is refused with BT_ERR_INVALID_ARG.
+ *
+ * Symbols named bt_debug_* (and bt_profile_*) are not part of this interface: they exist for the
+ * repository's own tests and timing scripts, set PROCESS-WIDE state that every handle of the process
+ * sees (kernel selection, tile shapes), are not thread-safe and may change or vanish.  A production
+ * host never calls them; bt_version() reports the library build.
+ *
  * Each declaration names the reference interface it stands in for
  * (paths relative to the ByteTransformer project root).
  *
