@@ -228,6 +228,10 @@ struct Workspace {
   __half *xa, *xb, *qkv, *ctx, *y, *mid;
   float* pre;  // pre-LayerNorm sum, kept in fp32 (LayerNorm as its own kernel), or the row-statistics partials
   size_t ln_stats_bytes;  // leading bytes of `pre` that hold the tagged row-statistics partials (fused LayerNorm)
+  // general-mask path of the padded entry points: the mask as one bit per (query, key), 128 bytes per row at
+  // most (S <= 1024), behind a word that says whether the bits may be used; null on the packed entry
+  int* mask_bits_flag;
+  uint32_t* mask_bits;
   size_t bytes;
 };
 
@@ -243,6 +247,8 @@ static Workspace carve(void* base, size_t rows, int hidden, int ffn, size_t n_ba
   };
   w.batch_idx = reinterpret_cast<int*>(take(n_batch_idx * 4));
   w.word_idx = reinterpret_cast<int*>(take(n_word_idx * 4));
+  w.mask_bits_flag = reinterpret_cast<int*>(take(n_word_idx ? 16 : 0));
+  w.mask_bits = reinterpret_cast<uint32_t*>(take(n_word_idx * 128));
   const size_t rh = rows * static_cast<size_t>(hidden) * 2;
   w.xa = reinterpret_cast<__half*>(take(rh));
   w.xb = reinterpret_cast<__half*>(take(rh));
@@ -316,6 +322,8 @@ struct GeneralMask {
   const __half* mask = nullptr;
   const __half* bias = nullptr;
   const int* kv_bound = nullptr;  // per (sequence, query tile): leading keys that matter (launch_mask_key_bound)
+  const uint32_t* bits = nullptr; // the mask as bits (launch_mask_bits), or null
+  const int* bits_flag = nullptr;
 };
 
 static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch_idx, int B, int max_len, int rows,
@@ -336,6 +344,8 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
     a.gen_mask = gm->mask;
     a.gen_bias = gm->bias;
     a.gen_kv_bound = gm->kv_bound;
+    a.gen_bits = gm->bits;
+    a.gen_bits_flag = gm->bits_flag;
     a.gen_inv_scale = sqrtf(static_cast<float>(h->cfg.size_per_head)) * h->cfg.tao;
   }
   cudaError_t e;
@@ -551,7 +561,7 @@ static int stack_general(bt_handle h, int first_layer, int n_layers, const void*
   cudaError_t e;
   {
     LaunchScope scope(h, BT_PROF_OFFSETS, stream);
-    e = launch_uniform_offsets(ws.batch_idx, B, S, stream);
+    e = launch_uniform_offsets(ws.batch_idx, B, S, stream, ws.mask_bits_flag);
   }
   if (e != cudaSuccess) return fail_cuda(h, e, "offsets launch");
   GeneralMask gm;
@@ -565,6 +575,17 @@ static int stack_general(bt_handle h, int first_layer, int n_layers, const void*
   }
   if (e != cudaSuccess) return fail_cuda(h, e, "mask key-bound launch");
   gm.kv_bound = ws.word_idx;
+  if (gm.bias == nullptr) {
+    // no bias: a mask of zeros and ones is applied from bits (one pre-pass per call; the kernel falls back to
+    // the fp16 mask if the pre-pass meets any other value)
+    {
+      LaunchScope scope(h, BT_PROF_OFFSETS, stream);
+      e = launch_mask_bits(gm.mask, B, S, ws.mask_bits, ws.mask_bits_flag, stream);
+    }
+    if (e != cudaSuccess) return fail_cuda(h, e, "mask bits launch");
+    gm.bits = ws.mask_bits;
+    gm.bits_flag = ws.mask_bits_flag;
+  }
   const __half* cur = reinterpret_cast<const __half*>(input);
   for (int l = 0; l < n_layers; ++l) {
     const bool last = (l == n_layers - 1);

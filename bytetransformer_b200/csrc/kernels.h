@@ -52,7 +52,13 @@ cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_id
 cudaError_t launch_pack_rows(const __half* padded, __half* packed, const int* batch_idx, int B, int S,
                              int hidden, cudaStream_t stream);
 // batch_idx[i] = i * S for i = 0..B (every sequence keeps all S rows: the general-mask path)
-cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream);
+// (`clear_flag`: a word the kernel also sets to zero, or null)
+cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream, int* clear_flag = nullptr);
+// One bit per (query, key) of a [B,S,S] mask: bit k of word k/32 of row (b*S + q) is set iff mask[b,q,k] == 1;
+// a row's words are mask_bits_stride_words(S) apart.  *flag_dev (zero beforehand) becomes 1 if some entry
+// is neither 0 nor 1, in which case the bits do not stand for the mask.
+int mask_bits_stride_words(int S);
+cudaError_t launch_mask_bits(const __half* mask, int B, int S, uint32_t* bits, int* flag_dev, cudaStream_t stream);
 // *flag_dev = 1 if every mask[b] is a right-padding mask (exactly the first len_b keys allowed in each of
 // the first len_b rows, no key from len_b on allowed in any later row; len_b = number of entries >= 0.5
 // in row 0), else 0.
@@ -118,6 +124,9 @@ struct MhaLaunch {
   const __half* gen_bias = nullptr;  // [head_num, max_len, max_len] or null
   float gen_inv_scale = 8.0f;        // sqrt(64) * tao
   const int* gen_kv_bound = nullptr; // [batch, ceil(max_len/128)] keys that matter per query tile (launch_mask_key_bound) or null
+  // the mask as bits (launch_mask_bits) and the word that says whether they may be used (0 = yes); null = no bits
+  const uint32_t* gen_bits = nullptr;
+  const int* gen_bits_flag = nullptr;
 };
 cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream);
 

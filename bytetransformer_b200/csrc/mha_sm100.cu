@@ -90,6 +90,11 @@ struct MhaArgs {
   int gen_seq_len;
   float gen_inv_scale;     // 1 / (softmax scale): the additive term is applied to the unscaled score
   const int* gen_kv_bound; // [batch, query tiles]: leading keys that matter for the query tile, or null
+  // A binary mask without bias is applied from one bit per (query, key) instead (gen_bits, rows
+  // `gen_bits_stride` words apart; usable when *gen_bits_flag == 0): the scores stay where they are
+  const uint32_t* gen_bits;
+  const int* gen_bits_flag;
+  int gen_bits_stride;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -196,6 +201,89 @@ __device__ __forceinline__ float tile_probs(uint32_t t_s, int kv_valid, float c,
   tmem_ld_wait();
   tmem_st_32x16(t_p + 16, pk);
   l += chunk_probs<MASKED>(vb, 0, kv_valid, c, m_ref, pk);
+  tmem_st_32x16(t_p, pk);
+  tmem_st_wait();
+  return l;
+}
+
+// Binary mask from bits: a key whose bit is clear has `neg` (= -10000 / scale) added to its score, exactly
+// what the additive form below does for mask values 0 and 1, without a pass over S.  `w` holds the bits of
+// the chunk's 32 keys.
+template <bool MASKED>
+__device__ __forceinline__ float chunk_max_bits(const uint32_t (&v)[32], int cbase, int kv_valid, uint32_t w, float neg) {
+  float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float a = __uint_as_float(v[i]), b = __uint_as_float(v[i + 1]);
+    a = ((w >> i) & 1u) ? a : a + neg;
+    b = ((w >> (i + 1)) & 1u) ? b : b + neg;
+    if (MASKED) {
+      a = (cbase + i < kv_valid) ? a : -INFINITY;
+      b = (cbase + i + 1 < kv_valid) ? b : -INFINITY;
+    }
+    m0 = fmaxf(m0, a);
+    m1 = fmaxf(m1, b);
+  }
+  return fmaxf(m0, m1);
+}
+template <bool MASKED>
+__device__ __forceinline__ float tile_row_max_bits(uint32_t t_s, int kv_valid, const uint4& bw, float neg) {
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32(t_s, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 32, vb);
+  float mx = chunk_max_bits<MASKED>(va, 0, kv_valid, bw.x, neg);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, va);
+  mx = fmaxf(mx, chunk_max_bits<MASKED>(vb, 32, kv_valid, bw.y, neg));
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 96, vb);
+  mx = fmaxf(mx, chunk_max_bits<MASKED>(va, 64, kv_valid, bw.z, neg));
+  tmem_ld_wait();
+  return fmaxf(mx, chunk_max_bits<MASKED>(vb, 96, kv_valid, bw.w, neg));
+}
+template <bool MASKED>
+__device__ __forceinline__ float chunk_probs_bits(const uint32_t (&v)[32], int cbase, int kv_valid, float c, float m_ref,
+                                                  uint32_t w, float neg, uint32_t (&out)[16]) {
+  float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
+    a = ((w >> (2 * i)) & 1u) ? a : a + neg;
+    b = ((w >> (2 * i + 1)) & 1u) ? b : b + neg;
+    float p0 = ex2_approx(fmaf(a, c, -m_ref));
+    float p1 = ex2_approx(fmaf(b, c, -m_ref));
+    if (MASKED) {
+      p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
+      p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
+    }
+    l0 += p0;
+    l1 += p1;
+    out[i] = pack_half2(p0, p1);
+  }
+  return l0 + l1;
+}
+template <bool MASKED>
+__device__ __forceinline__ float tile_probs_bits(uint32_t t_s, int kv_valid, float c, float m_ref, const uint4& bw,
+                                                 float neg) {
+  const uint32_t t_p = t_s + 64;
+  uint32_t va[32], vb[32], pk[16];
+  float l = 0.f;
+  tmem_ld_32x32(t_s + 96, va);
+  tmem_ld_wait();
+  tmem_ld_32x32(t_s + 64, vb);
+  l += chunk_probs_bits<MASKED>(va, 96, kv_valid, c, m_ref, bw.w, neg, pk);
+  tmem_ld_wait();
+  tmem_st_32x16(t_p + 48, pk);
+  tmem_ld_32x32(t_s + 32, va);
+  l += chunk_probs_bits<MASKED>(vb, 64, kv_valid, c, m_ref, bw.z, neg, pk);
+  tmem_ld_wait();
+  tmem_st_32x16(t_p + 32, pk);
+  tmem_ld_32x32(t_s, vb);
+  l += chunk_probs_bits<MASKED>(va, 32, kv_valid, c, m_ref, bw.y, neg, pk);
+  tmem_ld_wait();
+  tmem_st_32x16(t_p + 16, pk);
+  l += chunk_probs_bits<MASKED>(vb, 0, kv_valid, c, m_ref, bw.x, neg, pk);
   tmem_st_32x16(t_p, pk);
   tmem_st_wait();
   return l;
@@ -433,6 +521,9 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // binary mask, no bias: applied from bits inside the two softmax passes
+      const bool use_bits = GENERAL && args.gen_bits != nullptr && __ldg(args.gen_bits_flag) == 0;
+      const float bits_neg = -10000.0f * args.gen_inv_scale;
       for (int j = 0; j < n_kv; ++j) {
         const uint32_t jpar = j & 1;
         const int kv_valid = min(kKvRows, L - j * kKvRows);
@@ -442,7 +533,13 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           break;
         }
         tc_fence_after();
-        if (GENERAL) {
+        uint4 bw = make_uint4(~0u, ~0u, ~0u, ~0u);  // a row that does not exist masks nothing
+        if (GENERAL && use_bits) {
+          const int q_row = q0 + t * kQRows + r;
+          if (q_row < args.gen_seq_len)
+            bw = __ldg(reinterpret_cast<const uint4*>(args.gen_bits + (static_cast<size_t>(b) * args.gen_seq_len + q_row) *
+                                                                          args.gen_bits_stride) + j);
+        } else if (GENERAL) {
           const int S = args.gen_seq_len;
           const int q_row = q0 + t * kQRows + r;
           const bool q_ok = q_row < S;
@@ -452,7 +549,12 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
                              q_ok ? kv_valid : 0, (S & 7) == 0, args.gen_inv_scale);
         }
         // pass 1: row maximum (scaled to log2 units)
-        const float mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
+        float mx;
+        if (GENERAL && use_bits)
+          mx = c * (full_tile ? tile_row_max_bits<false>(t_s, kv_valid, bw, bits_neg)
+                              : tile_row_max_bits<true>(t_s, kv_valid, bw, bits_neg));
+        else
+          mx = c * (full_tile ? tile_row_max<false>(t_s, kv_valid) : tile_row_max<true>(t_s, kv_valid));
         if (j == 0) {
           m_ref = mx;
         } else {
@@ -475,8 +577,12 @@ mha_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaArgs args) {
           }
         }
         // pass 2: probabilities -> fp16 pairs -> tensor memory (over S), row sum
-        l_run += full_tile ? tile_probs<false>(t_s, kv_valid, c, m_ref)
-                           : tile_probs<true>(t_s, kv_valid, c, m_ref);
+        if (GENERAL && use_bits)
+          l_run += full_tile ? tile_probs_bits<false>(t_s, kv_valid, c, m_ref, bw, bits_neg)
+                             : tile_probs_bits<true>(t_s, kv_valid, c, m_ref, bw, bits_neg);
+        else
+          l_run += full_tile ? tile_probs<false>(t_s, kv_valid, c, m_ref)
+                             : tile_probs<true>(t_s, kv_valid, c, m_ref);
         if (!full_tile && t == 0) {
           // tail tile: blank the V rows of keys that do not belong to this sequence
           // (tile 0's PV is issued before tile 1's, so tile 0's warpgroup does it for both)
@@ -1133,7 +1239,13 @@ cudaError_t launch_mha(const MhaLaunch& a, cudaStream_t stream) {
   args.gen_seq_len = a.max_len;
   args.gen_inv_scale = a.gen_inv_scale;
   args.gen_kv_bound = a.gen_kv_bound;
-  // general [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence)
+  args.gen_bits = a.gen_bias == nullptr ? a.gen_bits : nullptr;
+  args.gen_bits_flag = a.gen_bits_flag;
+  args.gen_bits_stride = mask_bits_stride_words(a.max_len);
+  // General [B,S,S] mask (+ optional bias): one CTA per (128 query rows, head, sequence).  A persistent-CTA
+  // form of it (mask applied from the bits) was measured slower at batch 16 / 512 tokens (2.36 against 2.19 ms
+  // per 12 layers): 768 items of one to four key tiles fill the 296 CTAs' last round unevenly, while one CTA
+  // per item is balanced by the hardware's block scheduler.
   if (a.gen_mask != nullptr) return launch_per_item<true>(a, args, stream);
   // Measured on B200 (12 heads, 18.9k tokens): the persistent kernel is ahead at every length (sequences
   // of 64 / 128 / 256 / 384 / 1024 tokens: 70 / 40 / 47 / 57 / 105 us against 77 / 40 / 52 / 62 / 120) and for

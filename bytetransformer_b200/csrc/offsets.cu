@@ -134,9 +134,11 @@ restore_rows_kernel(const uint4* __restrict__ packed, uint4* __restrict__ padded
     dst[v] = v < n ? __ldg(src + v) : make_uint4(0u, 0u, 0u, 0u);
 }
 
-__global__ void __launch_bounds__(256) uniform_offsets_kernel(int* __restrict__ batch_idx, int B, int S) {
+__global__ void __launch_bounds__(256) uniform_offsets_kernel(int* __restrict__ batch_idx, int B, int S,
+                                                              int* __restrict__ clear_flag) {
   pdl_launch_dependents();
   pdl_wait();
+  if (clear_flag != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *clear_flag = 0;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i <= B; i += gridDim.x * blockDim.x) batch_idx[i] = i * S;
 }
 
@@ -219,6 +221,54 @@ mask_key_bound_kernel(const __half* __restrict__ mask, int S, int* __restrict__ 
   if (threadIdx.x == 0) bound[b * gridDim.x + blockIdx.x] = s_bound;
 }
 
+// The mask of the general path as one bit per (query, key): bit k of a row's word k/32 is set iff
+// mask[row, k] == 1.  `flag` (zero beforehand) is raised when some entry is neither 0 nor 1: the attention
+// kernel then keeps adding the fp16 mask itself.  Warp per mask row; a row's words are `stride_words`
+// apart (a multiple of 4, so that the 128 bits of a key tile are one aligned 16-byte load).
+__global__ void __launch_bounds__(256)
+mask_bits_kernel(const __half* __restrict__ mask, int S, long long rows, uint32_t* __restrict__ bits,
+                 int stride_words, int* __restrict__ flag) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const unsigned short* m = reinterpret_cast<const unsigned short*>(mask) + row * S;
+  uint32_t* out = bits + row * stride_words;
+  bool odd = false;  // an entry that is neither +-0 nor 1
+  if ((S & 7) == 0) {
+    const int nvec = S >> 3;
+    for (int v0 = 0; v0 < nvec; v0 += 32) {
+      const int v = v0 + lane;
+      uint32_t byte = 0;
+      if (v < nvec) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(m) + v);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t lo = w[i] & 0xffffu, hi = w[i] >> 16;
+          byte |= (lo == 0x3c00u ? 1u : 0u) << (2 * i);
+          byte |= (hi == 0x3c00u ? 1u : 0u) << (2 * i + 1);
+          odd = odd || (lo != 0x3c00u && (lo & 0x7fffu) != 0u) || (hi != 0x3c00u && (hi & 0x7fffu) != 0u);
+        }
+      }
+      uint32_t part = byte << ((lane & 3) * 8);
+      part |= __shfl_xor_sync(0xffffffffu, part, 1);
+      part |= __shfl_xor_sync(0xffffffffu, part, 2);
+      if ((lane & 3) == 0 && v < nvec) out[v >> 2] = part;
+    }
+  } else {
+    for (int k0 = 0; k0 < S; k0 += 32) {
+      const int k = k0 + lane;
+      const uint32_t h = k < S ? m[k] : 0u;
+      odd = odd || (h != 0x3c00u && (h & 0x7fffu) != 0u);
+      const uint32_t word = __ballot_sync(0xffffffffu, h == 0x3c00u);
+      if (lane == 0) out[k0 >> 5] = word;
+    }
+  }
+  if (__any_sync(0xffffffffu, odd) && lane == 0) atomicOr(flag, 1);
+}
+
 __global__ void set_flag_kernel(int* flag, int v) {
   pdl_launch_dependents();
   pdl_wait();
@@ -240,9 +290,18 @@ cudaError_t launch_build_offsets(const __half* mask, int B, int S, int* batch_id
   return launch_pdl(build_offsets_kernel, dim3(1), dim3(kOffThreads), 0, stream, mask, B, S, batch_idx, word_idx);
 }
 
-cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream) {
+cudaError_t launch_uniform_offsets(int* batch_idx, int B, int S, cudaStream_t stream, int* clear_flag) {
   const int grid = (B + 1 + 255) / 256;
-  return launch_pdl(uniform_offsets_kernel, dim3(grid), dim3(256), 0, stream, batch_idx, B, S);
+  return launch_pdl(uniform_offsets_kernel, dim3(grid), dim3(256), 0, stream, batch_idx, B, S, clear_flag);
+}
+
+int mask_bits_stride_words(int S) { return ((S + 127) / 128) * 4; }
+
+cudaError_t launch_mask_bits(const __half* mask, int B, int S, uint32_t* bits, int* flag_dev, cudaStream_t stream) {
+  if (B <= 0 || S <= 0) return cudaErrorInvalidValue;
+  const long long rows = static_cast<long long>(B) * S;
+  return launch_pdl(mask_bits_kernel, dim3(static_cast<unsigned>((rows + 7) / 8)), dim3(256), 0, stream, mask, S, rows,
+                    bits, mask_bits_stride_words(S), flag_dev);
 }
 
 cudaError_t launch_mask_is_right_padded(const __half* mask, int B, int S, int* flag_dev, cudaStream_t stream) {

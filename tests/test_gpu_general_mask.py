@@ -29,6 +29,10 @@ def _masks(kind, B, S, g):
         m[:, 5, :] = 0.0
         if S > 140:
             m[0, 130:140, :] = 0.0
+    elif kind == "soft":                # entries other than 0 and 1: the bits cannot stand for the mask
+        m = torch.tril(torch.ones(S, S)).expand(B, S, S).clone()
+        m[:, :, ::7] *= 0.75
+        m[:, 3, 1] = 0.25
     elif kind == "right_padded":
         lens = torch.randint(1, S + 1, (B,), generator=g)
         m = ((torch.arange(S)[None, :] < lens[:, None]).float().unsqueeze(1)).expand(B, S, S).clone()
@@ -82,6 +86,20 @@ def test_general_mask_seq_len_not_multiple_of_8(cuda_device):
 
 def test_general_mask_long_sequence_three_layers(cuda_device):
     _run(cuda_device, 12, 2, 640, "prefix_lm", True, 3, seed=5)
+
+
+@pytest.mark.parametrize("S,kind", [(77, "causal"), (640, "prefix_lm"), (96, "block_diagonal"), (1024, "causal")])
+def test_binary_mask_without_bias_is_applied_from_bits(cuda_device, S, kind):
+    """No bias and a mask of zeros and ones: a pre-pass turns the mask into one bit per (query, key) and the
+    attention kernel applies it inside its softmax passes; sequence lengths that are not multiples of 8 / 32 /
+    128 exercise the scalar pre-pass and the tail key tile."""
+    _run(cuda_device, 2, 2, S, kind, False, 2, seed=S)
+
+
+def test_mask_with_other_values_falls_back_to_the_additive_form(cuda_device):
+    """(1 - mask) * -10000 for entries like 0.25 or 0.75 cannot be expressed in bits: the pre-pass raises its
+    flag and the kernel adds the fp16 mask itself."""
+    _run(cuda_device, 4, 2, 200, "soft", False, 1, seed=23)
 
 
 def test_general_path_equals_packed_path_on_right_padded_masks(cuda_device):
