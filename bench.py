@@ -37,11 +37,20 @@ sys.path.insert(0, ROOT)
 METRIC = "bert_base_12L_packed_tokens_per_sec"
 UNIT = "tokens/s"
 WORKLOAD = "whole_box_1024x1024"
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the four GEMMs of a layer at an
-# 18.6k-token micro-batch, from the ncu capture summarised in profiles/gemm_kernels_microbatch18k.txt
-# (algorithmic bytes of the same four launches: 132.4 MB mean; DRAM sees less because outputs of one
-# kernel are still in the 126 MB L2 when the next kernel reads them).
-GEMM_DRAM_BYTES_PER_LAUNCH = 94.6e6
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch and packed token, mean of the four GEMMs of a layer,
+# from the two ncu captures summarised in profiles/gemm_kernels_microbatch18k.txt (18,645 tokens per launch: 94.6 MB)
+# and profiles/gemm_kernels_microbatch76k.txt (70,734 tokens: 455.6 MB).  The algorithmic bytes of the same launches
+# are 7,100 per token; DRAM sees less because a kernel's output is partly still in the 126 MB L2 when the next
+# kernel reads it, the more so the smaller the launch.  Between the two launch sizes the figure is interpolated.
+GEMM_DRAM_BYTES_PER_TOKEN = ((18645, 94.6e6 / 18645), (70734, 455.6e6 / 70734))
+
+
+def gemm_dram_bytes_per_launch(tokens_per_launch: float) -> float:
+    (t0, b0), (t1, b1) = GEMM_DRAM_BYTES_PER_TOKEN
+    w = min(1.0, max(0.0, (tokens_per_launch - t0) / (t1 - t0)))
+    return (b0 + w * (b1 - b0)) * tokens_per_launch
+
+
 WORKLOAD_DESC = "bert-base 12L, 1024 seqs, max_seq 1024, lens U[16,1024] seed 1234, split by LPT over the GPUs"
 
 
@@ -215,7 +224,7 @@ def main():
     n_gpus = world
 
     from bytetransformer_b200.encoder import Encoder
-    from bytetransformer_b200.runner import DEFAULT_TOKEN_BUDGET, PackedRunner
+    from bytetransformer_b200.runner import PackedRunner
     from bytetransformer_b200.sharding import lpt_shards
     from bytetransformer_b200.workloads import (BERT_BASE, attention_flops_per_layer, gemm_flops_per_layer,
                                                 lengths_for, make_weights)
@@ -232,8 +241,8 @@ def main():
     if args.fused_ln >= 0:
         from bytetransformer_b200 import _abi
         _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
-    budget = args.token_budget or DEFAULT_TOKEN_BUDGET
-    runner = PackedRunner(enc, lengths, mine, token_budget=budget, mix=not args.sorted_batches)
+    runner = PackedRunner(enc, lengths, mine, token_budget=args.token_budget, mix=not args.sorted_batches)
+    budget = runner.token_budget
     xs, outs = runner.make_device_inputs(seed=rank)
 
     barrier = ranks.barrier
@@ -310,7 +319,8 @@ def main():
     kernels = {}
     if not args.no_kernel_events and gemm_ms > 0:
         achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
-        traffic = GEMM_DRAM_BYTES_PER_LAUNCH if not (args.max_seqs or args.layers) else None
+        # per launch, like `achieved`: this rank's tokens per micro-batch times the captured per-token figure
+        traffic = gemm_dram_bytes_per_launch(my_tokens / max(1, len(runner.batches))) if not args.layers else None
         roofline = {"bound": "tensor", "kernel": "the four GEMMs of a layer: gemm_f16_pair_kernel (QKV, FFN1 + GELU), gemm_f16_ln_kernel (attention output and FFN2, with LayerNorm)", "achieved": achieved,
                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                     "peak_source": peaks["source"] + " sustained bf16 dense", "traffic": traffic,

@@ -16,15 +16,39 @@ import torch
 from .encoder import Encoder
 from .sharding import MicroBatch, micro_batches
 
-DEFAULT_TOKEN_BUDGET = 148 * 128  # one 128-row GEMM tile per SM and tile column
+TOKEN_BUDGET_UNIT = 148 * 128     # one 128-row GEMM tile per SM and tile column
+DEFAULT_TOKEN_BUDGET = TOKEN_BUDGET_UNIT
+MAX_TOKEN_BUDGET_UNITS = 4
+
+
+def pick_token_budget(total_tokens: int, min_batches: int = 8) -> int:
+    """Token budget of a micro-batch for a rank that holds `total_tokens`: the largest of 1..4 x 18,944
+    that still leaves at least `min_batches` micro-batches (else 18,944).
+
+    Larger launches amortise each kernel's first and last wave (measured on B200, BERT-base, 556,500 tokens on
+    one GPU: 3.72 / 3.86 / 3.89 / 3.93 M tokens/s at 1 / 2 / 3 / 4 units; the GEMM kernels gain 8 %, the
+    attention kernel nothing), while the end-to-end path overlaps its host copies with the compute of the
+    neighbouring micro-batches and so wants several of them: the first copy in and the last copy out are
+    exposed, 1/min_batches of the copy time."""
+    best = 1
+    for k in range(1, MAX_TOKEN_BUDGET_UNITS + 1):
+        if -(-int(total_tokens) // (k * TOKEN_BUDGET_UNIT)) >= min_batches:
+            best = k
+    return best * TOKEN_BUDGET_UNIT
 
 
 class PackedRunner:
     def __init__(self, enc: Encoder, lengths: Sequence[int], seq_ids: Sequence[int],
-                 token_budget: int = DEFAULT_TOKEN_BUDGET, mix: bool = True):
+                 token_budget: int = 0, mix: bool = True):
+        """`token_budget` 0 = pick_token_budget() of this rank's tokens."""
         self.enc = enc
         self.device = enc.device
         self.hidden = enc.hidden
+        if token_budget <= 0:
+            ids = np.asarray(seq_ids, dtype=np.int64)
+            token_budget = pick_token_budget(int(np.asarray(lengths, dtype=np.int64)[ids].sum()) if len(ids) else 0)
+            token_budget = max(token_budget, int(np.asarray(lengths)[ids].max()) if len(ids) else 1)
+        self.token_budget = int(token_budget)
         self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget, mix=mix)
         self.tokens = int(sum(mb.tokens for mb in self.batches))
         self.max_tokens = max([mb.tokens for mb in self.batches] + [1])

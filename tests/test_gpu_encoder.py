@@ -283,7 +283,7 @@ def test_whole_box_workload_full_size_properties(cuda_device):
       (c) the longest, a middle and the shortest sequence are checked against the oracle run on that
           sequence alone (tolerance of the fp16 path: max-abs 2e-2, mean-abs 1e-3)."""
     from bytetransformer_b200.encoder import Encoder
-    from bytetransformer_b200.runner import DEFAULT_TOKEN_BUDGET
+    from bytetransformer_b200.runner import pick_token_budget
     from bytetransformer_b200.sharding import micro_batches
     from bytetransformer_b200.workloads import BERT_BASE, lengths_for, make_weights
     dev = cuda_device
@@ -292,7 +292,7 @@ def test_whole_box_workload_full_size_properties(cuda_device):
     assert len(lens) == 1024 and lens.min() >= 16 and lens.max() <= 1024
     weights = make_weights(BERT_BASE, seed=7, device="cpu")
     enc = Encoder(nh, 64, [[t.to(dev) for t in layer] for layer in weights])
-    mbs = micro_batches(lens, np.arange(len(lens)), DEFAULT_TOKEN_BUDGET)
+    mbs = micro_batches(lens, np.arange(len(lens)), pick_token_budget(int(lens.sum())))   # as bench.py cuts them at N = 1
     assert sum(mb.tokens for mb in mbs) == int(lens.sum())
     order = np.argsort(lens, kind="stable")
     sampled = {int(order[-1]), int(order[len(order) // 2]), int(order[0])}

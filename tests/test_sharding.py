@@ -51,3 +51,17 @@ def test_micro_batches_property(lengths, budget):
 def test_micro_batch_rejects_oversized_sequence():
     with pytest.raises(ValueError):
         micro_batches([5000], [0], 4096)
+
+
+def test_token_budget_grows_with_the_rank_s_tokens_but_keeps_several_micro_batches():
+    from bytetransformer_b200.runner import TOKEN_BUDGET_UNIT, pick_token_budget
+    assert pick_token_budget(0) == TOKEN_BUDGET_UNIT
+    assert pick_token_budget(10_000) == TOKEN_BUDGET_UNIT
+    # the benchmark workload on 1 / 2 / 4 / 8 GPUs
+    assert pick_token_budget(556_500) == 4 * TOKEN_BUDGET_UNIT
+    assert pick_token_budget(278_250) == 2 * TOKEN_BUDGET_UNIT
+    assert pick_token_budget(139_125) == TOKEN_BUDGET_UNIT
+    assert pick_token_budget(69_563) == TOKEN_BUDGET_UNIT
+    for total in (556_500, 278_250, 10_000_000):
+        b = pick_token_budget(total)
+        assert -(-total // b) >= 8
