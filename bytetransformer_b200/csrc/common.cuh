@@ -290,6 +290,44 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(p));
   return fmaf(-0.5f * ax, e, fmaxf(x, 0.f));
 }
+// Two values at once with the packed fp32 instructions of sm_100 (fma.rn.f32x2: one issue slot for two
+// lanes of a 64-bit register pair): the polynomial and the final multiply-add, which are most of the
+// instructions of gelu_erf_fast, take half the issue slots.  Same arithmetic, same results.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void gelu_erf_fast_pair(float& x0, float& x1) {
+  const float a0 = fabsf(x0), a1 = fabsf(x1);
+  const unsigned long long z = pack_f32x2(fminf(a0 * 0.70710678118654752f, 4.3f), fminf(a1 * 0.70710678118654752f, 4.3f));
+  unsigned long long p = fma_f32x2(pack_f32x2(-0.002677350537851453f, -0.002677350537851453f), z,
+                                   pack_f32x2(0.02833780087530613f, 0.02833780087530613f));
+  p = fma_f32x2(p, z, pack_f32x2(-0.1465892493724823f, -0.1465892493724823f));
+  p = fma_f32x2(p, z, pack_f32x2(-0.9199854135513306f, -0.9199854135513306f));
+  p = fma_f32x2(p, z, pack_f32x2(-1.6274596452713013f, -1.6274596452713013f));
+  p = fma_f32x2(p, z, pack_f32x2(-3.764020948437974e-05f, -3.764020948437974e-05f));
+  float p0, p1, e0, e1;
+  unpack_f32x2(p, p0, p1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(p0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(p1));
+  const unsigned long long r = fma_f32x2(pack_f32x2(-0.5f * a0, -0.5f * a1), pack_f32x2(e0, e1),
+                                         pack_f32x2(fmaxf(x0, 0.f), fmaxf(x1, 0.f)));
+  unpack_f32x2(r, x0, x1);
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh( sqrt(2/pi) (x + 0.044715 x^3) ))
   const float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);

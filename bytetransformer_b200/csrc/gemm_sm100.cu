@@ -181,7 +181,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const CUtens
         for (int i = 0; i < kChunk; ++i) v[i] = gelu_tanh(v[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) v[i] = gelu_erf_fast(v[i]);
+        for (int i = 0; i < kChunk; i += 2) gelu_erf_fast_pair(v[i], v[i + 1]);
       }
     }
     const size_t off = static_cast<size_t>(row) * args.N + gcol +
@@ -828,6 +828,7 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
                            col_half * kColsPerThread;
     // ---- 1. v = acc + bias + residual -> tensor memory; shifted sums
     float sd = 0.f, sdd = 0.f, shift0 = 0.f;
+    unsigned long long sd2 = pack_f32x2(0.f, 0.f), sdd2 = sd2, nshift2 = sd2;
     {
       uint32_t raw[2][32];
       tmem_ld_32x32(t_row, raw[0]);
@@ -867,13 +868,18 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
             for (int j = 0; j < 4; ++j) {
               const float2 fb = __half22float2(bh[j]);
               const float2 fr = __half22float2(rh[j]);
-              const float v0 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j]) + (fb.x + fr.x);
-              const float v1 = __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1]) + (fb.y + fr.y);
-              if (ci == 0 && q == 0 && j == 0) shift0 = v0;
-              const float d0 = v0 - shift0, d1 = v1 - shift0;
-              sd += d0 + d1;
-              sdd = fmaf(d0, d0, sdd);
-              sdd = fmaf(d1, d1, sdd);
+              const unsigned long long br2 = add_f32x2(pack_f32x2(fb.x, fb.y), pack_f32x2(fr.x, fr.y));
+              const unsigned long long v2 = add_f32x2(
+                  pack_f32x2(__uint_as_float(raw[ci & 1][q * 8 + 2 * j]), __uint_as_float(raw[ci & 1][q * 8 + 2 * j + 1])), br2);
+              float v0, v1;
+              unpack_f32x2(v2, v0, v1);
+              if (ci == 0 && q == 0 && j == 0) {
+                shift0 = v0;
+                nshift2 = pack_f32x2(-v0, -v0);
+              }
+              const unsigned long long d2 = add_f32x2(v2, nshift2);
+              sd2 = add_f32x2(sd2, d2);
+              sdd2 = fma_f32x2(d2, d2, sdd2);
               raw[ci & 1][q * 8 + 2 * j] = __float_as_uint(v0);
               raw[ci & 1][q * 8 + 2 * j + 1] = __float_as_uint(v1);
             }
@@ -882,6 +888,11 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
         }
       }
       if (!res_ok) break;
+      float s0, s1, q0, q1;
+      unpack_f32x2(sd2, s0, s1);
+      unpack_f32x2(sdd2, q0, q1);
+      sd = s0 + s1;
+      sdd = q0 + q1;
     }
     const float lmean = shift0 + sd * (1.0f / kColsPerThread);
     const float m2 = fmaxf(sdd - sd * sd * (1.0f / kColsPerThread), 0.f);
@@ -968,6 +979,7 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
     }
     if (warp == 2 && lane == 0) gstamp(args.timing, it, 6);
     const float shift = -mean * rstd;
+    const unsigned long long rstd2 = pack_f32x2(rstd, rstd), shift2 = pack_f32x2(shift, shift);
     tmem_st_wait();  // the write-back of step 1 is complete before tensor memory is read again
     // ---- 4. normalise, gamma / beta, fp16, store (64 columns = 128 B per row at a time)
     const bool slab_full = row0 + 32 <= M;
@@ -1011,8 +1023,11 @@ __device__ __forceinline__ void ln_epilogue_loop(const GemmArgs& args, const CUt
           }
           float y[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            y[i] = fmaf(fmaf(__uint_as_float(raw[ci & 1][q * 8 + i]), rstd, shift), g[i], b[i]);
+          for (int i = 0; i < 8; i += 2) {
+            const unsigned long long n2 = fma_f32x2(
+                pack_f32x2(__uint_as_float(raw[ci & 1][q * 8 + i]), __uint_as_float(raw[ci & 1][q * 8 + i + 1])), rstd2, shift2);
+            unpack_f32x2(fma_f32x2(n2, pack_f32x2(g[i], g[i + 1]), pack_f32x2(b[i], b[i + 1])), y[i], y[i + 1]);
+          }
           uint4 u;
           u.x = pack_half2(y[0], y[1]);
           u.y = pack_half2(y[2], y[3]);

@@ -108,6 +108,15 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
+// Packed fp32 pairs (fma.rn.f32x2 / add.rn.f32x2 of sm_100: one issue slot for two values): the scale-and-shift
+// in front of the exponentials and the row sums behind them take half the instructions.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  unpack_f32x2(fma_f32x2(pack_f32x2(a0, a1), pack_f32x2(b, b), pack_f32x2(c, c)), d0, d1);
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+  unpack_f32x2(add_f32x2(pack_f32x2(d0, d1), pack_f32x2(a0, a1)), d0, d1);
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (P, fp16 pairs) is read from tensor memory.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -166,14 +175,15 @@ __device__ __forceinline__ float chunk_probs(const uint32_t (&v)[32], int cbase,
   float l0 = 0.f, l1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -m_ref));
-    float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -m_ref));
+    float t0, t1;
+    fma2(t0, t1, __uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), c, -m_ref);
+    float p0 = ex2_approx(t0);
+    float p1 = ex2_approx(t1);
     if (MASKED) {
       p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
       p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
     }
-    l0 += p0;
-    l1 += p1;
+    add2(l0, l1, p0, p1);
     out[i] = pack_half2(p0, p1);
   }
   return l0 + l1;
@@ -1030,13 +1040,15 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
           for (int i = 0; i < 128; ++i) s[i] = (i < kv_valid) ? s[i] : 0xff800000u;
         }
         // ---- exact row maximum
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 128; i += 4) {
+        for (int i = 0; i < 128; i += 8) {
           mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
           mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
         }
-        const float m_new = fmaxf(m_ref, c * fmaxf(mx0, mx1));
+        const float m_new = fmaxf(m_ref, c * max3(mx0, mx1, fmaxf(mx2, mx3)));
         bool pv_waited = (j == 0);  // (first tile of an item: the wait for the previous item's O covered it)
         if (j == 0) {
           m_ref = m_new;
@@ -1065,14 +1077,16 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
         float l0 = 0.f, l1 = 0.f;
         uint32_t pk[64];
 #pragma unroll
+        float l2 = 0.f, l3 = 0.f;
         for (int i = 0; i < 64; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), c, -m_ref));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), c, -m_ref));
-          l0 += p0;
-          l1 += p1;
+          float t0, t1;
+          fma2(t0, t1, __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]), c, -m_ref);
+          const float p0 = ex2_approx(t0);
+          const float p1 = ex2_approx(t1);
+          if (i & 1) add2(l2, l3, p0, p1); else add2(l0, l1, p0, p1);
           pk[i] = pack_half2(p0, p1);
         }
-        l_run += l0 + l1;
+        l_run += (l0 + l1) + (l2 + l3);
         if (!pv_waited) {
           // P belongs to the P V MMAs of the previous key tile until those have retired
           if (!mbar_wait_bounded(pv_done, (step - 1u) & 1u, abort_flag, args.status, kStatusMhaSoftmaxTimeout)) {
