@@ -331,6 +331,7 @@ static int run_mha(bt_handle h, const __half* qkv, __half* ctx, const int* batch
   MhaLaunch a;
   if (!h->tmap(&a.tm_qkv, qkv, rows, 3 * static_cast<uint64_t>(h->hidden), 64, 128))
     return fail(h, BT_ERR_CUDA, "cuTensorMapEncodeTiled failed for qkv");
+  a.has_tm_ctx = h->tmap(&a.tm_ctx, ctx, rows, static_cast<uint64_t>(h->hidden), 64, 32);
   a.ctx = ctx;
   a.batch_idx = batch_idx;
   a.batch = B;

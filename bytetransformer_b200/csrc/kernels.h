@@ -110,6 +110,8 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 // ---- fused multi-head attention -----------------------------------------------
 struct MhaLaunch {
   CUtensorMap tm_qkv;  // qkv [rows, 3H], box {64, 128}
+  CUtensorMap tm_ctx;  // ctx [rows, H], box {64, 32}: bulk stores of whole 32-row output slabs (has_tm_ctx)
+  bool has_tm_ctx = false;
   __half* ctx;         // [rows, H]
   const int* batch_idx;
   int batch;

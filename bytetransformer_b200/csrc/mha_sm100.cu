@@ -690,6 +690,7 @@ struct MhaPersistentArgs {
   int* status;
   int rows;     // rows allocated in qkv / ctx
   int max_len;  // upper bound of every sequence length
+  int tma_out;  // the kernel's second tensor map describes ctx: whole 32-row output slabs leave by bulk store
 };
 
 // Finds item n = (sequence b, query tile qt, head h); items are numbered sequence by sequence, inside
@@ -789,7 +790,8 @@ constexpr int kPersistentStages = 2;  // Q, K and V tiles each
 constexpr int kPersistentSmemBytes = 3 * kPersistentStages * kTileBytes + kTileBytes + 256;
 
 __global__ void __launch_bounds__(kPersistentThreads, 2)
-mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersistentArgs args) {
+mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_ctx,
+                      const MhaPersistentArgs args) {
   constexpr int kStages = kPersistentStages;
   constexpr int kSmemQ = 0;
   constexpr int kSmemK = kSmemQ + kStages * kTileBytes;
@@ -1130,10 +1132,15 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
         break;
       }
       tc_fence_after();
-      // O / row sum -> fp16 -> this warp's 32 x 128 B staging rows (16-byte units swizzled by the row) ->
-      // global memory with eight threads per row: a store instruction then covers four whole 128-byte
-      // lines instead of 16 bytes of 32 different lines (those took ~2k clocks of the load/store pipe per item).
+      // O / row sum -> fp16 -> this warp's 32 x 128 B staging rows (16-byte units swizzled by the row, the
+      // 128-byte swizzle of a tensor map) -> global memory.  A slab whose 32 rows all belong to the sequence
+      // leaves by one bulk store (the stores of the threads took 1.0-1.5 k clocks per item on the softmax
+      // warps' critical path); a slab that crosses the end of the sequence is stored by the threads, eight
+      // per row, so that a store instruction covers four whole 128-byte lines and rows of the next sequence
+      // are left alone.
       const float inv = 1.0f / l_run;
+      if (lane == 0) tma_store_wait_read();  // the previous item's bulk store has read the staging rows
+      __syncwarp();
       uint8_t* stage_out = smem + kSmemOut + warp * (32 * 128);
       uint32_t va[32], vb[32];
       tmem_ld_32x32(t_o, va);
@@ -1157,8 +1164,15 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
         w.w = pack_half2(__uint_as_float(vb[u * 8 + 6]) * inv, __uint_as_float(vb[u * 8 + 7]) * inv);
         *reinterpret_cast<uint4*>(stage_out + lane * 128 + (((4 + u) ^ (lane & 7)) << 4)) = w;
       }
+      const bool whole_slab = args.tma_out != 0 && qt * kQRows + warp * 32 + 32 <= L;
+      if (whole_slab) fence_proxy_async_smem();
       __syncwarp();
-      {
+      if (whole_slab) {
+        if (lane == 0) {
+          tma_store_2d(&tm_ctx, stage_out, head * kHeadDim, seq_start + qt * kQRows + warp * 32);
+          tma_store_commit();
+        }
+      } else {
         const int sub = lane >> 3, unit = lane & 7;  // row within a group of four, 16-byte unit of the row
         const int row0 = qt * kQRows + warp * 32;     // first query row of this warp's slab, within the sequence
         __half* out_base = args.ctx + static_cast<size_t>(seq_start + row0) * args.hidden + head * kHeadDim + unit * 8;
@@ -1175,6 +1189,7 @@ mha_persistent_kernel(const __grid_constant__ CUtensorMap tm_qkv, const MhaPersi
       qt = qt_n;
       head = head_n;
     }
+    if (lane == 0) tma_store_wait_all();  // the staging rows must outlive the last bulk store
     tc_fence_before();
   }
 
@@ -1212,13 +1227,14 @@ cudaError_t launch_persistent(const MhaLaunch& a, cudaStream_t stream) {
   args.status = a.status;
   args.rows = a.rows;
   args.max_len = a.max_len;
+  args.tma_out = a.has_tm_ctx ? 1 : 0;
   const long long items_max =
       static_cast<long long>(a.batch) * a.head_num * ((a.max_len + kQRows - 1) / kQRows);  // upper bound
   long long grid = 2LL * sms[dev];
   if (grid > items_max) grid = items_max;
   if (grid < 1) grid = 1;
   return launch_pdl(mha_persistent_kernel, dim3(static_cast<unsigned>(grid)), dim3(kPersistentThreads), kPersistentSmemBytes,
-                    stream, a.tm_qkv, args);
+                    stream, a.tm_qkv, a.has_tm_ctx ? a.tm_ctx : a.tm_qkv, args);
 }
 
 template <bool GENERAL>
