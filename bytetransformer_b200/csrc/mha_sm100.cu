@@ -261,14 +261,15 @@ __device__ __forceinline__ float chunk_probs_bits(const uint32_t (&v)[32], int c
     float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
     a = ((w >> (2 * i)) & 1u) ? a : a + neg;
     b = ((w >> (2 * i + 1)) & 1u) ? b : b + neg;
-    float p0 = ex2_approx(fmaf(a, c, -m_ref));
-    float p1 = ex2_approx(fmaf(b, c, -m_ref));
+    float t0, t1;
+    fma2(t0, t1, a, b, c, -m_ref);
+    float p0 = ex2_approx(t0);
+    float p1 = ex2_approx(t1);
     if (MASKED) {
       p0 = (cbase + 2 * i < kv_valid) ? p0 : 0.f;
       p1 = (cbase + 2 * i + 1 < kv_valid) ? p1 : 0.f;
     }
-    l0 += p0;
-    l1 += p1;
+    add2(l0, l1, p0, p1);
     out[i] = pack_half2(p0, p1);
   }
   return l0 + l1;
