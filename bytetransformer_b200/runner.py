@@ -93,6 +93,9 @@ class PackedRunner:
                     "s_in": torch.cuda.Stream(self.device), "s_out": torch.cuda.Stream(self.device),
                     "ev_in": [torch.cuda.Event() for _ in range(2)], "ev_cmp": [torch.cuda.Event() for _ in range(2)],
                     "ev_out": [torch.cuda.Event() for _ in range(2)], "ev_free_in": [torch.cuda.Event() for _ in range(2)],
+                    # whether a buffer pair has been used before: kept ACROSS calls, because the first copies of a
+                    # call are enqueued while the last micro-batches of the call before may still be computing
+                    "used": [False, False],
                 }
             self._e2e = st
         return self._e2e
@@ -104,7 +107,7 @@ class PackedRunner:
         st = self._e2e_state()
         cmp_stream = torch.cuda.current_stream(self.device)
         h2d = d2h = 0
-        used = [False, False]
+        used = st["used"]
         for i, (mb, cu, xh, oh) in enumerate(zip(self.batches, self.cu_dev, xs_host, outs_host)):
             if mb.tokens == 0:
                 continue

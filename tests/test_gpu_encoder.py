@@ -330,3 +330,37 @@ def test_whole_box_workload_full_size_properties(cuda_device):
         L = xs.shape[0]
         want = _oracle(xs.float()[None], torch.ones(1, L, L), layers32, nh, 64, ln_eps=1e-6)[-1][0]
         assert_close_fp16(got, want, f"sequence {sid} of {L} tokens")
+
+
+@pytest.mark.gpu
+def test_end_to_end_runner_matches_the_device_resident_path(cuda_device):
+    """PackedRunner.run_host (pinned host buffers, copies on their own streams, two device buffers each way) must give
+    exactly what run_device gives on the same micro-batches, also when it is called again at once: the first copies
+    of the second call are enqueued while the last micro-batches of the first may still be computing, and must
+    wait for them."""
+    from bytetransformer_b200.encoder import Encoder
+    from bytetransformer_b200.runner import PackedRunner
+    from bytetransformer_b200.workloads import BERT_BASE, make_weights
+    import copy
+    sh = copy.copy(BERT_BASE)
+    sh.layers = 2
+    enc = Encoder(sh.head_num, 64, make_weights(sh, seed=3, device=cuda_device))
+    rng = np.random.default_rng(5)
+    lens = rng.integers(1, 400, size=90)
+    runner = PackedRunner(enc, lens, np.arange(len(lens)), token_budget=4096)
+    assert len(runner.batches) >= 4
+    xs_h, outs_h = runner.make_host_inputs(seed=1)
+    xs_d = [x.to(cuda_device) for x in xs_h]
+    outs_d = [torch.empty_like(x) for x in xs_d]
+    runner.run_device(xs_d, outs_d)
+    torch.cuda.synchronize(cuda_device)
+    for attempt in range(3):
+        for o in outs_h:
+            o.zero_()
+        runner.run_host(xs_h, outs_h)
+        runner.run_host(xs_h, outs_h)      # back to back: no synchronisation in between
+        torch.cuda.synchronize(cuda_device)
+        for k, (oh, od) in enumerate(zip(outs_h, outs_d)):
+            assert torch.equal(oh, od.cpu()), f"attempt {attempt}: micro-batch {k} differs"
+    assert enc.device_status() == 0
+    enc.close()
