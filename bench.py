@@ -204,8 +204,9 @@ def main():
     ap.add_argument("--max-seqs", type=int, default=0,
                     help="profiling aid: keep only the first N sequences of the workload (small ncu captures)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only the first L layers")
-    ap.add_argument("--sorted-batches", action="store_true",
-                    help="A/B aid: micro-batches of similar lengths instead of the same mix of lengths in each")
+    ap.add_argument("--mixed-batches", action="store_true",
+                    help="A/B aid: equal micro-batches with the same mix of lengths in each, instead of filling "
+                         "one micro-batch after the other to the token budget in length order")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -241,7 +242,7 @@ def main():
     if args.fused_ln >= 0:
         from bytetransformer_b200 import _abi
         _abi.load().bt_debug_set_fused_layernorm(enc._h, args.fused_ln)
-    runner = PackedRunner(enc, lengths, mine, token_budget=args.token_budget, mix=not args.sorted_batches)
+    runner = PackedRunner(enc, lengths, mine, token_budget=args.token_budget, mix=args.mixed_batches)
     budget = runner.token_budget
     xs, outs = runner.make_device_inputs(seed=rank)
 

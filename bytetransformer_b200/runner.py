@@ -39,8 +39,12 @@ def pick_token_budget(total_tokens: int, min_batches: int = 8) -> int:
 
 class PackedRunner:
     def __init__(self, enc: Encoder, lengths: Sequence[int], seq_ids: Sequence[int],
-                 token_budget: int = 0, mix: bool = True):
-        """`token_budget` 0 = pick_token_budget() of this rank's tokens."""
+                 token_budget: int = 0, mix: bool = False):
+        """`token_budget` 0 = pick_token_budget() of this rank's tokens.  `mix` False (default): micro-batches are
+        filled to the budget one after the other in length order, so all but the last hold a whole number of
+        148 x 128-token waves of GEMM tiles (measured on one B200: +0.6 % over equal micro-batches, 30 waves per
+        GEMM and step instead of 32; the attention kernel takes the same time either way); True: equal
+        micro-batches with the same mix of lengths (sharding.micro_batches)."""
         self.enc = enc
         self.device = enc.device
         self.hidden = enc.hidden

@@ -292,7 +292,7 @@ def test_whole_box_workload_full_size_properties(cuda_device):
     assert len(lens) == 1024 and lens.min() >= 16 and lens.max() <= 1024
     weights = make_weights(BERT_BASE, seed=7, device="cpu")
     enc = Encoder(nh, 64, [[t.to(dev) for t in layer] for layer in weights])
-    mbs = micro_batches(lens, np.arange(len(lens)), pick_token_budget(int(lens.sum())))   # as bench.py cuts them at N = 1
+    mbs = micro_batches(lens, np.arange(len(lens)), pick_token_budget(int(lens.sum())), mix=False)   # as bench.py cuts them at N = 1
     assert sum(mb.tokens for mb in mbs) == int(lens.sum())
     order = np.argsort(lens, kind="stable")
     sampled = {int(order[-1]), int(order[len(order) // 2]), int(order[0])}
