@@ -206,6 +206,100 @@ class BertTransformer : public torch::jit::CustomClassHolder {
   Tensor head_info_;
 };
 
+// The whole stack as one object: `ByteTransformer.BertEncoder(head_num, head_size, weights)` with the
+// 12 tensors of every layer in turn (12 * n_layers tensors, each layer in the order of the one-layer class).
+// The reference has no such class: its Python test loops over one-layer objects and so re-packs the tokens for
+// every layer (unit_test/python_scripts/bert_transformer_test.py:191-200); here offsets and packing run once
+// per forward (bt_stack_forward_padded) and the activations stay packed between the layers.
+class BertEncoder : public torch::jit::CustomClassHolder {
+ public:
+  BertEncoder(int64_t head_num, int64_t head_size, std::vector<Tensor> weights)
+      : weights_(std::move(weights)), head_num_(head_num), head_size_(head_size) {
+    TORCH_CHECK(!weights_.empty() && weights_.size() % 12 == 0, "expected 12 weight tensors per layer");
+    n_layers_ = static_cast<int>(weights_.size() / 12);
+    st_ = weights_[0].scalar_type();
+    TORCH_CHECK(st_ == at::ScalarType::Half,
+                "Wrong Tensor type: this build runs fp16 only (the FP32 path is not built for sm_100a)");
+    const bool gb_fp32 = weights_[10].scalar_type() == at::ScalarType::Float;
+    bt_config cfg;
+    cfg.head_num = static_cast<int>(head_num);
+    cfg.size_per_head = static_cast<int>(head_size);
+    cfg.max_batch_size = 65535;
+    cfg.max_seq_len = 1024;
+    cfg.intermediate_mult = 4;
+    cfg.ln_eps = 1e-6f;
+    cfg.gelu_kind = BT_GELU_ERF;
+    cfg.tao = 1.0f;
+    cfg.gamma_beta_fp32 = gb_fp32 ? 1 : 0;
+    cfg.device = weights_[0].device().index();
+    const int rc = bt_create(&cfg, &handle_);
+    TORCH_CHECK(rc == BT_OK, "bt_create failed (code ", rc, "): head_size must be 64 and the device sm_100");
+    for (int l = 0; l < n_layers_; ++l) {
+      std::vector<Tensor> w(weights_.begin() + 12 * l, weights_.begin() + 12 * (l + 1));
+      check_weights(w);
+      for (int i : {4, 5, 10, 11})
+        TORCH_CHECK(w[i].scalar_type() == (gb_fp32 ? at::ScalarType::Float : at::ScalarType::Half),
+                    "LayerNorm gamma/beta must all be fp16 or all be fp32, in every layer");
+      bt_layer_weights lw;
+      const void** p = reinterpret_cast<const void**>(&lw);
+      for (int i = 0; i < 12; ++i) p[i] = w[i].data_ptr();
+      const int rc2 = bt_set_layer_weights(handle_, l, &lw);
+      TORCH_CHECK(rc2 == BT_OK, "bt_set_layer_weights failed: ", bt_last_error(handle_));
+    }
+  }
+  ~BertEncoder() { bt_destroy(handle_); }
+
+  Tensor forward(Tensor input, Tensor attr_mask) { return forwardv2(input, attr_mask, true); }
+
+  // is_remove_padding as in the one-layer class: true = packed path, false = every row computed and the whole
+  // [B,S,S] mask applied element by element.
+  Tensor forwardv2(Tensor input, Tensor attr_mask, bool is_remove_padding) {
+    BT_CHECK_INPUT(input, st_);
+    BT_CHECK_INPUT(attr_mask, st_);
+    TORCH_CHECK(input.dim() == 3, "input must be [batch, seq_len, hidden]");
+    const int batch = static_cast<int>(input.size(0));
+    const int seq = static_cast<int>(input.size(1));
+    TORCH_CHECK(seq <= 1024, "Input seq_len too long");
+    TORCH_CHECK(attr_mask.dim() == 3 && attr_mask.size(0) == batch && attr_mask.size(1) == seq &&
+                    attr_mask.size(2) == seq,
+                "attr_mask must be [batch, seq_len, seq_len]");
+    c10::cuda::CUDAGuard guard(input.device());
+    Tensor out = torch::empty_like(input);
+    size_t bytes = 0;
+    int rc = bt_workspace_bytes(handle_, batch, seq, &bytes);
+    TORCH_CHECK(rc == BT_OK, "bt_workspace_bytes failed: ", bt_last_error(handle_));
+    Tensor buf = torch::empty({static_cast<int64_t>(bytes)}, torch::dtype(torch::kInt8).device(input.device()));
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+    if (is_remove_padding)
+      rc = bt_stack_forward_padded(handle_, n_layers_, input.data_ptr(), attr_mask.data_ptr(), out.data_ptr(),
+                                   buf.data_ptr(), bytes, batch, seq, stream);
+    else
+      rc = bt_stack_forward_padded_general(handle_, n_layers_, input.data_ptr(), attr_mask.data_ptr(), nullptr,
+                                           out.data_ptr(), buf.data_ptr(), bytes, batch, seq, stream);
+    TORCH_CHECK(rc == BT_OK, "stack forward failed: ", bt_last_error(handle_));
+    return out;
+  }
+
+  int64_t num_layers() const { return n_layers_; }
+
+  // 12 * n_layers weight tensors + int64 [head_num, head_size]
+  std::vector<Tensor> get_pickle_info() const {
+    std::vector<Tensor> tmp(weights_);
+    Tensor info = torch::empty({2}, torch::dtype(torch::kInt64));
+    info[0] = head_num_;
+    info[1] = head_size_;
+    tmp.push_back(info);
+    return tmp;
+  }
+
+ private:
+  std::vector<Tensor> weights_;  // keeps the device memory alive; the library stores raw pointers
+  int64_t head_num_, head_size_;
+  int n_layers_ = 0;
+  at::ScalarType st_ = at::ScalarType::Half;
+  bt_handle handle_ = nullptr;
+};
+
 static auto registry = torch::RegisterOperators(
     "ByteTransformer::BertTransformer("
     "int head_num, int head_size,"
@@ -235,6 +329,21 @@ static auto bert_transformer_class =
               return c10::make_intrusive<BertTransformer>(head_num, head_size, state[0], state[1], state[2], state[3],
                                                           state[4], state[5], state[6], state[7], state[8], state[9],
                                                           state[10], state[11]);
+            });
+
+static auto bert_encoder_class =
+    torch::jit::class_<BertEncoder>("ByteTransformer", "BertEncoder")
+        .def(torch::jit::init<int64_t, int64_t, std::vector<Tensor>>())
+        .def("forward", &BertEncoder::forward)
+        .def("forwardv2", &BertEncoder::forwardv2)
+        .def("num_layers", &BertEncoder::num_layers)
+        .def_pickle(
+            [](const c10::intrusive_ptr<BertEncoder>& self) -> std::vector<Tensor> { return self->get_pickle_info(); },
+            [](std::vector<Tensor> state) -> c10::intrusive_ptr<BertEncoder> {
+              const Tensor info = state.back();
+              state.pop_back();
+              return c10::make_intrusive<BertEncoder>(info[0].item().to<int64_t>(), info[1].item().to<int64_t>(),
+                                                      std::move(state));
             });
 
 }  // namespace bt_th

@@ -127,3 +127,60 @@ def test_torchscript_pickle_round_trip(plugin, cuda_device):
     x = torch.randn(2, 16, H, generator=g).half().to(cuda_device)
     m = torch.ones(2, 16, 16, dtype=torch.float16, device=cuda_device)
     assert torch.equal(sm(x, m), sm2(x, m))
+
+
+def test_stack_class_registered(plugin):
+    assert torch.classes.ByteTransformer.BertEncoder is not None
+
+
+@pytest.mark.gpu
+def test_stack_class_equals_the_loop_over_one_layer_objects(plugin, cuda_device):
+    """ByteTransformer.BertEncoder (all layers in one object, tokens packed once per forward) against the reference's
+    way of running a model, a loop over one-layer objects, and against the oracle; with padding removal off it takes
+    the padded path for a causal mask.  Also the pickle state (12 tensors per layer + head info)."""
+    from oracle.bert_oracle import build_attr_mask, encoder_layer
+    g = torch.Generator().manual_seed(77)
+    nh, H, B, S, n_layers = 4, 256, 4, 96, 3
+    layers = [make_layer_weights(H, g, recipe="normal") for _ in range(n_layers)]
+    lens = torch.tensor([96, 1, 50, 77])
+    x = torch.randn(B, S, H, generator=g).half()
+    mask = build_attr_mask(lens, S, torch.float16)
+    flat = [t for w in layers for t in to_device_weights(w, cuda_device)]
+    enc = torch.classes.ByteTransformer.BertEncoder(nh, 64, flat)
+    assert enc.num_layers() == n_layers
+    xd, md = x.to(cuda_device), mask.to(cuda_device)
+    got = enc.forward(xd, md)
+    h = xd
+    for l in range(n_layers):
+        one = torch.classes.ByteTransformer.BertTransformer(nh, 64, *flat[12 * l:12 * (l + 1)])
+        h = one.forward(h, md)
+    valid = torch.arange(S)[None, :] < lens[:, None]
+    d = (got.float() - h.float()).abs().cpu()[valid]
+    assert d.max().item() <= 4e-3 and d.mean().item() <= 1e-4      # the last LayerNorm runs in different kernels
+    assert (got.cpu()[~valid] == 0).all()
+    want = x.float()
+    for w in layers:
+        want = encoder_layer(want, mask.float(), fp16_round(w), nh, 64, ln_eps=1e-6, gelu_kind="erf")
+    assert_close_fp16(got.cpu()[valid], want[valid], "stack class vs oracle")
+    # padded path: causal mask, every row computed
+    causal = torch.tril(torch.ones(S, S)).expand(B, S, S).contiguous().half()
+    want_c = x.float()
+    for w in layers:
+        want_c = encoder_layer(want_c, causal.float(), fp16_round(w), nh, 64, ln_eps=1e-6, gelu_kind="erf")
+    got_c = enc.forwardv2(xd, causal.to(cuda_device), False)
+    assert_close_fp16(got_c.cpu(), want_c, "stack class, causal mask, padded path")
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.enc = enc
+
+        def forward(self, a, m):
+            return self.enc.forward(a, m)
+
+    sm = torch.jit.script(M())
+    buf = io.BytesIO()
+    torch.jit.save(sm, buf)
+    buf.seek(0)
+    sm2 = torch.jit.load(buf)
+    assert torch.equal(sm(xd, md), sm2(xd, md))
