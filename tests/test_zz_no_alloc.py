@@ -87,3 +87,24 @@ def test_static_scratch_rejects_shapes_beyond_its_size(cuda_device):
     torch.cuda.synchronize(cuda_device)
     assert out.abs().max().item() == 0.0                       # nothing ran
     enc.close()
+
+
+@pytest.mark.gpu
+def test_handle_refuses_calls_while_another_device_is_current(cuda_device):
+    """A handle belongs to the device it was created on; with another device current every entry point that takes
+    the handle returns BT_ERR_INVALID_ARG before anything is launched (needs a second GPU to make one current)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from bytetransformer_b200 import _abi
+    lib = _abi.load()
+    B, S, nh = 2, 32, 2
+    enc, x, mask = _make(cuda_device, nh, B, S, 44, [32, 7])
+    out = torch.zeros_like(x)
+    other = 1 if cuda_device.index in (None, 0) else 0
+    with torch.cuda.device(other):
+        rc = lib.bt_layer_forward_padded_static(enc._h, 0, x.data_ptr(), mask.data_ptr(), out.data_ptr(), B, S, 0)
+        assert rc == _abi.BT_ERR_INVALID_ARG
+        assert b"current device" in lib.bt_last_error(enc._h)
+    torch.cuda.synchronize(cuda_device)
+    assert out.abs().max().item() == 0.0
+    enc.close()
