@@ -109,7 +109,7 @@ __device__ __forceinline__ void gstamp(long long* timing, int it, int slot) {
 }
 long long g_dbg_b_lbo = 0, g_dbg_b_sbo = 0, g_dbg_b_kstep = 0, g_dbg_force_block_n = 0, g_dbg_pair_mode = 0;
 long long g_dbg_early_w = 1;  // 1 = W blocks of the first tile requested before the dependency wait
-long long g_dbg_ln_pair = 0;  // GEMM + LayerNorm on SM pairs: 1 = always, anything else = never (default)
+long long g_dbg_ln_pair = 0;  // GEMM + LayerNorm on SM pairs: 0 = for K >= 2048 (default), 1 = always, anything else = never
 long long g_dbg_split_k = 0;  // 0 = policy, < 0 = never, > 0 = that many ranges whenever the shape allows
 
 // ------------------------------------------------------------------------------------------
@@ -1541,14 +1541,13 @@ cudaError_t launch_ln_gemm(const GemmLaunch& g, const GemmArgs& a_in, cudaStream
   auto kern = gemm_f16_ln_kernel;
   if (g.N % 256 != 0 || g.N > 1024 || !g.out_ln || !g.gamma || !g.beta || !g.residual || !g.bias || g.ln_epoch == 0)
     return cudaErrorInvalidValue;
-  // The pair form is selectable (debug key 9 = 1) but not the default.  Measured on 18.9k-row calls, 1800
-  // launches each: FFN2 (K = 3072, main loop the longer leg) 155 against 164 ms of kernel time, attention
-  // output (K = 768, epilogue the longer leg) 97 against 87 ms: a buffer of the shared accumulator is only
-  // released when the epilogue warps of BOTH CTAs are done with it.  With the pair form for FFN2 alone the
-  // kernels of a forward sum to 1 % less, but the forward as a whole does not change (150.6 against
-  // 150.4 ms per step over 20 steps, three A/B pairs on one box): the step runs at the power cap, and a
-  // kernel that finishes sooner by working the tensor cores harder gives the time back in clock.
-  const bool want_pair = g_dbg_ln_pair == 1;
+  // The pair form (main loop on SM pairs, half of the W tile per SM) is used where the main loop is the longer
+  // leg of a tile, i.e. for a long K (FFN2, K = 4 x hidden): measured in situ on 69.6k-row launches, 79.5 against
+  // 85 ms of FFN2 kernel time per three steps and +1.3 % on the whole forward.  For a short K (attention output)
+  // the epilogue is the longer leg, and a buffer of the pair's accumulator is only released when the epilogue
+  // warps of BOTH CTAs are done with it: 11 % slower there.  (On 18.9k-row launches, 1800 per step, the gain
+  // on FFN2 was 5 % of its kernel time and the forward did not move.)  Debug key 9: 1 = always, 2 = never.
+  const bool want_pair = g_dbg_ln_pair == 1 || (g_dbg_ln_pair == 0 && g.K >= 2048);
   if (want_pair) {
     GemmArgs ap = a_in;
     ap.idesc = make_idesc_f16(256, 256, 0, 1);
@@ -1688,7 +1687,7 @@ cudaError_t launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 // N % 256 == 0, 2 never), 6 = programmatic dependent launch on (1, default) / off (0),
 // 7 = split-K of the fp32-sum GEMMs (0 policy, < 0 never, > 0 that many K ranges),
 // 8 = W blocks of a CTA's first tile requested before the dependency wait (1, default) or after (0),
-// 9 = GEMM + LayerNorm on SM pairs (1 always; 0, the default, and 2 never).
+// 9 = GEMM + LayerNorm on SM pairs (0, the default: for K >= 2048; 1 always; 2 never).
 // value 0 restores the default for keys 1-5 and 7.
 // Device buffer of 148 x 16 x 8 long long for clock64 stamps of the GEMM kernels (null = off):
 // slots 0/1 MMA warp (accumulator free, last commit), 2/3 epilogue warp 2 (accumulator ready, tile
