@@ -38,11 +38,11 @@ METRIC = "bert_base_12L_packed_tokens_per_sec"
 UNIT = "tokens/s"
 WORKLOAD = "whole_box_1024x1024"
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch and packed token, mean of the four GEMMs of a layer,
-# from the two ncu captures summarised in profiles/gemm_kernels_microbatch18k.txt (18,645 tokens per launch: 94.7 MB)
-# and profiles/gemm_kernels_microbatch76k.txt (70,734 tokens: 455.3 MB).  The algorithmic bytes of the same launches
+# from the two ncu captures summarised in profiles/gemm_kernels_microbatch18k.txt (18,645 tokens per launch: 95.2 MB)
+# and profiles/gemm_kernels_microbatch76k.txt (70,734 tokens: 456.4 MB).  The algorithmic bytes of the same launches
 # are 7,100 per token; DRAM sees less because a kernel's output is partly still in the 126 MB L2 when the next
 # kernel reads it, the more so the smaller the launch.  Between the two launch sizes the figure is interpolated.
-GEMM_DRAM_BYTES_PER_TOKEN = ((18645, 94.7e6 / 18645), (70734, 455.3e6 / 70734))
+GEMM_DRAM_BYTES_PER_TOKEN = ((18645, 95.2e6 / 18645), (70734, 456.4e6 / 70734))
 
 
 def gemm_dram_bytes_per_launch(tokens_per_launch: float) -> float:
