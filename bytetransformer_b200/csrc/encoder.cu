@@ -125,12 +125,15 @@ struct bt_encoder_s {
   long long launches[BT_PROF_KINDS] = {};
   bool prof_on = false;
   // LayerNorm inside the attention-output / FFN2 GEMM kernel (bt_debug_set_fused_layernorm):
-  // 0 never, 1 from `fused_ln_min_tiles` 128-row tiles upwards, 2 always.  Measured on B200 (12 layers,
-  // hidden 768): at 141-148 row tiles per call the fused kernels make the whole forward 3 % faster
-  // (155.5 vs 160.6 ms per 556,500 tokens); at 42 and 65 row tiles they make it 4 % slower (1.57 vs 1.51 ms,
-  // 2.47 vs 2.37 ms), because the exchange of row statistics between CTAs lengthens the only wave.
+  // 0 never, 1 from `fused_ln_min_tiles` 128-row tiles (of allocated rows) upwards, 2 always.  Measured on
+  // B200 (12 layers, hidden 768, batch 16 through the padded entry point, ms per forward without / with the
+  // fused kernels): 32 row tiles 1.11 / 1.16, 40 tiles 1.45 / 1.28, 48 tiles 1.42 / 1.31, 64 tiles 1.54 / 1.46,
+  // 80 tiles 2.08 / 1.99, 96 tiles 2.14 / 2.10; at 141-148 tiles per call the fused kernels are worth 3 % of the
+  // forward.  Below ~40 tiles the exchange of row statistics between CTAs lengthens the only wave by more
+  // than the saved LayerNorm launch and fp32 round trip.  (An earlier form of the kernels lost up to 65
+  // tiles; the threshold stood at 100 then.)
   int fused_ln = 1;
-  int fused_ln_min_tiles = 100;
+  int fused_ln_min_tiles = 40;
   uint32_t ln_epoch = 0;  // fused LayerNorm launches since the statistics scratch of the current call was zeroed
   bool fused_ln_ffn2_only = false;  // keep the attention-output LayerNorm as its own kernel
   std::vector<cudaEvent_t> ev_pool;
