@@ -13,7 +13,7 @@ waiting for a rank that is gone.
       gone = board.failed_ranks()
       if gone - known: shards = reshard_after_failure(lengths, shards, gone); known = gone
       try: run(shards[rank]); board.heartbeat(step)
-      except Exception as e: board.report_failure(repr(e)); break
+      except Exception as e: board.report_failure(repr(e), step); break
 """
 from __future__ import annotations
 
@@ -68,8 +68,20 @@ class ShardBoard:
     def heartbeat(self, step: int) -> None:
         self.store.set(f"hb/{self.rank}", f"{int(step)}:{time.time():.3f}")
 
-    def report_failure(self, reason: str = "") -> None:
-        self.store.set(f"failed/{self.rank}", reason or "failed")
+    def report_failure(self, reason: str = "", step: int = -1) -> None:
+        """`step`: the step this rank did not finish (-1 = not known).  A survivor that has already run that step
+        runs it again for the sequences it takes over; one that has not, simply runs them as part of it."""
+        self.store.set(f"failed/{self.rank}", f"{int(step)}:{reason or 'failed'}")
+
+    def failure_step(self, rank: int) -> int:
+        """The step rank `rank` reported as unfinished, or -1 (not failed, or not known)."""
+        v = self._get(f"failed/{int(rank)}")
+        if v is None:
+            return -1
+        try:
+            return int(v.split(":", 1)[0])
+        except ValueError:
+            return -1
 
     def _get(self, key: str) -> Optional[str]:
         # (check first: a plain get() would wait for the key)

@@ -59,11 +59,15 @@ WORKER = textwrap.dedent("""
                 assert time.time() < deadline
                 time.sleep(0.01)
             if gone - known:
-                lost = [int(i) for r in gone - known for i in shards[r]]
                 new = reshard_after_failure(lengths, shards, gone)
-                # the step the failed rank did not finish is run again for its sequences by their new owners
-                redo = [i for i in new[rank].tolist() if i in lost]
-                done += [(step - 1, i) for i in redo]
+                for r in gone - known:
+                    # A step the failed rank did not finish and this rank has already run is run again for the
+                    # sequences it takes over; if this rank has not run it yet (the failed rank was ahead), the
+                    # new shard simply includes them.
+                    f = board.failure_step(r)
+                    lost = set(int(i) for i in shards[r])
+                    if 0 <= f < step:
+                        done += [(s, i) for s in range(f, step) for i in new[rank].tolist() if i in lost]
                 shards, known = new, set(gone)
         try:
             if rank == 1 and step == fail_step:
@@ -71,7 +75,7 @@ WORKER = textwrap.dedent("""
             done += [(step, int(i)) for i in shards[rank]]
             board.heartbeat(step)
         except RuntimeError as e:
-            board.report_failure(repr(e))
+            board.report_failure(repr(e), step)
             alive = False
             break
     board.publish("done", json.dumps(done))
