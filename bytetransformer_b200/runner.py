@@ -30,7 +30,7 @@ def pick_token_budget(total_tokens: int, min_batches: int = 4) -> int:
     attention kernel nothing), while the end-to-end path overlaps its host copies with the compute of the
     neighbouring micro-batches and so wants several of them: the first copy in and the last copy out are
     exposed.  With four: the benchmark's 556,500 tokens are cut with a budget of 75,776 on one and two GPUs,
-    37,888 on four and 18,944 on eight.  (Measured on four GPUs: two micro-batches of 69.6k tokens per rank
+    37,888 on four and 18,944 on eight; with `min_batches=1` (resident inputs) always 75,776.  (Measured on four GPUs: two micro-batches of 69.6k tokens per rank
     instead of four of 34.8k give +2 % with resident inputs and -3 % end to end.)"""
     best = 1
     for k in range(1, MAX_TOKEN_BUDGET_UNITS + 1):
@@ -41,8 +41,12 @@ def pick_token_budget(total_tokens: int, min_batches: int = 4) -> int:
 
 class PackedRunner:
     def __init__(self, enc: Encoder, lengths: Sequence[int], seq_ids: Sequence[int],
-                 token_budget: int = 0, mix: bool = False):
-        """`token_budget` 0 = pick_token_budget() of this rank's tokens.  `mix` False (default): micro-batches are
+                 token_budget: int = 0, mix: bool = False, min_batches: int = 4):
+        """`token_budget` 0 = pick_token_budget() of this rank's tokens with at least `min_batches` micro-batches:
+        4 (default) for run_host, whose copies hide behind the neighbouring micro-batches' compute; 1 for a runner
+        that only serves run_device, where nothing is overlapped and the largest launch is the fastest (on eight
+        GPUs a rank's 69.6k tokens of the benchmark then go through in one launch per kernel instead of four).
+        `mix` False (default): micro-batches are
         filled to the budget one after the other in length order, so all but the last hold a whole number of
         148 x 128-token waves of GEMM tiles (measured on one B200: +0.6 % over equal micro-batches, 30 waves per
         GEMM and step instead of 32; the attention kernel takes the same time either way); True: equal
@@ -52,7 +56,8 @@ class PackedRunner:
         self.hidden = enc.hidden
         if token_budget <= 0:
             ids = np.asarray(seq_ids, dtype=np.int64)
-            token_budget = pick_token_budget(int(np.asarray(lengths, dtype=np.int64)[ids].sum()) if len(ids) else 0)
+            token_budget = pick_token_budget(int(np.asarray(lengths, dtype=np.int64)[ids].sum()) if len(ids) else 0,
+                                             min_batches=max(1, int(min_batches)))
             token_budget = max(token_budget, int(np.asarray(lengths)[ids].max()) if len(ids) else 1)
         self.token_budget = int(token_budget)
         self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget, mix=mix)

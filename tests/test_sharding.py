@@ -65,3 +65,5 @@ def test_token_budget_grows_with_the_rank_s_tokens_but_keeps_several_micro_batch
     for total in (556_500, 278_250, 139_125, 69_563, 10_000_000):
         b = pick_token_budget(total)
         assert -(-total // b) >= 4
+        # inputs resident in device memory (nothing to overlap): the largest launch whatever the total
+        assert pick_token_budget(total, min_batches=1) == 4 * TOKEN_BUDGET_UNIT
