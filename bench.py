@@ -79,13 +79,20 @@ class ClockSampler:
             sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
         except Exception:
             sel = str(device_index)
-        self.cmd = ["nvidia-smi", "-i", sel, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"]
+        self.cmd = ["nvidia-smi", "-i", sel, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "50"]
+        self.skip = 0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment (longer on a box with eight GPUs) before its first line: wait for it, so that
+            # a timed region of a few hundred milliseconds is sampled too; what came before the region is left out
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 10.0 and self.proc.poll() is None:
+                time.sleep(0.01)
+            self.skip = len(self.rows)
         except Exception:
             self.proc = None
 
@@ -104,7 +111,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[self.skip:]:
             f = [x.strip() for x in r.split(",")]
             if len(f) < 7:
                 continue
@@ -259,6 +266,8 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+    barrier()
+    runner.run_device(xs, outs)  # the GPUs idled while the sampler came up: one more untimed step
     enc.profile_enable(True)     # resets the launch counters ...
     enc.profile_enable(False)    # ... without bracketing kernels: the headline region runs undisturbed
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
