@@ -207,8 +207,6 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the other BASELINE configurations (N = 1 extra key)")
     ap.add_argument("--token-budget", type=int, default=0)
     ap.add_argument("--e2e-token-budget", type=int, default=0, help="A/B aid: micro-batch budget of the host path")
-    ap.add_argument("--edge-tokens", type=int, default=-1,
-                    help="A/B aid: cap of the first and the last micro-batch of the host path (-1: the runner's policy)")
     ap.add_argument("--fused-ln", type=int, default=-1,
                     help="A/B aid: LayerNorm inside the GEMM kernels: 0 never, 1 default policy, 2 always, 3 FFN2 only")
     ap.add_argument("--max-seqs", type=int, default=0,
@@ -309,8 +307,8 @@ def main():
     e2e = None
     if not args.no_e2e:
         runner_e2e = PackedRunner(enc, lengths, mine, token_budget=args.e2e_token_budget or args.token_budget,
-                                  mix=args.mixed_batches, min_batches=4, edge_tokens=args.edge_tokens)
-        if runner_e2e.token_budget == runner.token_budget and runner_e2e.edge_tokens == 0:
+                                  mix=args.mixed_batches, min_batches=4)
+        if runner_e2e.token_budget == runner.token_budget:
             runner_e2e = runner
         xh, oh = runner_e2e.make_host_inputs(seed=100 + rank)
         h2d = d2h = 0

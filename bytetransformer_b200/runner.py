@@ -39,30 +39,13 @@ def pick_token_budget(total_tokens: int, min_batches: int = 4) -> int:
     return best * TOKEN_BUDGET_UNIT
 
 
-def pick_host_cut(total_tokens: int, min_batches: int = 4):
-    """(token budget, cap of the first and last micro-batch) for a rank that runs `total_tokens` from host memory:
-    pick_token_budget() when that is the largest size; otherwise (fewer tokens than four micro-batches of the
-    largest size) the largest size with a sixteenth of the tokens at either end, so that the first copy in and the
-    last copy out, which nothing covers, are short."""
-    budget = pick_token_budget(total_tokens, min_batches=max(1, int(min_batches)))
-    if min_batches > 1 and budget < MAX_TOKEN_BUDGET_UNITS * TOKEN_BUDGET_UNIT:
-        return MAX_TOKEN_BUDGET_UNITS * TOKEN_BUDGET_UNIT, int(total_tokens) // 16
-    return budget, 0
-
-
 class PackedRunner:
     def __init__(self, enc: Encoder, lengths: Sequence[int], seq_ids: Sequence[int],
-                 token_budget: int = 0, mix: bool = False, min_batches: int = 4, edge_tokens: int = -1):
+                 token_budget: int = 0, mix: bool = False, min_batches: int = 4):
         """`token_budget` 0 = pick_token_budget() of this rank's tokens with at least `min_batches` micro-batches:
         4 (default) for run_host, whose copies hide behind the neighbouring micro-batches' compute; 1 for a runner
         that only serves run_device, where nothing is overlapped and the largest launch is the fastest (on eight
         GPUs a rank's 69.6k tokens of the benchmark then go through in one launch per kernel instead of four).
-        `edge_tokens`: cap of the first and of the last micro-batch (sharding.micro_batches); -1 = policy: a rank
-        whose tokens do not fill four micro-batches of the largest size (the benchmark on four and eight GPUs)
-        takes a sixteenth of its tokens at either end and the largest size in between, so that run_host's first
-        copy in and last copy out are short (measured on one B200 with an eighth of the benchmark, 70.7k tokens:
-        4.3k + 61k + 4.1k tokens 17.75 ms, four micro-batches of 18k 18.2-18.7 ms; with four full-size
-        micro-batches and more, small ends gained nothing).
         `mix` False (default): micro-batches are
         filled to the budget one after the other in length order, so all but the last hold a whole number of
         148 x 128-token waves of GEMM tiles (measured on one B200: +0.6 % over equal micro-batches, 30 waves per
@@ -73,16 +56,11 @@ class PackedRunner:
         self.hidden = enc.hidden
         if token_budget <= 0:
             ids = np.asarray(seq_ids, dtype=np.int64)
-            total = int(np.asarray(lengths, dtype=np.int64)[ids].sum()) if len(ids) else 0
-            if edge_tokens < 0 and not mix:
-                token_budget, edge_tokens = pick_host_cut(total, min_batches)
-            else:
-                token_budget = pick_token_budget(total, min_batches=max(1, int(min_batches)))
+            token_budget = pick_token_budget(int(np.asarray(lengths, dtype=np.int64)[ids].sum()) if len(ids) else 0,
+                                             min_batches=max(1, int(min_batches)))
             token_budget = max(token_budget, int(np.asarray(lengths)[ids].max()) if len(ids) else 1)
         self.token_budget = int(token_budget)
-        self.edge_tokens = max(0, int(edge_tokens))
-        self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget, mix=mix,
-                                                       edge_tokens=0 if mix else self.edge_tokens)
+        self.batches: List[MicroBatch] = micro_batches(lengths, seq_ids, token_budget, mix=mix)
         self.tokens = int(sum(mb.tokens for mb in self.batches))
         self.max_tokens = max([mb.tokens for mb in self.batches] + [1])
         self.max_batch = max([len(mb.seq_ids) for mb in self.batches] + [1])

@@ -67,24 +67,3 @@ def test_token_budget_grows_with_the_rank_s_tokens_but_keeps_several_micro_batch
         assert -(-total // b) >= 4
         # inputs resident in device memory (nothing to overlap): the largest launch whatever the total
         assert pick_token_budget(total, min_batches=1) == 4 * TOKEN_BUDGET_UNIT
-
-
-def test_host_cut_has_small_ends_when_the_rank_has_few_tokens():
-    from bytetransformer_b200.runner import TOKEN_BUDGET_UNIT, pick_host_cut
-    from bytetransformer_b200.sharding import lpt_shards, micro_batches
-    from bytetransformer_b200.workloads import lengths_for
-    lengths = lengths_for("whole_box_1024x1024")
-    assert pick_host_cut(556_500) == (4 * TOKEN_BUDGET_UNIT, 0)          # one and two GPUs: full-size micro-batches
-    assert pick_host_cut(278_250) == (4 * TOKEN_BUDGET_UNIT, 0)
-    assert pick_host_cut(69_563) == (4 * TOKEN_BUDGET_UNIT, 69_563 // 16)  # eight GPUs
-    assert pick_host_cut(69_563, min_batches=1) == (4 * TOKEN_BUDGET_UNIT, 0)
-    mine = lpt_shards(lengths, 8)[3]
-    total = int(lengths[mine].sum())
-    budget, edge = pick_host_cut(total)
-    mbs = micro_batches(lengths, mine, budget, mix=False, edge_tokens=edge)
-    assert len(mbs) == 3 and mbs[0].tokens <= edge and mbs[-1].tokens <= edge and mbs[1].tokens <= budget
-    assert sorted(np.concatenate([m.seq_ids for m in mbs]).tolist()) == sorted(mine.tolist())
-    assert mbs[0].max_len >= mbs[1].max_len >= mbs[-1].max_len            # longest sequences first, shortest last
-    # ends that nothing fits into are simply left out; one or two sequences are never split up
-    assert [m.tokens for m in micro_batches([100, 200, 300], [0, 1, 2], 1000, mix=False, edge_tokens=50)] == [600]
-    assert sum(m.tokens for m in micro_batches([100, 200], [0, 1], 1000, mix=False, edge_tokens=150)) == 300
